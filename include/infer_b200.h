@@ -1,0 +1,115 @@
+/*
+ * infer_b200.h - C ABI of libinfer_b200.so, the sm_100a paged KV-cache path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream handle
+ * (cudaStream_t passed as void*; NULL = the legacy default stream).  No entry point
+ * allocates, frees or synchronises: outputs, pools and scratch memory belong to the
+ * caller, which makes each call capturable in a CUDA graph with static buffers, the
+ * scheme the reference engine uses for decode (infer/engine/model_runner.py:135-198).
+ * All functions return 0 on success and a negative INFER_ERR_* code otherwise;
+ * no C++ exception crosses this boundary.
+ *
+ * Layouts (bit-identical to the reference engine's, infer/engine/model_runner.py:47-126):
+ *   pools          [num_blocks, block_size, n_kv_heads, 128], contiguous, bf16 or e4m3 bytes
+ *   scales (e4m3)  fp32 [num_blocks, n_kv_heads], one per (page, kv head)
+ *   slot_mapping   int32 [n_tokens], flat slot = page * block_size + offset; < 0 = skip row
+ *   block_tables   int32 [batch, bt_stride], page ids, rows padded with -1 (never read
+ *                  beyond ceil(context_len / block_size))
+ *   context_lens   int32 [batch], keys per sequence INCLUDING the token appended this step;
+ *                  0 = the row is skipped and its output left untouched
+ *   cu_seqlens_*   int32 [batch + 1]
+ */
+#ifndef INFER_B200_H
+#define INFER_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define INFER_API __attribute__((visibility("default")))
+#else
+#define INFER_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    INFER_OK = 0,
+    INFER_ERR_NULL = -1,       /* a required pointer is NULL */
+    INFER_ERR_ALIGN = -2,      /* a pointer or stride is not 16-byte aligned */
+    INFER_ERR_STRIDE = -3,     /* a row stride is smaller than the row */
+    INFER_ERR_GEOMETRY = -4,   /* unsupported shape: head_dim != 128, block_size % 256 != 0,
+                                  n_q_heads % n_kv_heads != 0, group > 8, batch > 2048 ... */
+    INFER_ERR_WORKSPACE = -5,  /* scratch buffer missing, misaligned or too small */
+    INFER_ERR_CUDA = -6,       /* a CUDA call failed; see infer_last_cuda_error() */
+    INFER_ERR_DTYPE = -7,      /* pool dtype not valid for this entry point */
+    INFER_ERR_DEVICE = -8      /* the kernel reported a bounded wait that ran out */
+};
+
+enum { INFER_KV_BF16 = 0, INFER_KV_E4M3 = 1 };
+
+/* Opaque pool handle: geometry + the TMA descriptors of the K and V pools.  It owns no
+ * device memory.  Replaces the per-layer cache views the reference hands to its
+ * attention modules (infer/engine/model_runner.py:58-64) and backs the KVCachePool class
+ * (include/kvcache.hpp:32-97). */
+typedef struct infer_kv_pool infer_kv_pool_t;
+
+INFER_API int infer_kv_pool_create(infer_kv_pool_t** pool, void* k_cache, void* v_cache,
+                         float* k_scale, float* v_scale, int64_t num_blocks, int block_size,
+                         int n_kv_heads, int head_dim, int dtype);
+INFER_API int infer_kv_pool_destroy(infer_kv_pool_t* pool);
+
+/* KV append.  Replaces store_kvcache / store_kvcache_kernel (infer/ops/attention.py:16-45):
+ * row i of k and v ([n_tokens, n_kv_heads, 128] bf16, row pitch k_row_stride / v_row_stride
+ * ELEMENTS, so column slices of a fused qkv output are accepted as the reference accepts
+ * them) goes to flat slot slot_mapping[i].  An e4m3 pool quantises on write with one scale
+ * per (page, kv head) and needs infer_kv_append_workspace_bytes() of scratch. */
+INFER_API int infer_kv_append(const infer_kv_pool_t* pool, const void* k, const void* v,
+                    int64_t k_row_stride, int64_t v_row_stride, const int32_t* slot_mapping,
+                    int64_t n_tokens, void* workspace, size_t workspace_bytes, void* stream);
+INFER_API size_t infer_kv_append_workspace_bytes(const infer_kv_pool_t* pool);
+
+/* Paged decode attention.  Replaces the decode branch of Attention.forward
+ * (flash_attn_with_kvcache(q[:,None], k_cache, v_cache, cache_seqlens, block_table,
+ * softmax_scale, causal=True), infer/ops/attention.py:117-121) and fills the empty
+ * flash_attn_decode stub (src/operators/flashattn/flashattn_decode.cu:1-13).
+ * q, out: bf16 [batch, n_q_heads, 128] contiguous. */
+INFER_API int infer_paged_decode(const infer_kv_pool_t* pool, void* out, const void* q,
+                       const int32_t* context_lens, const int32_t* block_tables,
+                       int64_t bt_stride, int batch, int n_q_heads, float softmax_scale,
+                       void* workspace, size_t workspace_bytes, void* stream);
+INFER_API size_t infer_paged_decode_workspace_bytes(const infer_kv_pool_t* pool, int batch, int n_q_heads);
+
+/* Paged chunked-prefill attention.  Replaces the prefill branch
+ * (flash_attn_varlen_func(q, k_cache, v_cache, cu_seqlens_q/k, max_seqlen_q/k,
+ * softmax_scale, causal=True, block_table), infer/ops/attention.py:110-116).  Keys of
+ * sequence b are its first cu_seqlens_k[b+1]-cu_seqlens_k[b] cached tokens (append the
+ * chunk first); the causal mask is aligned to the bottom-right corner.
+ * q, out: bf16 [total_q, n_q_heads, 128] contiguous. */
+INFER_API int infer_paged_prefill(const infer_kv_pool_t* pool, void* out, const void* q,
+                        const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                        const int32_t* block_tables, int64_t bt_stride, int batch,
+                        int max_seqlen_q, int max_seqlen_k, int n_q_heads,
+                        float softmax_scale, void* stream);
+
+/* Dense causal attention.  Replaces flash_attn_prefill_impl
+ * (src/operators/flashattn/flashattn.cu:269-328; schema src/bindings.cpp:9):
+ * Q, O bf16 [B, Hq, S, 128], K, V bf16 [B, Hkv, S, 128], scale 1/sqrt(128) computed
+ * inside, GQA by kv_head = head / (Hq/Hkv). */
+INFER_API int infer_flash_attn_prefill(const void* q, const void* k, const void* v, void* o,
+                             int batch, int n_q_heads, int n_kv_heads, int seq_len, void* stream);
+
+/* Reads the device status word the last decode call on this workspace left behind
+ * (synchronises the stream).  0 = no bounded wait ran out. */
+INFER_API int infer_paged_decode_status(const void* workspace, void* stream);
+
+INFER_API const char* infer_strerror(int code);
+INFER_API int infer_last_cuda_error(void);
+INFER_API int infer_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* INFER_B200_H */

@@ -1,0 +1,159 @@
+// Shared declarations of the sm_100a paged KV-cache kernels: pool handle, error
+// plumbing, and the PTX wrappers (mbarrier, TMA, ldmatrix, mma) the kernels use.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/infer_b200.h"
+
+namespace ib {
+
+constexpr int kHeadDim = 128;
+constexpr int kMaxBatch = 2048;      // context-length prefix table kept in shared memory
+constexpr int kMaxGroup = 8;         // query heads per KV head
+
+// One tensor map per (pool, token-box height): dims {128, n_kv_heads, num_slots},
+// box {inner, 1, rows}, 128-byte swizzle.
+struct PoolMaps {
+    CUtensorMap k;
+    CUtensorMap v;
+};
+
+}  // namespace ib
+
+struct infer_kv_pool {
+    void* k_cache;
+    void* v_cache;
+    float* k_scale;
+    float* v_scale;
+    int64_t num_blocks;
+    int64_t num_slots;
+    int block_size;
+    int n_kv_heads;
+    int head_dim;
+    int dtype;        // INFER_KV_BF16 | INFER_KV_E4M3
+    int elem_bytes;
+    int sm_count;
+    int device;
+    // token-box heights 16, 32, 64, 128 (index = log2(rows) - 4)
+    ib::PoolMaps maps[4];
+};
+
+namespace ib {
+
+void set_cuda_error(cudaError_t e);
+int check_launch();
+// Encodes a 3-D tiled tensor map with 128-byte swizzle; returns INFER_OK or INFER_ERR_CUDA.
+int encode_map_3d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t d0, uint64_t d1,
+                  uint64_t d2, uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0,
+                  uint32_t b1, uint32_t b2);
+
+#define IB_CUDA(expr)                                   \
+    do {                                                \
+        cudaError_t e_ = (expr);                        \
+        if (e_ != cudaSuccess) {                        \
+            ib::set_cuda_error(e_);                     \
+            return INFER_ERR_CUDA;                      \
+        }                                               \
+    } while (0)
+
+__host__ __device__ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// ------------------------------------------------------------------ device helpers
+#ifdef __CUDACC__
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_mbar_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: returns false when the limit ran out (about a second of polling).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < (1u << 22); ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (i > 64) __nanosleep(i > 4096 ? 256 : 32);
+    }
+    return false;
+}
+
+// 3-D tiled TMA load global -> shared of this CTA, completion on an mbarrier.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x,
+                                            int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                              uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+// D(16x8,f32) += A(16x16,bf16,row) * B(16x8,bf16,col)
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&t);
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// Byte offset of 16-byte chunk `chunk` of row `row` in a [rows][128 B] tile written by TMA
+// with 128-byte swizzle (tile base 1024-byte aligned).
+__device__ __forceinline__ uint32_t swz128(int row, int chunk) {
+    return static_cast<uint32_t>(row * 128 + ((chunk ^ (row & 7)) << 4));
+}
+
+#endif  // __CUDACC__
+
+}  // namespace ib

@@ -1,0 +1,116 @@
+// Work decomposition shared by the paged decode kernels and their reduce kernel.
+//
+// A "tile" is TT consecutive tokens of one sequence for one group of HPC kv heads.  Tiles
+// are numbered sequence by sequence, head group by head group:
+//     first(b, hg) = NG * tiles_before(b) + hg * tiles(b),   NG = n_kv_heads / HPC.
+// CTA c of a grid of `grid` CTAs owns the tile range [c * chunk, (c + 1) * chunk) with
+// chunk = ceil(total / grid), so every CTA streams the same number of KV bytes whatever
+// the mix of context lengths.  A range is cut into segments at (sequence, head group)
+// boundaries.  A segment that covers its whole (b, hg) writes the output row directly;
+// otherwise it leaves an un-normalised partial (running max, sum, accumulator) in one of
+// the CTA's two scratch slots: slot 0 when the segment continues a (b, hg) begun by an
+// earlier CTA, slot 1 when it begins one that a later CTA continues.  The reduce kernel
+// merges, for every (b, hg) that spans several CTAs, slot 1 of the first CTA with slot 0
+// of the following ones.
+#pragma once
+
+#include "common.cuh"
+
+namespace ib {
+
+constexpr int kStatusMagic = 0x5AFE0000;   // header[0] == magic | code after a bounded wait ran out
+
+struct DecodeParams {
+    const __nv_bfloat16* q;
+    __nv_bfloat16* out;
+    const int32_t* context_lens;
+    const int32_t* block_tables;
+    int64_t bt_stride;
+    const void* k_cache;
+    const void* v_cache;
+    const float* k_scale;
+    const float* v_scale;
+    int batch;
+    int n_q_heads;
+    int n_kv_heads;
+    int group;        // query heads per kv head
+    int block_size;
+    int num_blocks;
+    int hpc;          // kv heads per tile
+    int tile_tokens;  // TT
+    float scale_log2; // softmax_scale * log2(e)
+    // scratch
+    int* header;      // [0] status, [1] total tiles, [2] chunk, [3] grid
+    int* prefix;      // [batch + 1] tiles before each sequence
+    float* ws_ml;     // [grid * 2][rows][2]
+    float* ws_o;      // [grid * 2][rows][128]
+};
+
+struct DecodeLayout {
+    size_t header_off, prefix_off, ml_off, o_off, total;
+};
+
+inline DecodeLayout decode_layout(int grid, int rows) {
+    DecodeLayout l;
+    l.header_off = 0;
+    l.prefix_off = 64;
+    l.ml_off = (l.prefix_off + size_t(kMaxBatch + 1) * 4 + 255) / 256 * 256;
+    l.o_off = (l.ml_off + size_t(grid) * 2 * rows * 2 * 4 + 255) / 256 * 256;
+    l.total = l.o_off + size_t(grid) * 2 * rows * kHeadDim * 4;
+    return l;
+}
+
+#ifdef __CUDACC__
+
+// Exclusive prefix of tiles per sequence into shared memory (s_tp[batch] = total).
+// Every thread of the CTA must call it; ends with a __syncthreads().
+__device__ inline void build_tile_prefix(const int32_t* __restrict__ context_lens, int batch, int tile_tokens,
+                                         int* s_tp, int* s_scratch /* blockDim.x ints */) {
+    const int nt = blockDim.x, tid = threadIdx.x;
+    const int per = (batch + nt - 1) / nt;
+    const int lo = min(batch, tid * per), hi = min(batch, lo + per);
+    int sum = 0;
+    for (int i = lo; i < hi; ++i) sum += (max(context_lens[i], 0) + tile_tokens - 1) / tile_tokens;
+    s_scratch[tid] = sum;
+    __syncthreads();
+    // Hillis-Steele inclusive scan over nt values
+    for (int off = 1; off < nt; off <<= 1) {
+        int v = tid >= off ? s_scratch[tid - off] : 0;
+        __syncthreads();
+        s_scratch[tid] += v;
+        __syncthreads();
+    }
+    int run = s_scratch[tid] - sum;
+    for (int i = lo; i < hi; ++i) {
+        s_tp[i] = run;
+        run += (max(context_lens[i], 0) + tile_tokens - 1) / tile_tokens;
+    }
+    if (tid == nt - 1) s_tp[batch] = s_scratch[nt - 1];
+    __syncthreads();
+}
+
+struct Segment {
+    int b, hg, t0, t1, ntiles;
+};
+
+// Segment of the (b, hg) that contains global tile g, cut at `hi`.
+__device__ __forceinline__ Segment locate_segment(const int* s_tp, int batch, int ng, int g, int hi) {
+    // last b with ng * s_tp[b] <= g  (skips empty sequences, whose prefix equals the next one's)
+    int lo_b = 0, hi_b = batch;   // invariant: ng*s_tp[lo_b] <= g < ng*s_tp[hi_b]
+    while (hi_b - lo_b > 1) {
+        const int mid = (lo_b + hi_b) >> 1;
+        if (ng * s_tp[mid] <= g) lo_b = mid; else hi_b = mid;
+    }
+    Segment s;
+    s.b = lo_b;
+    s.ntiles = s_tp[lo_b + 1] - s_tp[lo_b];
+    const int rel = g - ng * s_tp[lo_b];
+    s.hg = rel / s.ntiles;
+    s.t0 = rel - s.hg * s.ntiles;
+    s.t1 = min(s.ntiles, s.t0 + (hi - g));
+    return s;
+}
+
+#endif  // __CUDACC__
+
+}  // namespace ib

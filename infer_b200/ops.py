@@ -1,0 +1,211 @@
+"""Operators of the paged KV-cache path, behind the reference's call signatures.
+
+* ``store_kvcache(key, value, k_cache, v_cache, slot_mapping)`` - same arguments and the
+  same stride asserts as the reference's Triton wrapper (infer/ops/attention.py:38-45).
+* ``paged_attn_decode`` / ``paged_attn_prefill`` - the two calls the reference makes into
+  the flash_attn package (infer/ops/attention.py:110-121), with the keyword names it uses.
+* ``flash_attn_prefill(Q, K, V, O)`` - the reference's own dense op (src/bindings.cpp:9).
+
+Every op launches hand-written sm_100a kernels through the C ABI on the current CUDA
+stream and is also registered as ``torch.ops._C.<name>`` with out-parameter schemas in
+the style of src/bindings.cpp:4-23.  Nothing here computes on the CPU or through PyTorch.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import torch
+
+from . import _lib
+
+_POOLS: dict = {}
+_WORKSPACES: dict = {}
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p(0)
+
+
+class KVPool:
+    """Handle on a pair of page pools ``[num_blocks, block_size, Hkv, 128]`` (bf16, or uint8
+    holding e4m3 bytes together with fp32 ``[num_blocks, Hkv]`` scales).  Owns no memory;
+    keeps the tensors alive and carries the TMA descriptors built once by the library."""
+
+    def __init__(self, k_cache, v_cache, k_scale=None, v_scale=None):
+        for t in (k_cache, v_cache):
+            if not (t.is_cuda and t.dim() == 4 and t.is_contiguous()):
+                raise ValueError("pools must be contiguous CUDA tensors [num_blocks, block_size, Hkv, head_dim]")
+        if k_cache.shape != v_cache.shape or k_cache.dtype != v_cache.dtype:
+            raise ValueError("k and v pools must agree in shape and dtype")
+        fp8 = k_cache.dtype in (torch.uint8, torch.float8_e4m3fn)
+        if not fp8 and k_cache.dtype != torch.bfloat16:
+            raise ValueError("pools must be bf16 or e4m3 bytes")
+        if fp8:
+            nb, _, hkv, _ = k_cache.shape
+            for s in (k_scale, v_scale):
+                if s is None or s.dtype != torch.float32 or tuple(s.shape) != (nb, hkv) or not s.is_contiguous():
+                    raise ValueError("e4m3 pools need contiguous fp32 scales [num_blocks, Hkv]")
+        self.k_cache, self.v_cache, self.k_scale, self.v_scale = k_cache, v_cache, k_scale, v_scale
+        self.fp8 = fp8
+        self.num_blocks, self.block_size, self.n_kv_heads, self.head_dim = k_cache.shape
+        self.device = k_cache.device
+        lib = _lib.load()
+        handle = C.c_void_p()
+        with torch.cuda.device(self.device):
+            rc = lib.infer_kv_pool_create(C.byref(handle), _ptr(k_cache), _ptr(v_cache), _ptr(k_scale), _ptr(v_scale),
+                                          self.num_blocks, self.block_size, self.n_kv_heads, self.head_dim,
+                                          _lib.KV_E4M3 if fp8 else _lib.KV_BF16)
+        _lib.check(rc, "infer_kv_pool_create")
+        self.handle = handle
+
+    def __del__(self):
+        h = getattr(self, "handle", None)
+        if h:
+            _lib.load().infer_kv_pool_destroy(h)
+            self.handle = None
+
+
+def pool_of(k_cache, v_cache, k_scale=None, v_scale=None) -> KVPool:
+    """Pool handle for these cache tensors, created on first use (one per layer in practice)."""
+    key = (k_cache.data_ptr(), v_cache.data_ptr(), tuple(k_cache.shape), k_cache.dtype,
+           k_scale.data_ptr() if k_scale is not None else 0)
+    pool = _POOLS.get(key)
+    if pool is None:
+        pool = _POOLS[key] = KVPool(k_cache, v_cache, k_scale, v_scale)
+    return pool
+
+
+def release_pools():
+    _POOLS.clear()
+    _WORKSPACES.clear()
+
+
+def _workspace(device, nbytes: int) -> torch.Tensor:
+    """Zero-initialised scratch, grown on demand, one per device (never inside a graph
+    capture: call the op once eagerly first, as the reference's capture loop does)."""
+    ws = _WORKSPACES.get(device)
+    if ws is None or ws.numel() < nbytes:
+        ws = _WORKSPACES[device] = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+    return ws
+
+
+# --------------------------------------------------------------------------- append
+def store_kvcache(key, value, k_cache, v_cache, slot_mapping, k_scale=None, v_scale=None):
+    n, num_heads, head_dim = key.shape
+    d = num_heads * head_dim
+    assert key.stride(-1) == 1 and value.stride(-1) == 1
+    assert key.stride(1) == head_dim and value.stride(1) == head_dim
+    assert k_cache.stride(1) == d and v_cache.stride(1) == d
+    assert slot_mapping.numel() == n
+    if key.dtype != torch.bfloat16 or value.dtype != torch.bfloat16:
+        raise RuntimeError("store_kvcache: key/value must be bf16")
+    if slot_mapping.dtype != torch.int32 or not slot_mapping.is_cuda:
+        raise RuntimeError("store_kvcache: slot_mapping must be an int32 CUDA tensor")
+    pool = pool_of(k_cache, v_cache, k_scale, v_scale)
+    lib = _lib.load()
+    ws, ws_bytes = None, 0
+    if pool.fp8:
+        ws_bytes = lib.infer_kv_append_workspace_bytes(pool.handle)
+        ws = _workspace(pool.device, ws_bytes)
+    with torch.cuda.device(pool.device):
+        rc = lib.infer_kv_append(pool.handle, _ptr(key), _ptr(value), key.stride(0), value.stride(0),
+                                 _ptr(slot_mapping), n, _ptr(ws), ws_bytes, _stream())
+    _lib.check(rc, "store_kvcache")
+
+
+# --------------------------------------------------------------------------- decode
+def paged_attn_decode(q, k_cache, v_cache, cache_seqlens, block_table, softmax_scale,
+                      out=None, k_scale=None, v_scale=None):
+    """q [B, Hq, 128] (or [B, 1, Hq, 128] as the reference passes it) -> same shape."""
+    shape = q.shape
+    q3 = q.reshape(shape[0], shape[-2], shape[-1])
+    if q3.dtype != torch.bfloat16 or not q3.is_contiguous():
+        raise RuntimeError("paged_attn_decode: q must be contiguous bf16")
+    for name, t in (("cache_seqlens", cache_seqlens), ("block_table", block_table)):
+        if t.dtype != torch.int32 or not t.is_cuda:
+            raise RuntimeError(f"paged_attn_decode: {name} must be an int32 CUDA tensor")
+    if block_table.stride(-1) != 1:
+        raise RuntimeError("paged_attn_decode: block_table rows must be contiguous")
+    pool = pool_of(k_cache, v_cache, k_scale, v_scale)
+    o = torch.empty_like(q3) if out is None else out.view(q3.shape)
+    lib = _lib.load()
+    b, hq, _ = q3.shape
+    need = lib.infer_paged_decode_workspace_bytes(pool.handle, b, hq)
+    ws = _workspace(pool.device, need)
+    with torch.cuda.device(pool.device):
+        rc = lib.infer_paged_decode(pool.handle, _ptr(o), _ptr(q3), _ptr(cache_seqlens), _ptr(block_table),
+                                    block_table.stride(0), b, hq, float(softmax_scale), _ptr(ws), ws.numel(),
+                                    _stream())
+        _lib.check(rc, "paged_attn_decode")
+        if os.environ.get("INFER_B200_CHECK") == "1":
+            _lib.check(lib.infer_paged_decode_status(_ptr(ws), _stream()), "paged_attn_decode (device status)")
+    return o.view(shape)
+
+
+# --------------------------------------------------------------------------- prefill
+def paged_attn_prefill(q, k_cache, v_cache, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
+                       softmax_scale, block_table, out=None):
+    """q [total_q, Hq, 128]; keys come from the pools through block_table; causal,
+    bottom-right aligned (the flash_attn_varlen_func convention)."""
+    if q.dtype != torch.bfloat16 or not q.is_contiguous() or q.dim() != 3:
+        raise RuntimeError("paged_attn_prefill: q must be contiguous bf16 [total_q, Hq, 128]")
+    for name, t in (("cu_seqlens_q", cu_seqlens_q), ("cu_seqlens_k", cu_seqlens_k), ("block_table", block_table)):
+        if t.dtype != torch.int32 or not t.is_cuda:
+            raise RuntimeError(f"paged_attn_prefill: {name} must be an int32 CUDA tensor")
+    pool = pool_of(k_cache, v_cache)
+    o = torch.empty_like(q) if out is None else out
+    lib = _lib.load()
+    with torch.cuda.device(pool.device):
+        rc = lib.infer_paged_prefill(pool.handle, _ptr(o), _ptr(q), _ptr(cu_seqlens_q), _ptr(cu_seqlens_k),
+                                     _ptr(block_table), block_table.stride(0), cu_seqlens_q.numel() - 1,
+                                     int(max_seqlen_q), int(max_seqlen_k), q.shape[1], float(softmax_scale),
+                                     _stream())
+    _lib.check(rc, "paged_attn_prefill")
+    return o
+
+
+def flash_attn_prefill(Q, K, V, O):
+    """Dense causal attention, Q/O [B, Hq, S, 128], K/V [B, Hkv, S, 128]; writes O."""
+    for t in (Q, K, V, O):
+        if t.dtype != torch.bfloat16 or not t.is_contiguous() or not t.is_cuda or t.dim() != 4:
+            raise RuntimeError("flash_attn_prefill: tensors must be contiguous bf16 CUDA [B, H, S, 128]")
+    if Q.shape[-1] != 128 or K.shape != V.shape or O.shape != Q.shape or K.shape[2] != Q.shape[2]:
+        raise RuntimeError("flash_attn_prefill: shape mismatch")
+    lib = _lib.load()
+    with torch.cuda.device(Q.device):
+        rc = lib.infer_flash_attn_prefill(_ptr(Q), _ptr(K), _ptr(V), _ptr(O), Q.shape[0], Q.shape[1], K.shape[1],
+                                          Q.shape[2], _stream())
+    _lib.check(rc, "flash_attn_prefill")
+
+
+# --------------------------------------------------------------------------- torch.ops._C
+_REGISTERED = False
+
+
+def register_torch_ops():
+    """Registers the ops under the ``_C`` namespace the reference uses
+    (TORCH_LIBRARY(_C), src/bindings.cpp:4-37), CUDA dispatch key only."""
+    global _REGISTERED, _torch_lib
+    if _REGISTERED:
+        return
+    lib = torch.library.Library("_C", "FRAGMENT")
+    lib.define("flash_attn_prefill(Tensor Q, Tensor K, Tensor V, Tensor! O) -> ()")
+    lib.define("store_kvcache(Tensor key, Tensor value, Tensor! k_cache, Tensor! v_cache, Tensor slot_mapping) -> ()")
+    lib.define("paged_attn_decode(Tensor! out, Tensor q, Tensor k_cache, Tensor v_cache, Tensor cache_seqlens, "
+               "Tensor block_table, float softmax_scale) -> ()")
+    lib.define("paged_attn_prefill(Tensor! out, Tensor q, Tensor k_cache, Tensor v_cache, Tensor cu_seqlens_q, "
+               "Tensor cu_seqlens_k, int max_seqlen_q, int max_seqlen_k, float softmax_scale, Tensor block_table) -> ()")
+    lib.impl("flash_attn_prefill", lambda Q, K, V, O: flash_attn_prefill(Q, K, V, O), "CUDA")
+    lib.impl("store_kvcache", lambda k, v, kc, vc, sm: store_kvcache(k, v, kc, vc, sm), "CUDA")
+    lib.impl("paged_attn_decode",
+             lambda out, q, kc, vc, sl, bt, sc: (paged_attn_decode(q, kc, vc, sl, bt, sc, out=out), None)[1], "CUDA")
+    lib.impl("paged_attn_prefill",
+             lambda out, q, kc, vc, cq, ck, mq, mk, sc, bt:
+             (paged_attn_prefill(q, kc, vc, cq, ck, mq, mk, sc, bt, out=out), None)[1], "CUDA")
+    _torch_lib = lib
+    _REGISTERED = True
