@@ -1,0 +1,338 @@
+"""Benchmark of the paged KV-cache hot path: KV append + paged decode attention.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload at N GPUs: the Qwen3-8B decode shape (32 query / 8 KV heads, head_dim 128,
+page 256 tokens, context lengths uniform in [512, 8192], one appended token per sequence),
+batch 64*N, KV heads sharded N ways (rank r owns 8/N KV heads and their query heads of
+every sequence; page ids, slots and lengths are replicated).  Per-GPU KV bytes are the same
+at every N (weak scaling); at N=1 it is exactly the 64-sequence configuration.  A step is
+one append (one new row per sequence) followed by one paged decode attention pass.
+
+One JSON line is printed by rank 0:
+  value      whole-job KV GB/s: algorithmic KV bytes of all ranks / step time (max over ranks),
+             inputs resident in HBM, timed with CUDA events;
+  e2e        same metric with the step's host inputs copied from pinned memory and the
+             attention output copied back inside the timed region;
+  roofline   the decode kernels (partition + reduce) against the measured HBM copy peak;
+  append     bulk-append throughput (32768 rows, the chunked-prefill append) in tok/s;
+  cpu_baseline  the torch-CPU restatement of the reference path, timed on a sample.
+
+``--impl reference`` times that CPU restatement alone (the reference has no CPU or
+buildable GPU implementation of this path; the oracle port stands in for it).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "paged decode-attn KV GB/s"
+UNIT = "GB/s"
+BASE_BATCH = 64
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peak():
+    try:
+        with open(ROOT / "MEASURED_PEAKS.json") as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[3:7]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_workload(world: int, rank: int, device, base_batch: int = BASE_BATCH):
+    from infer_b200 import workloads
+    return workloads.config1(device=device, seed=1001, batch=base_batch * world, n_kv_heads=8 // world,
+                             n_q_heads=32 // world, tensor_seed=1001 + rank)
+
+
+# ------------------------------------------------------------------------------- CPU leg
+def cpu_sample(w, n_seqs: int, repeats: int):
+    """Times append + decode of the torch-CPU restatement on the first ``n_seqs`` sequences.
+    Returns (seconds per pass, KV bytes per pass, threads)."""
+    from oracle import paged_kv_oracle as oracle
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    pages = sorted({p for t in w.block_tables[:n_seqs] for p in t})
+    remap = {p: i for i, p in enumerate(pages)}
+    idx = torch.tensor(pages, device=w.k_cache.device)
+    kc, vc = w.k_cache[idx].cpu(), w.v_cache[idx].cpu()
+    tables = [[remap[p] for p in t] for t in w.block_tables[:n_seqs]]
+    width = max(len(t) for t in tables)
+    bt = torch.tensor([t + [-1] * (width - len(t)) for t in tables], dtype=torch.int32)
+    lens = w.context_lens[:n_seqs]
+    cl = torch.tensor(lens, dtype=torch.int32)
+    slots = torch.tensor([t[(n - 1) // 256] * 256 + (n - 1) % 256 for t, n in zip(tables, lens)], dtype=torch.int32)
+    q, k, v = w.q[:n_seqs].cpu(), w.k[:n_seqs].cpu(), w.v[:n_seqs].cpu()
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        oracle.store_kvcache(k, v, kc, vc, slots)
+        oracle.paged_decode_bf16_sdpa(q, kc, vc, cl, bt, w.scale)
+        best = min(best, time.perf_counter() - t0)
+    kv_bytes = sum(lens) * w.n_kv_heads * 128 * 2 * 2
+    return best, kv_bytes, threads
+
+
+def run_reference(args, rank, world):
+    """The reference arm: the CPU restatement on the host cores, rank 0 only."""
+    if rank != 0:
+        return
+    from infer_b200 import workloads
+    w = workloads.config1(device="cpu", seed=1001, batch=8, tensor_seed=1001)   # sample: first 8 sequences' lengths
+    n_seqs = 8
+    for _ in range(args.warmup):
+        cpu_sample(w, n_seqs, 1)
+    times = []
+    for _ in range(args.steps):
+        t, kv_bytes, threads = cpu_sample(w, n_seqs, 1)
+        times.append(t)
+    t = statistics.mean(times)
+    value = kv_bytes / t / 1e9
+    sample = f"append + decode of {n_seqs} sequences ({kv_bytes / 1e6:.0f} MB of KV) of the same length distribution"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "qwen3-8b decode shape, sample of 8 sequences on host cores", "block_size": 256},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ------------------------------------------------------------------------------- GPU leg
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=BASE_BATCH,
+                    help="sequences per GPU share (default 64 = the benchmark configuration; smaller values "
+                         "give the small case used for profiler captures)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    if 8 % world:
+        raise SystemExit("KV-head sharding needs a GPU count that divides 8")
+
+    import torch.distributed as dist
+    from infer_b200 import ops
+
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    w = build_workload(world, rank, device, args.batch)
+    cl = w.context_lens_tensor().to(device)
+    bt = w.block_tables_tensor().to(device)
+    slots = w.slot_mapping.to(device)
+    out = torch.empty_like(w.q)
+    kv_bytes = w.kv_bytes()                      # this rank's algorithmic KV bytes per step
+    stream = torch.cuda.current_stream()
+
+    def step():
+        ops.store_kvcache(w.k, w.v, w.k_cache, w.v_cache, slots)
+        ops.paged_attn_decode(w.q, w.k_cache, w.v_cache, cl, bt, w.scale, out=out)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+
+    # ---- device-resident timing: K steps back to back, per-step events around the decode
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        start.record(stream)
+        for i in range(args.steps):
+            ev[i][0].record(stream)
+            ops.store_kvcache(w.k, w.v, w.k_cache, w.v_cache, slots)
+            ev[i][1].record(stream)
+            ops.paged_attn_decode(w.q, w.k_cache, w.v_cache, cl, bt, w.scale, out=out)
+            ev[i][2].record(stream)
+        stop.record(stream)
+        barrier()
+        # keep the sampler alive for at least a few samples on very short runs
+        if start.elapsed_time(stop) < 500:
+            t_end = time.time() + 0.6
+            while time.time() < t_end:
+                step()
+            torch.cuda.synchronize()
+    total_ms = start.elapsed_time(stop)
+    decode_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+    append_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+
+    # ---- end to end: host inputs in pinned memory, output read back, every step
+    host = {k: getattr(w, k).cpu().pin_memory() for k in ("q", "k", "v")}
+    host.update(slots=slots.cpu().pin_memory(), cl=cl.cpu().pin_memory(), bt=bt.cpu().pin_memory())
+    dev = {k: torch.empty_like(v, device=device) for k, v in host.items()}
+    out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    h2d = sum(v.numel() * v.element_size() for v in host.values())
+    d2h = out_host.numel() * out_host.element_size()
+
+    def e2e_step():
+        for k, v in host.items():
+            dev[k].copy_(v, non_blocking=True)
+        ops.store_kvcache(dev["k"], dev["v"], w.k_cache, w.v_cache, dev["slots"])
+        ops.paged_attn_decode(dev["q"], w.k_cache, w.v_cache, dev["cl"], dev["bt"], w.scale, out=out)
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()       # the caller reads the result every step
+
+    for _ in range(args.warmup):
+        e2e_step()
+    barrier()
+    e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e_start.record(stream)
+    for _ in range(args.steps):
+        e2e_step()
+    e_stop.record(stream)
+    barrier()
+    e2e_ms = e_start.elapsed_time(e_stop)
+
+    # ---- bulk append (the chunked-prefill append: 32768 rows)
+    n_bulk = 32768
+    hkv = w.n_kv_heads
+    gen = torch.Generator(device=device).manual_seed(5)
+    bk = torch.randn(n_bulk, hkv, 128, generator=gen, device=device).bfloat16()
+    bv = torch.randn(n_bulk, hkv, 128, generator=gen, device=device).bfloat16()
+    bslots = torch.randperm(w.num_blocks * 256, generator=gen, device=device)[:n_bulk].to(torch.int32)
+    for _ in range(3):
+        ops.store_kvcache(bk, bv, w.k_cache, w.v_cache, bslots)
+    torch.cuda.synchronize()
+    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 20
+    a0.record(stream)
+    for _ in range(reps):
+        ops.store_kvcache(bk, bv, w.k_cache, w.v_cache, bslots)
+    a1.record(stream)
+    torch.cuda.synchronize()
+    bulk_ms = a0.elapsed_time(a1) / reps
+    bulk_bytes = n_bulk * hkv * 128 * 2 * (2 + 2)
+
+    # ---- max over ranks
+    t = torch.tensor([total_ms, decode_ms, append_ms, e2e_ms, bulk_ms], device=device, dtype=torch.float64)
+    b = torch.tensor([float(kv_bytes)], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(b, op=dist.ReduceOp.SUM)
+    total_ms, decode_ms, append_ms, e2e_ms, bulk_ms = t.tolist()
+    job_bytes = b.item()
+
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        step_ms = total_ms / args.steps
+        value = job_bytes / (step_ms * 1e-3) / 1e9
+        achieved = kv_bytes / (decode_ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"qwen3-8b decode shape: batch {args.batch * world}, ctx U[512,8192], 32q/8kv heads "
+                                   f"sharded {world}-way by KV head, page 256, 1 appended token per sequence",
+                       "global_batch": args.batch * world, "kv_bytes_per_gpu": kv_bytes,
+                       "l2": "KV per step (1.1 GB per GPU) exceeds L2 (126 MB); no flush needed",
+                       "parallelism": f"kv-head-shard{world}"},
+            "e2e": {"value": job_bytes / (e2e_ms / args.steps * 1e-3) / 1e9, "unit": UNIT,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": 3 * args.steps,
+            "roofline": {"bound": "hbm", "kernel": "decode_tma_kernel + decode_reduce_kernel", "achieved": achieved,
+                         "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
+                         "frac_of_8000": achieved / 8000.0, "decode_ms": decode_ms, "traffic": None},
+            "append": {"decode_shape_us": append_ms * 1e3, "decode_shape_tok_s": args.batch * world / (append_ms * 1e-3),
+                       "bulk_rows": n_bulk, "bulk_tok_s": n_bulk / (bulk_ms * 1e-3),
+                       "bulk_gbs": bulk_bytes / (bulk_ms * 1e-3) / 1e9, "bulk_frac": bulk_bytes / (bulk_ms * 1e-3) / 1e9 / peak},
+            "clocks": clocks.summary(),
+        }
+        if not args.no_cpu_baseline and world == 1:
+            secs, cpu_bytes, threads = cpu_sample(w, 8, 2)
+            line["cpu_baseline"] = {
+                "value": cpu_bytes / secs / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
+                "sample": f"append + decode of the first 8 sequences ({cpu_bytes / 1e6:.0f} MB of KV), best of 2"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -180,9 +180,10 @@ size_t infer_kv_append_workspace_bytes(const infer_kv_pool_t* pool) {
 int infer_kv_append(const infer_kv_pool_t* pool, const void* k, const void* v, int64_t k_row_stride,
                     int64_t v_row_stride, const int32_t* slot_mapping, int64_t n_tokens, void* workspace,
                     size_t workspace_bytes, void* stream_) {
-    if (!pool || !k || !v || !slot_mapping) return INFER_ERR_NULL;
+    if (!pool) return INFER_ERR_NULL;
     if (n_tokens < 0) return INFER_ERR_GEOMETRY;
     if (n_tokens == 0) return INFER_OK;
+    if (!k || !v || !slot_mapping) return INFER_ERR_NULL;
     const int64_t row = int64_t(pool->n_kv_heads) * ib::kHeadDim;
     if (k_row_stride < row || v_row_stride < row) return INFER_ERR_STRIDE;
     if (!ib::aligned16(k) || !ib::aligned16(v) || k_row_stride % 8 || v_row_stride % 8) return INFER_ERR_ALIGN;

@@ -106,14 +106,19 @@ def store_kvcache(key, value, k_cache, v_cache, slot_mapping, k_scale=None, v_sc
         raise RuntimeError("store_kvcache: key/value must be bf16")
     if slot_mapping.dtype != torch.int32 or not slot_mapping.is_cuda:
         raise RuntimeError("store_kvcache: slot_mapping must be an int32 CUDA tensor")
+    if n == 0:
+        return
     pool = pool_of(k_cache, v_cache, k_scale, v_scale)
     lib = _lib.load()
+    # the pitch of a single row is meaningless (torch may report any stride for a size-1 dim)
+    k_pitch = key.stride(0) if n > 1 else d
+    v_pitch = value.stride(0) if n > 1 else d
     ws, ws_bytes = None, 0
     if pool.fp8:
         ws_bytes = lib.infer_kv_append_workspace_bytes(pool.handle)
         ws = _workspace(pool.device, ws_bytes)
     with torch.cuda.device(pool.device):
-        rc = lib.infer_kv_append(pool.handle, _ptr(key), _ptr(value), key.stride(0), value.stride(0),
+        rc = lib.infer_kv_append(pool.handle, _ptr(key), _ptr(value), k_pitch, v_pitch,
                                  _ptr(slot_mapping), n, _ptr(ws), ws_bytes, _stream())
     _lib.check(rc, "store_kvcache")
 
@@ -142,7 +147,7 @@ def paged_attn_decode(q, k_cache, v_cache, cache_seqlens, block_table, softmax_s
                                     block_table.stride(0), b, hq, float(softmax_scale), _ptr(ws), ws.numel(),
                                     _stream())
         _lib.check(rc, "paged_attn_decode")
-        if os.environ.get("INFER_B200_CHECK") == "1":
+        if os.environ.get("INFER_B200_CHECK") == "1" and not torch.cuda.is_current_stream_capturing():
             _lib.check(lib.infer_paged_decode_status(_ptr(ws), _stream()), "paged_attn_decode (device status)")
     return o.view(shape)
 

@@ -134,11 +134,11 @@ def _pool_size(lens, slack=1.1):
 
 
 def _decode_workload(name, seed, n_q_heads, n_kv_heads, lens, num_blocks, device,
-                     shared_prefix=0, n_shared=0, fp8=False, with_pool=True):
+                     shared_prefix=0, n_shared=0, fp8=False, with_pool=True, tensor_seed=None):
     rng = np.random.default_rng(seed)
     tables, refs = _allocate(lens, num_blocks, rng, shared_prefix, n_shared)
     slots = [t[(n - 1) // BLOCK_SIZE] * BLOCK_SIZE + (n - 1) % BLOCK_SIZE for t, n in zip(tables, lens)]
-    gen = torch.Generator(device=device).manual_seed(seed)
+    gen = torch.Generator(device=device).manual_seed(seed if tensor_seed is None else tensor_seed)
     b = len(lens)
     q = _randn((b, n_q_heads, HEAD_DIM), gen, device)
     k = _randn((b, n_kv_heads, HEAD_DIM), gen, device)
@@ -161,12 +161,14 @@ def config0(device="cpu", seed=1000):
 
 
 def config1(device="cpu", seed=1001, batch=64, lo=512, hi=8192, n_kv_heads=8, n_q_heads=32,
-            with_pool=True):
-    """Qwen3-8B decode shape: Hq32/Hkv8, 64 sequences, ctx U{512..8192}, pool = tokens + 10%."""
+            with_pool=True, tensor_seed=None):
+    """Qwen3-8B decode shape: Hq32/Hkv8, 64 sequences, ctx U{512..8192}, pool = tokens + 10%.
+    ``n_kv_heads``/``n_q_heads`` below 8/32 build one KV-head shard directly; ``tensor_seed``
+    then gives each shard its own values while the integer metadata stays replicated."""
     rng = np.random.default_rng(seed)
     lens = rng.integers(lo, hi + 1, size=batch)
     return _decode_workload("qwen3-8b-decode", seed, n_q_heads, n_kv_heads, lens, _pool_size(lens),
-                            device, with_pool=with_pool)
+                            device, with_pool=with_pool, tensor_seed=tensor_seed)
 
 
 def config2(device="cpu", seed=1002, n_seqs=16, max_prefix=4096, chunk=2048):

@@ -1,0 +1,63 @@
+"""FP8-e4m3 KV: append bit-exact (bytes and scales) against the oracle's rule, decode within
+the FP8 tolerance."""
+import pytest
+import torch
+
+from gpu_util import ATOL_FP8, RTOL_FP8, assert_close, bits_equal
+from infer_b200 import ops, workloads
+from infer_b200.metadata import chunk_slots
+from oracle import paged_kv_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _empty_pools(num_blocks, hkv, device):
+    mk = lambda: torch.zeros(num_blocks, 256, hkv, 128, dtype=torch.uint8, device=device)
+    ms = lambda: torch.zeros(num_blocks, hkv, dtype=torch.float32, device=device)
+    return mk(), mk(), ms(), ms()
+
+
+def _fill_both(w, rounds):
+    """Builds the FP8 pools by appending every sequence's existing tokens in several calls
+    (so pages see their scale grow between calls), on the GPU and on the oracle."""
+    cpu = _empty_pools(w.num_blocks, w.n_kv_heads, "cpu")
+    gpu = _empty_pools(w.num_blocks, w.n_kv_heads, "cuda")
+    bounds = [0.0, 0.3, 0.35, 1.0][:rounds + 1] if rounds == 3 else [0.0, 1.0]
+    for lo_f, hi_f in zip(bounds[:-1], bounds[1:]):
+        slots = []
+        for t, n in zip(w.block_tables, w.context_lens):
+            slots.extend(chunk_slots(t, int(lo_f * (n - 1)), int(hi_f * (n - 1)), 256))
+        if not slots:
+            continue
+        idx = torch.tensor(slots, dtype=torch.int64)
+        k = w.k_cache.view(-1, w.n_kv_heads, 128)[idx]
+        v = w.v_cache.view(-1, w.n_kv_heads, 128)[idx]
+        s32 = idx.to(torch.int32)
+        oracle.store_kvcache_fp8(k, v, *cpu, s32)
+        ops.store_kvcache(k.cuda(), v.cuda(), gpu[0], gpu[1], s32.cuda(), gpu[2], gpu[3])
+    return cpu, gpu
+
+
+@pytest.mark.parametrize("rounds", [1, 3])
+def test_fp8_append_bit_exact(rounds):
+    w = workloads.config3()
+    cpu, gpu = _fill_both(w, rounds)
+    torch.cuda.synchronize()
+    assert torch.equal(cpu[2], gpu[2].cpu()), "k scales differ"
+    assert torch.equal(cpu[3], gpu[3].cpu()), "v scales differ"
+    assert bits_equal(cpu[0], gpu[0]), "k bytes differ"
+    assert bits_equal(cpu[1], gpu[1]), "v bytes differ"
+
+
+def test_fp8_decode_step():
+    w = workloads.config3()
+    cpu, gpu = _fill_both(w, 3)
+    # the decode step's own append, then attention
+    oracle.store_kvcache_fp8(w.k, w.v, *cpu, w.slot_mapping)
+    ops.store_kvcache(w.k.cuda(), w.v.cuda(), gpu[0], gpu[1], w.slot_mapping.cuda(), gpu[2], gpu[3])
+    cl, bt = w.context_lens_tensor(), w.block_tables_tensor()
+    got = ops.paged_attn_decode(w.q.cuda(), gpu[0], gpu[1], cl.cuda(), bt.cuda(), w.scale, k_scale=gpu[2], v_scale=gpu[3])
+    torch.cuda.synchronize()
+    assert bits_equal(cpu[0], gpu[0]) and torch.equal(cpu[2], gpu[2].cpu())
+    want = oracle.paged_decode(w.q, cpu[0], cpu[1], cl, bt, w.scale, cpu[2], cpu[3])
+    assert_close(got, want, ATOL_FP8, RTOL_FP8, "fp8 decode vs fp8 oracle")
