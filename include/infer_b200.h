@@ -45,7 +45,9 @@ enum {
     INFER_ERR_WORKSPACE = -5,  /* scratch buffer missing, misaligned or too small */
     INFER_ERR_CUDA = -6,       /* a CUDA call failed; see infer_last_cuda_error() */
     INFER_ERR_DTYPE = -7,      /* pool dtype not valid for this entry point */
-    INFER_ERR_DEVICE = -8      /* the kernel reported a bounded wait that ran out */
+    INFER_ERR_DEVICE = -8,     /* the kernel reported a bounded wait that ran out */
+    INFER_ERR_TOO_LARGE = -9   /* the problem needs more than the built-in scratch of
+                                  infer_paged_decode_noalloc */
 };
 
 enum { INFER_KV_BF16 = 0, INFER_KV_E4M3 = 1 };
@@ -100,6 +102,34 @@ INFER_API int infer_paged_prefill(const infer_kv_pool_t* pool, void* out, const 
  * inside, GQA by kv_head = head / (Hq/Hkv). */
 INFER_API int infer_flash_attn_prefill(const void* q, const void* k, const void* v, void* o,
                              int batch, int n_q_heads, int n_kv_heads, int seq_len, void* stream);
+
+/* Paged decode attention for callers that cannot provide scratch memory.  It has no
+ * counterpart in the reference.  Same arguments and results as infer_paged_decode, minus the
+ * workspace: the partial results of contexts that are split over several thread blocks go to
+ * a 2 MiB array that is part of the library image on the device (every GPU that loads the
+ * library holds those 2 MiB until the process exits).
+ *
+ * It is meant for two kinds of caller: an engine that has already handed every free byte of
+ * device memory to the KV pools - the reference sizes its pool from whatever is left after
+ * warm-up (infer/engine/model_runner.py:47-58), so a later cudaMalloc for scratch may fail -
+ * and a host runtime that binds this C ABI through a thin shim (cgo, JNI, ctypes) and only
+ * ever holds device pointers it was lent, with no device allocator of its own.
+ *
+ * The function calls no cudaMalloc/cudaFree and no allocating library routine.  The first
+ * call on a device looks up the device address of the built-in array (the device must be
+ * current, and must be the one the pool was created on); make that first call before any
+ * stream capture.  Every call on a device shares the one array, which keeps the previous
+ * call's contents; the function clears the status word that must start at zero, everything
+ * else is rewritten before it is read.  Two calls that overlap on the GPU (different
+ * streams, or concurrent graphs) race on the array: serialise them.
+ *
+ * Limits: the scratch layout for the pool's geometry and this GPU must fit 2 MiB (bf16 pools,
+ * up to 8 query heads per KV head, GPUs of up to about 240 SMs) and batch <= 2048; anything
+ * larger returns INFER_ERR_TOO_LARGE without launching. */
+INFER_API int infer_paged_decode_noalloc(const infer_kv_pool_t* pool, void* out, const void* q,
+                               const int32_t* context_lens, const int32_t* block_tables,
+                               int64_t bt_stride, int batch, int n_q_heads, float softmax_scale,
+                               void* stream);
 
 /* Reads the device status word the last decode call on this workspace left behind
  * (synchronises the stream).  0 = no bounded wait ran out. */

@@ -13,6 +13,7 @@ LIB_PATH = _HERE / "libinfer_b200.so"
 
 OK = 0
 ERR_NULL, ERR_ALIGN, ERR_STRIDE, ERR_GEOMETRY, ERR_WORKSPACE, ERR_CUDA, ERR_DTYPE, ERR_DEVICE = range(-1, -9, -1)
+ERR_TOO_LARGE = -9
 KV_BF16, KV_E4M3 = 0, 1
 
 _vp, _i32, _i64, _sz, _f32 = C.c_void_p, C.c_int, C.c_int64, C.c_size_t, C.c_float
@@ -25,6 +26,7 @@ SIGNATURES = {
     "infer_kv_append_workspace_bytes": (_sz, [_vp]),
     "infer_paged_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _f32, _vp, _sz, _vp]),
     "infer_paged_decode_workspace_bytes": (_sz, [_vp, _i32, _i32]),
+    "infer_paged_decode_noalloc": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _f32, _vp]),
     "infer_paged_prefill": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _f32, _vp]),
     "infer_flash_attn_prefill": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
     "infer_paged_decode_status": (_i32, [_vp, _vp]),

@@ -12,6 +12,7 @@
 // The work split (equal KV bytes per CTA, two scratch slots per CTA) is described in
 // decode_common.cuh.
 #include <cstdlib>
+#include <mutex>
 
 #include "decode_common.cuh"
 
@@ -566,6 +567,54 @@ int infer_paged_decode_status(const void* workspace, void* stream_) {
     IB_CUDA(cudaMemcpyAsync(&word, workspace, sizeof(int), cudaMemcpyDeviceToHost, st));
     IB_CUDA(cudaStreamSynchronize(st));
     return (word & 0xFFFF0000) == ib::kStatusMagic ? INFER_ERR_DEVICE : INFER_OK;
+}
+
+// ------------------------------------------------------------------ entry point without scratch
+namespace ib {
+
+// Scratch of infer_paged_decode_noalloc: lives in the library's device image, one copy per
+// GPU that loads the library.  In host code the NAME below is only a handle for
+// cudaGetSymbolAddress; kernels must be given the address that call returns.
+constexpr size_t kBuiltinScratchBytes = size_t(2) << 20;
+static __device__ __align__(256) unsigned char g_builtin_scratch[kBuiltinScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static void* g_builtin_scratch_addr[kMaxDevices];   // device address per device ordinal, 0 = not looked up yet
+static std::mutex g_builtin_scratch_mutex;
+
+}  // namespace ib
+
+int infer_paged_decode_noalloc(const infer_kv_pool_t* pool, void* out, const void* q, const int32_t* context_lens,
+                               const int32_t* block_tables, int64_t bt_stride, int batch, int n_q_heads,
+                               float softmax_scale, void* stream_) {
+    using namespace ib;
+    if (!pool || !out || !q || !context_lens || !block_tables) return INFER_ERR_NULL;
+    if (n_q_heads <= 0 || n_q_heads % pool->n_kv_heads != 0 || batch < 0) return INFER_ERR_GEOMETRY;
+    if (batch > kMaxBatch) return INFER_ERR_TOO_LARGE;
+    const DecodeConfig cfg = decode_config(pool, n_q_heads);
+    if (decode_layout(cfg.grid, cfg.rows).total > kBuiltinScratchBytes) return INFER_ERR_TOO_LARGE;
+
+    int dev = -1;
+    IB_CUDA(cudaGetDevice(&dev));
+    if (dev != pool->device || dev < 0 || dev >= kMaxDevices) {
+        set_cuda_error(cudaErrorInvalidDevice);
+        return INFER_ERR_CUDA;
+    }
+    void* scratch = nullptr;
+    {
+        // once per device, with that device current: resolve the array's device address
+        std::lock_guard<std::mutex> lock(g_builtin_scratch_mutex);
+        if (!g_builtin_scratch_addr[dev]) {
+            void* addr = nullptr;
+            IB_CUDA(cudaGetSymbolAddress(&addr, g_builtin_scratch));
+            g_builtin_scratch_addr[dev] = addr;
+        }
+        scratch = g_builtin_scratch_addr[dev];
+    }
+    // the array keeps the previous call's bytes: the status word has to start at zero
+    IB_CUDA(cudaMemsetAsync(scratch, 0, 64, static_cast<cudaStream_t>(stream_)));
+    return infer_paged_decode(pool, out, q, context_lens, block_tables, bt_stride, batch, n_q_heads, softmax_scale,
+                              scratch, kBuiltinScratchBytes, stream_);
 }
 
 }  // extern "C"

@@ -132,6 +132,8 @@ const char* infer_strerror(int code) {
         case INFER_ERR_CUDA: return "CUDA error (see infer_last_cuda_error)";
         case INFER_ERR_DTYPE: return "pool dtype not supported by this entry point";
         case INFER_ERR_DEVICE: return "a bounded device-side wait ran out";
+        case INFER_ERR_TOO_LARGE: return "problem exceeds the 2 MiB built-in scratch of infer_paged_decode_noalloc "
+                                         "(bf16 pools, batch <= 2048); use infer_paged_decode with a workspace";
         default: return "unknown error code";
     }
 }
