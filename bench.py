@@ -164,6 +164,69 @@ def run_reference(args, rank, world):
     }))
 
 
+# ------------------------------------------------------------------------------- prefill leg
+def run_prefill(args):
+    """Chunked prefill over cached prefixes: append the chunk, then causal attention over
+    prefix + chunk.  FLOPs = 4 * 128 * Hq * sum(chunk * prefix + chunk * (chunk + 1) / 2)."""
+    from infer_b200 import ops, workloads
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    n_seqs = 16 if args.batch == BASE_BATCH else args.batch
+    w = workloads.config2(device=device, n_seqs=n_seqs)
+    cu_q, cu_k = (t.to(device) for t in w.cu_seqlens())
+    bt = w.block_tables_tensor().to(device)
+    slots = w.slot_mapping.to(device)
+    out = torch.empty_like(w.q)
+    mq, mk = max(w.new_lens), max(w.context_lens)
+    flops = 4 * 128 * w.n_q_heads * sum(c * (n - c) + c * (c + 1) // 2 for c, n in zip(w.new_lens, w.context_lens))
+    stream = torch.cuda.current_stream()
+
+    def step():
+        ops.store_kvcache(w.k, w.v, w.k_cache, w.v_cache, slots)
+        ops.paged_attn_prefill(w.q, w.k_cache, w.v_cache, cu_q, cu_k, mq, mk, w.scale, bt, out=out)
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    with ClockSampler(0) as clocks:
+        for i in range(args.steps):
+            ev[i][0].record(stream)
+            ops.store_kvcache(w.k, w.v, w.k_cache, w.v_cache, slots)
+            ev[i][1].record(stream)
+            ops.paged_attn_prefill(w.q, w.k_cache, w.v_cache, cu_q, cu_k, mq, mk, w.scale, bt, out=out)
+            ev[i][2].record(stream)
+        torch.cuda.synchronize()
+        t_end = time.time() + 0.5
+        while time.time() < t_end:
+            step()
+        torch.cuda.synchronize()
+    attn_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+    append_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+    step_ms = statistics.mean(e[0].elapsed_time(e[2]) for e in ev)
+    try:
+        with open(ROOT / "MEASURED_PEAKS.json") as f:
+            peak, kind = float(json.load(f)["bf16_tflops_sustained"]), "of measured (sustained)"
+    except Exception:
+        peak, kind = 1400.0, "of fallback"
+    achieved = flops / (attn_ms * 1e-3) / 1e12
+    n_tok = sum(w.new_lens)
+    print(json.dumps({
+        "metric": "paged chunked-prefill attention TFLOP/s", "value": flops / (step_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"paged chunked prefill: {n_seqs} sequences, prefix U[0,4096], chunk 2048, 16q/8kv heads, "
+                               "page 256; append of the chunk + causal attention over prefix + chunk",
+                   "flops_per_step": flops, "l2": "q + KV read per step exceed L2"},
+        "gpu_launches": 2 * args.steps,
+        "roofline": {"bound": "tensor", "kernel": "prefill attention kernel", "achieved": achieved, "peak": peak,
+                     "unit": "TFLOP/s", "frac": achieved / peak, "peak_kind": kind, "attn_ms": attn_ms, "traffic": None},
+        "append": {"rows": n_tok, "ms": append_ms, "tok_s": n_tok / (append_ms * 1e-3),
+                   "gbs": n_tok * w.n_kv_heads * 128 * 2 * 4 / (append_ms * 1e-3) / 1e9},
+        "clocks": clocks.summary(),
+    }))
+
+
 # ------------------------------------------------------------------------------- GPU leg
 def main():
     ap = argparse.ArgumentParser()
@@ -172,6 +235,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
+                    help="decode = the headline append + paged decode step; prefill = the paged chunked-prefill "
+                         "configuration (16 sequences, prefix U[0,4096], chunk 2048), single GPU")
     ap.add_argument("--batch", type=int, default=BASE_BATCH,
                     help="sequences per GPU share (default 64 = the benchmark configuration; smaller values "
                          "give the small case used for profiler captures)")
@@ -186,6 +252,11 @@ def main():
         return
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    if args.workload == "prefill":
+        if world != 1:
+            raise SystemExit("--workload prefill runs on one GPU")
+        run_prefill(args)
+        return
     if 8 % world:
         raise SystemExit("KV-head sharding needs a GPU count that divides 8")
 

@@ -89,8 +89,8 @@ INFER_API size_t infer_paged_decode_workspace_bytes(const infer_kv_pool_t* pool,
  * softmax_scale, causal=True, block_table), infer/ops/attention.py:110-116).  Keys of
  * sequence b are its first cu_seqlens_k[b+1]-cu_seqlens_k[b] cached tokens (append the
  * chunk first); the causal mask is aligned to the bottom-right corner.
- * q, out: bf16 [total_q, n_q_heads, 128] contiguous. */
-INFER_API int infer_paged_prefill(const infer_kv_pool_t* pool, void* out, const void* q,
+ * q, out: bf16 [total_q, n_q_heads, 128] contiguous; total_q = cu_seqlens_q[batch]. */
+INFER_API int infer_paged_prefill(const infer_kv_pool_t* pool, void* out, const void* q, int64_t total_q,
                         const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
                         const int32_t* block_tables, int64_t bt_stride, int batch,
                         int max_seqlen_q, int max_seqlen_k, int n_q_heads,

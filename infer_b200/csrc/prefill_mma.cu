@@ -2,28 +2,9 @@
 // [B,H,S,128] op) on the mma.sync tensor path: 64 query rows per CTA (16 per warp), K/V
 // tiles of 64 tokens staged by a producer warp with TMA into a 3-stage ring, online softmax
 // in registers.  The same kernel serves both layouts; only the TMA coordinates differ.
-#include "common.cuh"
+#include "prefill.cuh"
 
 namespace ib {
-
-struct PrefillParams {
-    const __nv_bfloat16* q;
-    __nv_bfloat16* out;
-    int64_t q_row_stride;     // elements between consecutive query rows
-    int64_t q_head_stride;    // elements between query heads
-    int64_t q_batch_stride;   // dense only: elements between batches
-    const int32_t* cu_q;      // paged only
-    const int32_t* cu_k;      // paged only
-    const int32_t* block_tables;
-    int64_t bt_stride;
-    int n_q_heads;
-    int n_kv_heads;
-    int group;
-    int block_size;
-    int seq_len;              // dense only
-    float scale_log2;
-    int* status;              // may be null
-};
 
 constexpr int kPfStages = 3;
 constexpr int kPfTile = 64;                      // keys per tile
@@ -247,7 +228,7 @@ __global__ void __launch_bounds__(kPfThreads) prefill_mma_kernel(PrefillParams p
     }
 }
 
-static int launch_prefill(bool paged, const PrefillParams& p, const CUtensorMap& mk, const CUtensorMap& mv,
+int launch_prefill_mma(bool paged, const PrefillParams& p, const CUtensorMap& mk, const CUtensorMap& mv,
                           int max_q, int batch, cudaStream_t st) {
     if (max_q <= 0 || batch <= 0) return INFER_OK;
     dim3 grid((max_q + 63) / 64, p.n_q_heads, batch);
@@ -262,71 +243,3 @@ static int launch_prefill(bool paged, const PrefillParams& p, const CUtensorMap&
 }
 
 }  // namespace ib
-
-extern "C" {
-
-int infer_paged_prefill(const infer_kv_pool_t* pool, void* out, const void* q, const int32_t* cu_seqlens_q,
-                        const int32_t* cu_seqlens_k, const int32_t* block_tables, int64_t bt_stride, int batch,
-                        int max_seqlen_q, int max_seqlen_k, int n_q_heads, float softmax_scale, void* stream_) {
-    using namespace ib;
-    if (!pool || !out || !q || !cu_seqlens_q || !cu_seqlens_k || !block_tables) return INFER_ERR_NULL;
-    if (pool->dtype != INFER_KV_BF16) return INFER_ERR_DTYPE;
-    if (batch < 0 || n_q_heads <= 0 || n_q_heads % pool->n_kv_heads != 0 || bt_stride <= 0 || max_seqlen_q < 0 ||
-        max_seqlen_k < max_seqlen_q || batch > 65535 || n_q_heads > 65535)
-        return INFER_ERR_GEOMETRY;
-    if (!aligned16(out) || !aligned16(q)) return INFER_ERR_ALIGN;
-    PrefillParams p{};
-    p.q = static_cast<const __nv_bfloat16*>(q);
-    p.out = static_cast<__nv_bfloat16*>(out);
-    p.q_row_stride = int64_t(n_q_heads) * kHeadDim;
-    p.q_head_stride = kHeadDim;
-    p.q_batch_stride = 0;
-    p.cu_q = cu_seqlens_q;
-    p.cu_k = cu_seqlens_k;
-    p.block_tables = block_tables;
-    p.bt_stride = bt_stride;
-    p.n_q_heads = n_q_heads;
-    p.n_kv_heads = pool->n_kv_heads;
-    p.group = n_q_heads / pool->n_kv_heads;
-    p.block_size = pool->block_size;
-    p.seq_len = 0;
-    p.scale_log2 = softmax_scale * 1.4426950408889634f;
-    p.status = nullptr;
-    return launch_prefill(true, p, pool->maps[2].k, pool->maps[2].v, max_seqlen_q, batch,
-                          static_cast<cudaStream_t>(stream_));
-}
-
-int infer_flash_attn_prefill(const void* q, const void* k, const void* v, void* o, int batch, int n_q_heads,
-                             int n_kv_heads, int seq_len, void* stream_) {
-    using namespace ib;
-    if (!q || !k || !v || !o) return INFER_ERR_NULL;
-    if (batch <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads != 0 || seq_len <= 0 ||
-        batch > 65535 || n_q_heads > 65535)
-        return INFER_ERR_GEOMETRY;
-    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return INFER_ERR_ALIGN;
-    CUtensorMap mk, mv;
-    // K, V [B, Hkv, S, 128]: dims {128, S, B*Hkv}; a box never crosses into the next head,
-    // rows past S are filled with zeros.
-    int rc = encode_map_3d(&mk, k, 2, kHeadDim, uint64_t(seq_len), uint64_t(batch) * n_kv_heads, 256,
-                           uint64_t(seq_len) * 256, 64, kPfTile, 1);
-    if (rc == INFER_OK)
-        rc = encode_map_3d(&mv, v, 2, kHeadDim, uint64_t(seq_len), uint64_t(batch) * n_kv_heads, 256,
-                           uint64_t(seq_len) * 256, 64, kPfTile, 1);
-    if (rc != INFER_OK) return rc;
-    PrefillParams p{};
-    p.q = static_cast<const __nv_bfloat16*>(q);
-    p.out = static_cast<__nv_bfloat16*>(o);
-    p.q_row_stride = kHeadDim;
-    p.q_head_stride = int64_t(seq_len) * kHeadDim;
-    p.q_batch_stride = int64_t(n_q_heads) * seq_len * kHeadDim;
-    p.n_q_heads = n_q_heads;
-    p.n_kv_heads = n_kv_heads;
-    p.group = n_q_heads / n_kv_heads;
-    p.block_size = 1;
-    p.seq_len = seq_len;
-    p.scale_log2 = 1.4426950408889634f / sqrtf(float(kHeadDim));
-    p.status = nullptr;
-    return launch_prefill(false, p, mk, mv, seq_len, batch, static_cast<cudaStream_t>(stream_));
-}
-
-}  // extern "C"

@@ -1,0 +1,417 @@
+// Causal attention over many query rows on the 5th-generation tensor cores (tcgen05).
+//
+// One CTA = 128 query rows of one (sequence, query head).  Per 128-key tile:
+//   S = Q K^T        tcgen05.mma, A = Q and B = K from shared memory (K-major, 128-byte
+//                    swizzle, written by TMA), accumulator in tensor memory (128 columns)
+//   softmax          four warps, one thread per query row = one TMEM lane: tcgen05.ld of the
+//                    row, running max / sum in registers, P written to shared memory as bf16
+//   O_j = P V        tcgen05.mma, A = P (K-major), B = V (MN-major: dims contiguous),
+//                    accumulator in tensor memory; the softmax threads fold O_j into their
+//                    register accumulator with the online-softmax correction
+// S and O are double-buffered in TMEM (4 x 128 = all 512 columns), so S_{j+1} is computed
+// while the softmax of tile j runs.  Warp roles: 0-3 softmax, 4 TMA producer, 5 MMA issue
+// and TMEM allocation.  Every barrier wait is bounded; a wait that runs out raises a CTA-wide
+// abort flag, every role drains to the common epilogue, TMEM is freed and a status is set.
+#include "prefill.cuh"
+
+namespace ib {
+
+constexpr int kTcRows = 128;                 // query rows per CTA
+constexpr int kTcKeys = 128;                 // keys per tile
+constexpr int kTcHalf = 128 * 128;           // bytes of one [128 rows][64 elems] swizzled sub-tile
+constexpr int kTcTile = 2 * kTcHalf;         // 32 KiB: Q, K, V or P tile
+constexpr int kTcThreads = 192;
+
+struct TcSmem {
+    static constexpr int q = 0;
+    static constexpr int k = q + kTcTile;            // 2 stages
+    static constexpr int v = k + 2 * kTcTile;        // 2 stages
+    static constexpr int p = v + 2 * kTcTile;
+    static constexpr int bars = p + kTcTile;         // 8-byte mbarriers
+    static constexpr int n_bars = 20;
+    static constexpr int misc = bars + n_bars * 8;   // tmem base, abort flag
+    static constexpr int total = misc + 16;
+};
+
+enum TcBar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, S_EMPTY = 11, P_FULL = 13,
+             O_FULL = 14, O_EMPTY = 16, DRAIN = 18 };
+
+// ---- tcgen05 wrappers
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+        "%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle, 8-row groups 1024 bytes apart.
+//   K-major operands ([rows][64 elems] sub-tiles): lbo unused.
+//   MN-major operand (V as [keys][64 dims]): lbo = distance between the two 64-dim halves.
+__device__ __forceinline__ uint64_t tc_desc(uint32_t smem_addr, uint32_t lbo_bytes) {
+    uint64_t d = 0;
+    d |= uint64_t((smem_addr >> 4) & 0x3FFF);
+    d |= uint64_t((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= uint64_t((1024 >> 4) & 0x3FFF) << 32;
+    d |= uint64_t(1) << 46;        // descriptor version for sm_100
+    d |= uint64_t(2) << 61;        // SWIZZLE_128B
+    return d;
+}
+// kind::f16 instruction descriptor: D f32, A and B bf16, M = N = 128.
+constexpr uint32_t tc_idesc(bool b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+}
+
+// Bounded wait that also gives up as soon as another thread raised the abort flag.
+__device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < (1u << 22); ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 63) == 63) {
+            if (*abort_flag) return false;
+            __nanosleep(i > 4096 ? 256 : 32);
+        }
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+template <bool PAGED>
+__global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams p,
+                                                                   const __grid_constant__ CUtensorMap map_q,
+                                                                   const __grid_constant__ CUtensorMap map_k,
+                                                                   const __grid_constant__ CUtensorMap map_v) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t base = smem_u32(smem);
+    const uint32_t bar0 = base + TcSmem::bars;
+    volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(smem + TcSmem::misc);
+    volatile int* s_abort = reinterpret_cast<volatile int*>(smem + TcSmem::misc + 4);
+    auto bar = [&](int which, int idx = 0) { return bar0 + uint32_t(which + idx) * 8; };
+
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int qt = int(gridDim.x) - 1 - int(blockIdx.x);    // longest rows first
+    int lq, lk, q0 = 0;
+    int64_t q_base;
+    if (PAGED) {
+        q0 = p.cu_q[b];
+        lq = p.cu_q[b + 1] - q0;
+        lk = p.cu_k[b + 1] - p.cu_k[b];
+        q_base = int64_t(q0) * p.q_row_stride + int64_t(h) * p.q_head_stride;
+    } else {
+        lq = lk = p.seq_len;
+        q_base = int64_t(b) * p.q_batch_stride + int64_t(h) * p.q_head_stride;
+    }
+    if (qt * kTcRows >= lq) return;                          // whole CTA leaves before any barrier or TMEM use
+    const int shift = lk - lq;
+    const int last_row = min(lq, qt * kTcRows + kTcRows) - 1;
+    const int n_kt = (shift + last_row) / kTcKeys + 1;
+    const int kvh = h / p.group;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar(Q_FULL), 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar(K_FULL, i), 1);
+            mbar_init(bar(K_EMPTY, i), 1);
+            mbar_init(bar(V_FULL, i), 1);
+            mbar_init(bar(V_EMPTY, i), 1);
+            mbar_init(bar(S_FULL, i), 1);
+            mbar_init(bar(S_EMPTY, i), 128);
+            mbar_init(bar(O_FULL, i), 1);
+            mbar_init(bar(O_EMPTY, i), 128);
+        }
+        mbar_init(bar(P_FULL), 128);
+        mbar_init(bar(DRAIN), 1);
+        *s_abort = 0;
+        fence_mbar_init();
+        fence_proxy_async();
+    }
+    if (warp == 5) {
+        // all 512 columns: S0, S1, O0, O1 (one CTA per SM by shared-memory use)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(base + uint32_t(TcSmem::misc)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *s_tmem;
+    bool ok = true;
+
+    if (warp == 4) {
+        // ================================================================= TMA producer
+        if (lane == 0) {
+            tma_prefetch_desc(&map_q);
+            tma_prefetch_desc(&map_k);
+            tma_prefetch_desc(&map_v);
+            mbar_expect_tx(bar(Q_FULL), kTcTile);
+            for (int half = 0; half < 2; ++half) {
+                if (PAGED) tma_load_3d(base + TcSmem::q + half * kTcHalf, &map_q, bar(Q_FULL), half * 64, h, q0 + qt * kTcRows);
+                else tma_load_3d(base + TcSmem::q + half * kTcHalf, &map_q, bar(Q_FULL), half * 64, qt * kTcRows, b * p.n_q_heads + h);
+            }
+            auto load_tile = [&](const CUtensorMap* map, uint32_t dst, uint32_t full, int j) {
+                int c1, c2;
+                if (PAGED) {
+                    const int tok0 = j * kTcKeys;
+                    const int page = p.block_tables[int64_t(b) * p.bt_stride + tok0 / p.block_size];
+                    c1 = kvh;
+                    c2 = page * p.block_size + tok0 % p.block_size;
+                } else {
+                    c1 = j * kTcKeys;
+                    c2 = b * p.n_kv_heads + kvh;
+                }
+                mbar_expect_tx(full, kTcTile);
+                tma_load_3d(dst, map, full, 0, c1, c2);
+                tma_load_3d(dst + kTcHalf, map, full, 64, c1, c2);
+            };
+            int k_issued = 0, v_issued = 0;
+            // order K0, K1, V0, K2, V1, ...: K of the next tile is needed before V of this one
+            for (int j = 0; j <= n_kt && ok; ++j) {
+                if (j < n_kt) {
+                    if (tc_wait(bar(K_EMPTY, j & 1), ((j >> 1) & 1) ^ 1, s_abort)) {
+                        load_tile(&map_k, base + TcSmem::k + (j & 1) * kTcTile, bar(K_FULL, j & 1), j);
+                        ++k_issued;
+                    } else ok = false;
+                }
+                if (j >= 1 && ok) {
+                    const int jv = j - 1;
+                    if (tc_wait(bar(V_EMPTY, jv & 1), ((jv >> 1) & 1) ^ 1, s_abort)) {
+                        load_tile(&map_v, base + TcSmem::v + (jv & 1) * kTcTile, bar(V_FULL, jv & 1), jv);
+                        ++v_issued;
+                    } else ok = false;
+                }
+            }
+            // never leave with a copy in flight: wait (bounded) for everything that was armed
+            mbar_wait(bar(Q_FULL), 0);
+            for (int j = max(0, k_issued - 2); j < k_issued; ++j) mbar_wait(bar(K_FULL, j & 1), (j >> 1) & 1);
+            for (int j = max(0, v_issued - 2); j < v_issued; ++j) mbar_wait(bar(V_FULL, j & 1), (j >> 1) & 1);
+        }
+    } else if (warp == 5) {
+        // ================================================================= MMA issue
+        constexpr uint32_t idesc_s = tc_idesc(false), idesc_pv = tc_idesc(true);
+        const uint32_t q_addr = base + TcSmem::q, p_addr = base + TcSmem::p;
+        auto issue_s = [&](int j) {      // S[j&1] = Q K_j^T
+            if (!tc_wait(bar(K_FULL, j & 1), (j >> 1) & 1, s_abort)) return false;
+            if (!tc_wait(bar(S_EMPTY, j & 1), ((j >> 1) & 1) ^ 1, s_abort)) return false;
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t k_addr = base + TcSmem::k + (j & 1) * kTcTile;
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    const uint32_t off = (kk >> 2) * kTcHalf + (kk & 3) * 32;
+                    tc_mma(tmem + (j & 1) * 128, tc_desc(q_addr + off, 16), tc_desc(k_addr + off, 16), idesc_s, kk > 0);
+                }
+                tc_commit(bar(S_FULL, j & 1));
+                tc_commit(bar(K_EMPTY, j & 1));
+            }
+            __syncwarp();
+            return true;
+        };
+        if (!tc_wait(bar(Q_FULL), 0, s_abort)) ok = false;
+        if (ok) ok = issue_s(0);
+        for (int j = 0; j < n_kt && ok; ++j) {
+            if (j + 1 < n_kt) ok = issue_s(j + 1);
+            if (ok && !tc_wait(bar(V_FULL, j & 1), (j >> 1) & 1, s_abort)) ok = false;
+            if (ok && PAGED && j == n_kt - 1) {
+                // keys past the end of the context: P is 0 there, but 0 * (stale bytes) must not
+                // produce NaN, so clear those V rows before the tensor core reads them
+                const int valid = lk - j * kTcKeys;
+                if (valid < kTcKeys) {
+                    uint8_t* vt = smem + TcSmem::v + (j & 1) * kTcTile;
+                    for (int i = valid * 8 + lane; i < kTcKeys * 8; i += 32) {
+                        *reinterpret_cast<uint4*>(vt + i * 16) = make_uint4(0, 0, 0, 0);
+                        *reinterpret_cast<uint4*>(vt + kTcHalf + i * 16) = make_uint4(0, 0, 0, 0);
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                }
+            }
+            if (ok && !tc_wait(bar(P_FULL), j & 1, s_abort)) ok = false;
+            if (ok && !tc_wait(bar(O_EMPTY, j & 1), ((j >> 1) & 1) ^ 1, s_abort)) ok = false;
+            if (!ok) break;
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t v_addr = base + TcSmem::v + (j & 1) * kTcTile;
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t a_off = (ks >> 2) * kTcHalf + (ks & 3) * 32;   // 16 keys along P's K-major rows
+                    const uint32_t b_off = ks * 16 * 128;                         // 16 key rows of V
+                    tc_mma(tmem + 256 + (j & 1) * 128, tc_desc(p_addr + a_off, 16), tc_desc(v_addr + b_off, kTcHalf),
+                           idesc_pv, ks > 0);
+                }
+                tc_commit(bar(O_FULL, j & 1));
+                tc_commit(bar(V_EMPTY, j & 1));
+            }
+            __syncwarp();
+        }
+        // all tensor-core work issued by this warp must have retired before TMEM is freed
+        if (lane == 0) tc_commit(bar(DRAIN));
+        __syncwarp();
+        mbar_wait(bar(DRAIN), 0);
+    } else {
+        // ================================================================= softmax, one row per thread
+        const int r = threadIdx.x;                                 // row in the tile == TMEM lane
+        const uint32_t lane_sel = uint32_t(warp * 32) << 16;
+        const int row = qt * kTcRows + r;
+        const int pos = shift + row;
+        const int cta_first_pos = shift + qt * kTcRows;
+        float o_acc[128];
+#pragma unroll
+        for (int i = 0; i < 128; ++i) o_acc[i] = 0.f;
+        float m_run = -INFINITY, l_run = 0.f;
+        uint8_t* p_row = smem + TcSmem::p + r * 128;
+        const int rx = r & 7;
+
+        for (int j = 0; j < n_kt; ++j) {
+            if (ok && !tc_wait(bar(S_FULL, j & 1), (j >> 1) & 1, s_abort)) ok = false;
+            float alpha = 0.f;
+            if (ok) {
+                tc_fence_after();
+                const uint32_t s_addr = tmem + lane_sel + (j & 1) * 128;
+                const int key0 = j * kTcKeys;
+                const int limit = pos - key0;                        // columns <= limit are visible
+                const bool masked = key0 + kTcKeys - 1 > cta_first_pos;
+                // pass 1: row maximum
+                float mx = -INFINITY;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t v[32];
+                    tc_ld32(s_addr + c * 32, v);
+                    tc_wait_ld();
+                    if (masked) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, c * 32 + i <= limit ? __uint_as_float(v[i]) : -INFINITY);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+                    }
+                }
+                const float m_new = fmaxf(m_run, mx * p.scale_log2);
+                const float m_use = m_new == -INFINITY ? 0.f : m_new;
+                alpha = fast_exp2(m_run - m_use);
+                // P smem and O_{j-1} are free / ready once PV_{j-1} has retired
+                if (j > 0 && !tc_wait(bar(O_FULL, (j - 1) & 1), ((j - 1) >> 1) & 1, s_abort)) ok = false;
+                if (ok) {
+                    // pass 2: P = exp2(S * c - m), row sum, bf16 into the swizzled P tile
+                    float rs = 0.f;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t v[32];
+                        tc_ld32(s_addr + c * 32, v);
+                        tc_wait_ld();
+                        uint32_t packed[16];
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            float e0 = fast_exp2(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_use));
+                            float e1 = fast_exp2(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_use));
+                            if (masked) {
+                                if (c * 32 + i > limit) e0 = 0.f;
+                                if (c * 32 + i + 1 > limit) e1 = 0.f;
+                            }
+                            rs += e0 + e1;
+                            packed[i >> 1] = pack_bf16(e0, e1);
+                        }
+                        // 32 keys = 4 chunks of 16 bytes; key c*32 lives in half c/2, chunk (c&1)*4 + q
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            const int chunk16 = (c & 1) * 4 + q4;
+                            *reinterpret_cast<uint4*>(p_row + (c >> 1) * kTcHalf + ((chunk16 ^ rx) << 4)) =
+                                make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
+                        }
+                    }
+                    l_run = l_run * alpha + rs;
+                    m_run = m_new;
+                    tc_fence_before();
+                    mbar_arrive(bar(S_EMPTY, j & 1));
+                    fence_proxy_async();
+                    mbar_arrive(bar(P_FULL));
+                }
+            }
+            // fold O_{j-1} into the register accumulator and rescale to the new maximum
+            if (ok && j > 0) {
+                tc_fence_after();
+                const uint32_t o_addr = tmem + lane_sel + 256 + ((j - 1) & 1) * 128;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t v[32];
+                    tc_ld32(o_addr + c * 32, v);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = (o_acc[c * 32 + i] + __uint_as_float(v[i])) * alpha;
+                }
+                tc_fence_before();
+                mbar_arrive(bar(O_EMPTY, (j - 1) & 1));
+            }
+        }
+        // last tile's O
+        if (ok && !tc_wait(bar(O_FULL, (n_kt - 1) & 1), ((n_kt - 1) >> 1) & 1, s_abort)) ok = false;
+        if (ok) {
+            tc_fence_after();
+            const uint32_t o_addr = tmem + lane_sel + 256 + ((n_kt - 1) & 1) * 128;
+            const float inv = 1.f / l_run;
+            __nv_bfloat16* dst = p.out + q_base + int64_t(row) * p.q_row_stride;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t v[32];
+                tc_ld32(o_addr + c * 32, v);
+                tc_wait_ld();
+                if (row < lq) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 w;
+                        w.x = pack_bf16((o_acc[c * 32 + i] + __uint_as_float(v[i])) * inv, (o_acc[c * 32 + i + 1] + __uint_as_float(v[i + 1])) * inv);
+                        w.y = pack_bf16((o_acc[c * 32 + i + 2] + __uint_as_float(v[i + 2])) * inv, (o_acc[c * 32 + i + 3] + __uint_as_float(v[i + 3])) * inv);
+                        w.z = pack_bf16((o_acc[c * 32 + i + 4] + __uint_as_float(v[i + 4])) * inv, (o_acc[c * 32 + i + 5] + __uint_as_float(v[i + 5])) * inv);
+                        w.w = pack_bf16((o_acc[c * 32 + i + 6] + __uint_as_float(v[i + 6])) * inv, (o_acc[c * 32 + i + 7] + __uint_as_float(v[i + 7])) * inv);
+                        *reinterpret_cast<uint4*>(dst + c * 32 + i) = w;
+                    }
+                }
+            }
+            tc_fence_before();
+        }
+    }
+
+    // ===================================================================== common epilogue
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+    if (threadIdx.x == 0 && *s_abort && p.status) atomicExch(p.status, 0x5AFE0005);
+}
+
+int launch_prefill_tc(bool paged, const PrefillParams& p, const CUtensorMap& mq, const CUtensorMap& mk,
+                      const CUtensorMap& mv, int max_q, int batch, cudaStream_t st) {
+    if (max_q <= 0 || batch <= 0) return INFER_OK;
+    dim3 grid((max_q + kTcRows - 1) / kTcRows, p.n_q_heads, batch);
+    const int smem = TcSmem::total + 1024;
+    if (paged) {
+        IB_CUDA(cudaFuncSetAttribute(prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        prefill_tc_kernel<true><<<grid, kTcThreads, smem, st>>>(p, mq, mk, mv);
+    } else {
+        IB_CUDA(cudaFuncSetAttribute(prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        prefill_tc_kernel<false><<<grid, kTcThreads, smem, st>>>(p, mq, mk, mv);
+    }
+    return check_launch();
+}
+
+}  // namespace ib

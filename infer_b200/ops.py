@@ -166,7 +166,7 @@ def paged_attn_prefill(q, k_cache, v_cache, cu_seqlens_q, cu_seqlens_k, max_seql
     o = torch.empty_like(q) if out is None else out
     lib = _lib.load()
     with torch.cuda.device(pool.device):
-        rc = lib.infer_paged_prefill(pool.handle, _ptr(o), _ptr(q), _ptr(cu_seqlens_q), _ptr(cu_seqlens_k),
+        rc = lib.infer_paged_prefill(pool.handle, _ptr(o), _ptr(q), q.shape[0], _ptr(cu_seqlens_q), _ptr(cu_seqlens_k),
                                      _ptr(block_table), block_table.stride(0), cu_seqlens_q.numel() - 1,
                                      int(max_seqlen_q), int(max_seqlen_k), q.shape[1], float(softmax_scale),
                                      _stream())

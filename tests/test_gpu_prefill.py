@@ -12,6 +12,13 @@ from oracle import paged_kv_oracle as oracle
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(params=["1", "2"], ids=["mma", "tcgen05"], autouse=True)
+def prefill_impl(request, monkeypatch):
+    """Every test of this file runs on both prefill kernels."""
+    monkeypatch.setenv("INFER_B200_PREFILL_IMPL", request.param)
+    return request.param
+
+
 def _run(w):
     d = to_dev(w)
     cu_q, cu_k = w.cu_seqlens()
