@@ -5,11 +5,13 @@
 //                    swizzle, written by TMA), accumulator in tensor memory (128 columns)
 //   softmax          four warps, one thread per query row = one TMEM lane: tcgen05.ld of the
 //                    row, running max / sum in registers, P written to shared memory as bf16
-//   O_j = P V        tcgen05.mma, A = P (K-major), B = V (MN-major: dims contiguous),
-//                    accumulator in tensor memory; the softmax threads fold O_j into their
-//                    register accumulator with the online-softmax correction
-// S and O are double-buffered in TMEM (4 x 128 = all 512 columns), so S_{j+1} is computed
-// while the softmax of tile j runs.  Warp roles: 0-3 softmax, 4 TMA producer, 5 MMA issue
+//   O += P V         tcgen05.mma, A = P (K-major), B = V (MN-major: dims contiguous), the
+//                    accumulator stays in tensor memory for the whole key loop
+// The softmax keeps a reference maximum per row and only moves it (rescaling the row of O in
+// tensor memory and the running sum) when the true maximum has grown by more than 2^8; the
+// result is exact because O and the sum always share the same reference.  S and P are
+// double-buffered, so S_{j+1} and P V_j run on the tensor core while the softmax of the next
+// tile proceeds.  Warp roles: 0-3 softmax, 4 TMA producer, 5 MMA issue
 // and TMEM allocation.  Every barrier wait is bounded; a wait that runs out raises a CTA-wide
 // abort flag, every role drains to the common epilogue, TMEM is freed and a status is set.
 #include "prefill.cuh"
@@ -26,15 +28,16 @@ struct TcSmem {
     static constexpr int q = 0;
     static constexpr int k = q + kTcTile;            // 2 stages
     static constexpr int v = k + 2 * kTcTile;        // 2 stages
-    static constexpr int p = v + 2 * kTcTile;
-    static constexpr int bars = p + kTcTile;         // 8-byte mbarriers
+    static constexpr int p = v + 2 * kTcTile;        // 2 buffers
+    static constexpr int bars = p + 2 * kTcTile;     // 8-byte mbarriers
     static constexpr int n_bars = 20;
     static constexpr int misc = bars + n_bars * 8;   // tmem base, abort flag
     static constexpr int total = misc + 16;
 };
 
 enum TcBar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, S_EMPTY = 11, P_FULL = 13,
-             O_FULL = 14, O_EMPTY = 16, DRAIN = 18 };
+             P_EMPTY = 15, PV_DONE = 17, DRAIN = 18 };
+constexpr float kLazyLog2 = 8.f;              // the reference maximum may lag the true one by 2^8
 
 // ---- tcgen05 wrappers
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -61,6 +64,18 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+        "%29,%30,%31};"
+        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+          "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+          "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]), "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor, 128-byte swizzle, 8-row groups 1024 bytes apart.
@@ -135,17 +150,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
             mbar_init(bar(V_EMPTY, i), 1);
             mbar_init(bar(S_FULL, i), 1);
             mbar_init(bar(S_EMPTY, i), 128);
-            mbar_init(bar(O_FULL, i), 1);
-            mbar_init(bar(O_EMPTY, i), 128);
+            mbar_init(bar(P_FULL, i), 128);
+            mbar_init(bar(P_EMPTY, i), 1);
         }
-        mbar_init(bar(P_FULL), 128);
+        mbar_init(bar(PV_DONE), 1);
         mbar_init(bar(DRAIN), 1);
         *s_abort = 0;
         fence_mbar_init();
         fence_proxy_async();
     }
     if (warp == 5) {
-        // all 512 columns: S0, S1, O0, O1 (one CTA per SM by shared-memory use)
+        // S0, S1, O = 384 columns; allocations are powers of two (one CTA per SM by shared-memory use)
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(base + uint32_t(TcSmem::misc)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -244,21 +259,22 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
                     __syncwarp();
                 }
             }
-            if (ok && !tc_wait(bar(P_FULL), j & 1, s_abort)) ok = false;
-            if (ok && !tc_wait(bar(O_EMPTY, j & 1), ((j >> 1) & 1) ^ 1, s_abort)) ok = false;
+            if (ok && !tc_wait(bar(P_FULL, j & 1), (j >> 1) & 1, s_abort)) ok = false;
             if (!ok) break;
             tc_fence_after();
             if (lane == 0) {
                 const uint32_t v_addr = base + TcSmem::v + (j & 1) * kTcTile;
+                const uint32_t pj_addr = p_addr + (j & 1) * kTcTile;
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
                     const uint32_t a_off = (ks >> 2) * kTcHalf + (ks & 3) * 32;   // 16 keys along P's K-major rows
                     const uint32_t b_off = ks * 16 * 128;                         // 16 key rows of V
-                    tc_mma(tmem + 256 + (j & 1) * 128, tc_desc(p_addr + a_off, 16), tc_desc(v_addr + b_off, kTcHalf),
-                           idesc_pv, ks > 0);
+                    tc_mma(tmem + 256, tc_desc(pj_addr + a_off, 16), tc_desc(v_addr + b_off, kTcHalf), idesc_pv,
+                           (j > 0 || ks > 0) ? 1u : 0u);
                 }
-                tc_commit(bar(O_FULL, j & 1));
+                tc_commit(bar(PV_DONE));
                 tc_commit(bar(V_EMPTY, j & 1));
+                tc_commit(bar(P_EMPTY, j & 1));
             }
             __syncwarp();
         }
@@ -273,99 +289,91 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
         const int row = qt * kTcRows + r;
         const int pos = shift + row;
         const int cta_first_pos = shift + qt * kTcRows;
-        float o_acc[128];
-#pragma unroll
-        for (int i = 0; i < 128; ++i) o_acc[i] = 0.f;
-        float m_run = -INFINITY, l_run = 0.f;
-        uint8_t* p_row = smem + TcSmem::p + r * 128;
+        const uint32_t o_addr = tmem + lane_sel + 256;
+        float m_ref = -INFINITY, l_run = 0.f;                      // reference maximum (log2 domain), row sum
         const int rx = r & 7;
 
         for (int j = 0; j < n_kt; ++j) {
             if (ok && !tc_wait(bar(S_FULL, j & 1), (j >> 1) & 1, s_abort)) ok = false;
-            float alpha = 0.f;
-            if (ok) {
-                tc_fence_after();
+            if (!ok) continue;
+            tc_fence_after();
+            uint32_t sv[128];
+            {
                 const uint32_t s_addr = tmem + lane_sel + (j & 1) * 128;
-                const int key0 = j * kTcKeys;
-                const int limit = pos - key0;                        // columns <= limit are visible
-                const bool masked = key0 + kTcKeys - 1 > cta_first_pos;
-                // pass 1: row maximum
-                float mx = -INFINITY;
+                tc_ld32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+                tc_ld32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
+                tc_ld32(s_addr + 64, *reinterpret_cast<uint32_t(*)[32]>(&sv[64]));
+                tc_ld32(s_addr + 96, *reinterpret_cast<uint32_t(*)[32]>(&sv[96]));
+                tc_wait_ld();
+            }
+            tc_fence_before();
+            mbar_arrive(bar(S_EMPTY, j & 1));                        // S_{j+2} may overwrite this buffer
+
+            const int key0 = j * kTcKeys;
+            const int limit = pos - key0;                            // columns <= limit are visible
+            const bool masked = key0 + kTcKeys - 1 > cta_first_pos;
+            float mx = -INFINITY;
+            if (masked) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t v[32];
-                    tc_ld32(s_addr + c * 32, v);
-                    tc_wait_ld();
-                    if (masked) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, c * 32 + i <= limit ? __uint_as_float(v[i]) : -INFINITY);
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
-                    }
+                for (int i = 0; i < 128; ++i) {
+                    if (i > limit) sv[i] = 0xff800000u;              // -inf
+                    mx = fmaxf(mx, __uint_as_float(sv[i]));
                 }
-                const float m_new = fmaxf(m_run, mx * p.scale_log2);
-                const float m_use = m_new == -INFINITY ? 0.f : m_new;
-                alpha = fast_exp2(m_run - m_use);
-                // P smem and O_{j-1} are free / ready once PV_{j-1} has retired
-                if (j > 0 && !tc_wait(bar(O_FULL, (j - 1) & 1), ((j - 1) >> 1) & 1, s_abort)) ok = false;
-                if (ok) {
-                    // pass 2: P = exp2(S * c - m), row sum, bf16 into the swizzled P tile
-                    float rs = 0.f;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
+            }
+            mx *= p.scale_log2;
+            // move the reference only when the maximum outgrew it by more than 2^kLazyLog2
+            const bool move = mx > m_ref + kLazyLog2 || (m_ref == -INFINITY && mx > -INFINITY);
+            if (__any_sync(0xffffffffu, move)) {
+                const float m_new = move ? mx : m_ref;
+                const float alpha = m_ref == -INFINITY ? 0.f : fast_exp2(m_ref - m_new);
+                if (j > 0) {
+                    // O holds tiles < j once P V_{j-1} has retired; P V_j cannot start before P_FULL below
+                    if (!tc_wait(bar(PV_DONE), (j - 1) & 1, s_abort)) { ok = false; continue; }
+                    tc_fence_after();
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         uint32_t v[32];
-                        tc_ld32(s_addr + c * 32, v);
+                        tc_ld32(o_addr + c * 32, v);
                         tc_wait_ld();
-                        uint32_t packed[16];
 #pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            float e0 = fast_exp2(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_use));
-                            float e1 = fast_exp2(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_use));
-                            if (masked) {
-                                if (c * 32 + i > limit) e0 = 0.f;
-                                if (c * 32 + i + 1 > limit) e1 = 0.f;
-                            }
-                            rs += e0 + e1;
-                            packed[i >> 1] = pack_bf16(e0, e1);
-                        }
-                        // 32 keys = 4 chunks of 16 bytes; key c*32 lives in half c/2, chunk (c&1)*4 + q
-#pragma unroll
-                        for (int q4 = 0; q4 < 4; ++q4) {
-                            const int chunk16 = (c & 1) * 4 + q4;
-                            *reinterpret_cast<uint4*>(p_row + (c >> 1) * kTcHalf + ((chunk16 ^ rx) << 4)) =
-                                make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
-                        }
+                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                        tc_st32(o_addr + c * 32, v);
                     }
-                    l_run = l_run * alpha + rs;
-                    m_run = m_new;
-                    tc_fence_before();
-                    mbar_arrive(bar(S_EMPTY, j & 1));
-                    fence_proxy_async();
-                    mbar_arrive(bar(P_FULL));
+                    tc_wait_st();
                 }
+                l_run *= alpha;
+                m_ref = m_new;
             }
-            // fold O_{j-1} into the register accumulator and rescale to the new maximum
-            if (ok && j > 0) {
-                tc_fence_after();
-                const uint32_t o_addr = tmem + lane_sel + 256 + ((j - 1) & 1) * 128;
+            const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+
+            if (!tc_wait(bar(P_EMPTY, j & 1), ((j >> 1) & 1) ^ 1, s_abort)) { ok = false; continue; }
+            uint8_t* p_row = smem + TcSmem::p + (j & 1) * kTcTile + r * 128;
+            float rs0 = 0.f, rs1 = 0.f;
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t v[32];
-                    tc_ld32(o_addr + c * 32, v);
-                    tc_wait_ld();
+            for (int c8 = 0; c8 < 16; ++c8) {                        // 8 keys = one 16-byte chunk
+                uint32_t w[4];
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = (o_acc[c * 32 + i] + __uint_as_float(v[i])) * alpha;
+                for (int i = 0; i < 4; ++i) {
+                    const float e0 = fast_exp2(fmaf(__uint_as_float(sv[c8 * 8 + 2 * i]), p.scale_log2, -m_use));
+                    const float e1 = fast_exp2(fmaf(__uint_as_float(sv[c8 * 8 + 2 * i + 1]), p.scale_log2, -m_use));
+                    rs0 += e0;
+                    rs1 += e1;
+                    w[i] = pack_bf16(e0, e1);
                 }
-                tc_fence_before();
-                mbar_arrive(bar(O_EMPTY, (j - 1) & 1));
+                *reinterpret_cast<uint4*>(p_row + (c8 >> 3) * kTcHalf + (((c8 & 7) ^ rx) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
+            l_run += rs0 + rs1;
+            tc_fence_before();
+            fence_proxy_async();
+            mbar_arrive(bar(P_FULL, j & 1));
         }
-        // last tile's O
-        if (ok && !tc_wait(bar(O_FULL, (n_kt - 1) & 1), ((n_kt - 1) >> 1) & 1, s_abort)) ok = false;
+        // O is complete once the last P V has retired
+        if (ok && !tc_wait(bar(PV_DONE), (n_kt - 1) & 1, s_abort)) ok = false;
         if (ok) {
             tc_fence_after();
-            const uint32_t o_addr = tmem + lane_sel + 256 + ((n_kt - 1) & 1) * 128;
             const float inv = 1.f / l_run;
             __nv_bfloat16* dst = p.out + q_base + int64_t(row) * p.q_row_stride;
 #pragma unroll
@@ -377,10 +385,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
                         uint4 w;
-                        w.x = pack_bf16((o_acc[c * 32 + i] + __uint_as_float(v[i])) * inv, (o_acc[c * 32 + i + 1] + __uint_as_float(v[i + 1])) * inv);
-                        w.y = pack_bf16((o_acc[c * 32 + i + 2] + __uint_as_float(v[i + 2])) * inv, (o_acc[c * 32 + i + 3] + __uint_as_float(v[i + 3])) * inv);
-                        w.z = pack_bf16((o_acc[c * 32 + i + 4] + __uint_as_float(v[i + 4])) * inv, (o_acc[c * 32 + i + 5] + __uint_as_float(v[i + 5])) * inv);
-                        w.w = pack_bf16((o_acc[c * 32 + i + 6] + __uint_as_float(v[i + 6])) * inv, (o_acc[c * 32 + i + 7] + __uint_as_float(v[i + 7])) * inv);
+                        w.x = pack_bf16(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
+                        w.y = pack_bf16(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
+                        w.z = pack_bf16(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
+                        w.w = pack_bf16(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
                         *reinterpret_cast<uint4*>(dst + c * 32 + i) = w;
                     }
                 }
