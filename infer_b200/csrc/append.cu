@@ -14,6 +14,7 @@ __global__ void __launch_bounds__(256) append_bf16_kernel(
     const uint4* __restrict__ k, const uint4* __restrict__ v, int64_t k_pitch16, int64_t v_pitch16,
     uint4* __restrict__ k_cache, uint4* __restrict__ v_cache, const int32_t* __restrict__ slot_mapping,
     int64_t n_tokens, int chunks, int64_t num_slots) {
+    pdl_launch_dependents();   // an attention kernel behind this one may run its prologue already
     const int64_t total = n_tokens * chunks;
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
     for (int64_t u0 = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; u0 < total; u0 += 2 * stride) {

@@ -13,6 +13,7 @@
 // decode_common.cuh.
 #include <cstdlib>
 #include <mutex>
+#include <utility>
 
 #include "decode_common.cuh"
 
@@ -28,6 +29,8 @@ __global__ void __launch_bounds__(128) decode_simple_kernel(DecodeParams p) {
     __shared__ float s_o[4][G][kHeadDim];
 
     build_tile_prefix(p.context_lens, p.batch, TT, s_tp, s_scan);
+    pdl_launch_dependents();
+    pdl_wait();
     const int ng = p.n_kv_heads;
     const int total = ng * s_tp[p.batch];
     const int chunk = max(1, (total + int(gridDim.x) - 1) / int(gridDim.x));
@@ -143,8 +146,9 @@ __global__ void __launch_bounds__(128) decode_simple_kernel(DecodeParams p) {
 }
 
 // =========================================================================== reduce kernel
-// grid = batch * NG, 128 threads (one per output dim); rows = HPC * group per (b, hg)
+// grid = batch * NG, 128 threads: warp w merges rows w, w + 4, ...; a lane owns 4 output dims.
 __global__ void __launch_bounds__(128) decode_reduce_kernel(DecodeParams p, int rows) {
+    pdl_wait();
     const int ng = p.n_kv_heads / p.hpc;
     const int b = blockIdx.x / ng, hg = blockIdx.x - b * ng;
     const int nt = p.prefix[b + 1] - p.prefix[b];
@@ -153,22 +157,28 @@ __global__ void __launch_bounds__(128) decode_reduce_kernel(DecodeParams p, int 
     const int s = ng * p.prefix[b] + hg * nt, e = s + nt;
     const int c0 = s / chunk, c1 = (e - 1) / chunk;
     if (c0 == c1) return;
-    const int d = threadIdx.x;
-    for (int r = 0; r < rows; ++r) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int r = warp; r < rows; r += 4) {
         float mm = -INFINITY;
         for (int c = c0; c <= c1; ++c) {
             const int slot = c * 2 + (c == c0 ? 1 : 0);
             mm = fmaxf(mm, p.ws_ml[(int64_t(slot) * rows + r) * 2]);
         }
-        float ll = 0.f, oo = 0.f;
+        float ll = 0.f;
+        float4 oo = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int c = c0; c <= c1; ++c) {
             const int slot = c * 2 + (c == c0 ? 1 : 0);
-            const float mc = p.ws_ml[(int64_t(slot) * rows + r) * 2];
-            const float a = mc == -INFINITY ? 0.f : exp2f(mc - mm);
-            ll += p.ws_ml[(int64_t(slot) * rows + r) * 2 + 1] * a;
-            oo += p.ws_o[(int64_t(slot) * rows + r) * kHeadDim + d] * a;
+            const float2 ml = *reinterpret_cast<const float2*>(p.ws_ml + (int64_t(slot) * rows + r) * 2);
+            const float a = ml.x == -INFINITY ? 0.f : exp2f(ml.x - mm);
+            const float4 o = *reinterpret_cast<const float4*>(p.ws_o + (int64_t(slot) * rows + r) * kHeadDim + lane * 4);
+            ll += ml.y * a;
+            oo.x += o.x * a; oo.y += o.y * a; oo.z += o.z * a; oo.w += o.w * a;
         }
-        p.out[(int64_t(b) * p.n_q_heads + hg * rows + r) * kHeadDim + d] = __float2bfloat16(oo / ll);
+        const float inv = 1.f / ll;
+        uint2 packed;
+        packed.x = pack_bf16(oo.x * inv, oo.y * inv);
+        packed.y = pack_bf16(oo.z * inv, oo.w * inv);
+        *reinterpret_cast<uint2*>(p.out + (int64_t(b) * p.n_q_heads + hg * rows + r) * kHeadDim + lane * 4) = packed;
     }
 }
 
@@ -218,6 +228,10 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_kernel(DecodeParams
         fence_proxy_async();
     }
     build_tile_prefix(p.context_lens, p.batch, TT, s_tp, s_scan);   // ends with __syncthreads
+    // Everything above only reads step metadata; the pools and q may still be written by the
+    // kernel in front of this one (the append) when this kernel was launched programmatically.
+    pdl_launch_dependents();
+    pdl_wait();
 
     const int ng = p.n_kv_heads / HPC;
     const int total = ng * s_tp[p.batch];
@@ -434,6 +448,10 @@ struct DecodeConfig {
     int rows;   // partial rows per scratch slot
 };
 
+static void set_cuda_error_if(cudaError_t e) {
+    if (e != cudaSuccess) set_cuda_error(e);
+}
+
 static int env_int(const char* name, int dflt) {
     const char* s = std::getenv(name);
     return s && *s ? std::atoi(s) : dflt;
@@ -464,9 +482,27 @@ static DecodeConfig decode_config(const infer_kv_pool* pool, int n_q_heads) {
     return c;
 }
 
+// Launch with the programmatic-serialization attribute: the kernel may begin while the one in
+// front of it in the stream drains; it synchronises itself with pdl_wait().
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 template <int G, bool FP8>
 static void launch_simple(const DecodeParams& p, int grid, cudaStream_t st) {
-    decode_simple_kernel<G, FP8><<<grid, 128, 0, st>>>(p);
+    set_cuda_error_if(launch_pdl(decode_simple_kernel<G, FP8>, dim3(grid), dim3(128), 0, st, p));
 }
 
 template <int HPC>
@@ -475,7 +511,8 @@ static int launch_tma(const DecodeParams& p, const infer_kv_pool* pool, int grid
     while ((16 << idx) != 128 / HPC) ++idx;
     const int smem = TmaSmem::total + 1024;
     IB_CUDA(cudaFuncSetAttribute(decode_tma_kernel<HPC>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    decode_tma_kernel<HPC><<<grid, kTmaThreads, smem, st>>>(p, pool->maps[idx].k, pool->maps[idx].v);
+    IB_CUDA(launch_pdl(decode_tma_kernel<HPC>, dim3(grid), dim3(kTmaThreads), smem, st, p, pool->maps[idx].k,
+                       pool->maps[idx].v));
     return INFER_OK;
 }
 
@@ -556,7 +593,7 @@ int infer_paged_decode(const infer_kv_pool_t* pool, void* out, const void* q, co
     }
     int rc = check_launch();
     if (rc != INFER_OK) return rc;
-    decode_reduce_kernel<<<batch * (pool->n_kv_heads / cfg.hpc), 128, 0, st>>>(p, cfg.rows);
+    IB_CUDA(launch_pdl(decode_reduce_kernel, dim3(batch * (pool->n_kv_heads / cfg.hpc)), dim3(128), 0, st, p, cfg.rows));
     return check_launch();
 }
 

@@ -65,8 +65,8 @@ class KVPool:
 
     def __del__(self):
         h = getattr(self, "handle", None)
-        if h:
-            _lib.load().infer_kv_pool_destroy(h)
+        if h and _lib is not None and getattr(_lib, "_lib", None) is not None:   # not at interpreter teardown
+            _lib._lib.infer_kv_pool_destroy(h)
             self.handle = None
 
 
