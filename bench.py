@@ -197,7 +197,7 @@ def run_prefill(args):
             ops.paged_attn_prefill(w.q, w.k_cache, w.v_cache, cu_q, cu_k, mq, mk, w.scale, bt, out=out)
             ev[i][2].record(stream)
         torch.cuda.synchronize()
-        t_end = time.time() + 0.5
+        t_end = time.time() + (0.0 if args.profile else 0.5)
         while time.time() < t_end:
             step()
         torch.cuda.synchronize()
@@ -235,6 +235,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile", action="store_true",
+                    help="short run for profiler captures: no end-to-end leg, no CPU baseline, no padding of the "
+                         "clock-sampling window, 3 bulk appends")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
                     help="decode = the headline append + paged decode step; prefill = the paged chunked-prefill "
                          "configuration (16 sequences, prefix U[0,4096], chunk 2048), single GPU")
@@ -304,7 +307,7 @@ def main():
         stop.record(stream)
         barrier()
         # keep the sampler alive for at least a few samples on very short runs
-        if start.elapsed_time(stop) < 500:
+        if start.elapsed_time(stop) < 500 and not args.profile:
             t_end = time.time() + 0.6
             while time.time() < t_end:
                 step()
@@ -314,31 +317,35 @@ def main():
     append_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
 
     # ---- end to end: host inputs in pinned memory, output read back, every step
-    host = {k: getattr(w, k).cpu().pin_memory() for k in ("q", "k", "v")}
-    host.update(slots=slots.cpu().pin_memory(), cl=cl.cpu().pin_memory(), bt=bt.cpu().pin_memory())
-    dev = {k: torch.empty_like(v, device=device) for k, v in host.items()}
+    from infer_b200.staging import StepStaging
+    src = {"q": w.q, "k": w.k, "v": w.v, "slots": slots, "cl": cl, "bt": bt}
+    stage = StepStaging({k: (tuple(v.shape), v.dtype) for k, v in src.items()}, device)
+    for k, v in src.items():
+        stage.host[k].copy_(v)                                # the step's inputs as the host produced them
+    dev = stage.dev
     out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
-    h2d = sum(v.numel() * v.element_size() for v in host.values())
+    h2d = sum(v.numel() * v.element_size() for v in src.values())
     d2h = out_host.numel() * out_host.element_size()
 
     def e2e_step():
-        for k, v in host.items():
-            dev[k].copy_(v, non_blocking=True)
+        stage.upload()                                        # one copy for q, k, v and the step metadata
         ops.store_kvcache(dev["k"], dev["v"], w.k_cache, w.v_cache, dev["slots"])
         ops.paged_attn_decode(dev["q"], w.k_cache, w.v_cache, dev["cl"], dev["bt"], w.scale, out=out)
         out_host.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()       # the caller reads the result every step
 
-    for _ in range(args.warmup):
-        e2e_step()
-    barrier()
     e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if not args.profile:
+        for _ in range(args.warmup):
+            e2e_step()
+    barrier()
     e_start.record(stream)
-    for _ in range(args.steps):
-        e2e_step()
+    if not args.profile:
+        for _ in range(args.steps):
+            e2e_step()
     e_stop.record(stream)
     barrier()
-    e2e_ms = e_start.elapsed_time(e_stop)
+    e2e_ms = max(e_start.elapsed_time(e_stop), 1e-6)
 
     # ---- bulk append (the chunked-prefill append: 32768 rows)
     n_bulk = 32768
@@ -347,11 +354,11 @@ def main():
     bk = torch.randn(n_bulk, hkv, 128, generator=gen, device=device).bfloat16()
     bv = torch.randn(n_bulk, hkv, 128, generator=gen, device=device).bfloat16()
     bslots = torch.randperm(w.num_blocks * 256, generator=gen, device=device)[:n_bulk].to(torch.int32)
-    for _ in range(3):
+    reps = 3 if args.profile else 20
+    for _ in range(0 if args.profile else 3):
         ops.store_kvcache(bk, bv, w.k_cache, w.v_cache, bslots)
     torch.cuda.synchronize()
     a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    reps = 20
     a0.record(stream)
     for _ in range(reps):
         ops.store_kvcache(bk, bv, w.k_cache, w.v_cache, bslots)
@@ -394,7 +401,7 @@ def main():
                        "bulk_gbs": bulk_bytes / (bulk_ms * 1e-3) / 1e9, "bulk_frac": bulk_bytes / (bulk_ms * 1e-3) / 1e9 / peak},
             "clocks": clocks.summary(),
         }
-        if not args.no_cpu_baseline and world == 1:
+        if not args.no_cpu_baseline and not args.profile and world == 1:
             secs, cpu_bytes, threads = cpu_sample(w, 8, 2)
             line["cpu_baseline"] = {
                 "value": cpu_bytes / secs / 1e9, "unit": UNIT, "cores": threads, "kind": "port",

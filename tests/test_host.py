@@ -101,3 +101,17 @@ def test_two_rank_head_sharding_over_gloo():
         p.join(30)
         assert p.exitcode == 0
     assert ok
+
+
+def test_step_staging_round_trip():
+    from infer_b200.staging import StepStaging
+    spec = {"slots": ((7,), torch.int32), "q": ((3, 4, 128), torch.bfloat16), "bt": ((3, 5), torch.int32)}
+    st = StepStaging(spec, "cpu")
+    st.host["slots"].copy_(torch.arange(7, dtype=torch.int32))
+    st.host["q"].fill_(0.5)
+    st.host["bt"].fill_(-1)
+    st.upload()
+    assert st.dev["slots"].tolist() == list(range(7))
+    assert float(st.dev["q"].float().sum()) == 0.5 * 3 * 4 * 128
+    assert bool((st.dev["bt"] == -1).all())
+    assert st.dev["q"].data_ptr() % 256 == st._dev.data_ptr() % 256      # every view is 256-byte aligned
