@@ -123,8 +123,8 @@ INFER_API int infer_flash_attn_prefill(const void* q, const void* k, const void*
  * else is rewritten before it is read.  Two calls that overlap on the GPU (different
  * streams, or concurrent graphs) race on the array: serialise them.
  *
- * Limits: the scratch layout for the pool's geometry and this GPU must fit 2 MiB (bf16 pools,
- * up to 8 query heads per KV head, GPUs of up to about 240 SMs) and batch <= 2048; anything
+ * Limits: the scratch layout for the pool's geometry and this GPU must fit 2 MiB (up to 8 query
+ * heads per KV head, GPUs of up to about 240 SMs) and batch <= 2048; anything
  * larger returns INFER_ERR_TOO_LARGE without launching. */
 INFER_API int infer_paged_decode_noalloc(const infer_kv_pool_t* pool, void* out, const void* q,
                                const int32_t* context_lens, const int32_t* block_tables,

@@ -439,6 +439,266 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_kernel(DecodeParams
     if (!ok && lane == 0) atomicExch(p.header, kStatusMagic | 2);
 }
 
+// =========================================================================== TMA kernel, e4m3 pools
+// Same work split, ring and merge as decode_tma_kernel<1>, with a tile of one whole 256-token
+// page of one kv head (32 KiB of K + 32 KiB of V).  K and V bytes go from shared memory to
+// the tensor cores as f16 (e4m3 -> f16 is exact), q is converted to f16 once per segment.
+// The page's K scale is folded into the softmax exponent; the V scale is handled by keeping
+// the accumulator in units of the current page's V scale and folding scale changes into the
+// online-softmax correction, so no per-element dequantisation multiply is needed.
+constexpr int kFp8TileTokens = 256;
+
+struct Fp8Smem {
+    static constexpr int meta = TmaSmem::total;                 // [kStages][2] floats: k scale, v scale
+    static constexpr int total = meta + kStages * 8;
+};
+
+__global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_fp8_kernel(DecodeParams p,
+                                                                        const __grid_constant__ CUtensorMap map_k,
+                                                                        const __grid_constant__ CUtensorMap map_v) {
+    constexpr int TT = kFp8TileTokens;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    float* s_merge = reinterpret_cast<float*>(smem + TmaSmem::merge);
+    int* s_tp = reinterpret_cast<int*>(smem + TmaSmem::prefix);
+    int* s_scan = reinterpret_cast<int*>(smem + TmaSmem::scan);
+    uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + TmaSmem::bars);
+    volatile float* s_meta = reinterpret_cast<volatile float*>(smem + Fp8Smem::meta);
+    const uint32_t tiles_u32 = smem_u32(smem);
+    const uint32_t full0 = smem_u32(s_bar), empty0 = full0 + kStages * 8;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full0 + s * 8, 1);
+            mbar_init(empty0 + s * 8, kConsumerWarps);
+        }
+        fence_mbar_init();
+        fence_proxy_async();
+    }
+    build_tile_prefix(p.context_lens, p.batch, TT, s_tp, s_scan);
+    pdl_launch_dependents();
+    pdl_wait();
+
+    const int ng = p.n_kv_heads;
+    const int total = ng * s_tp[p.batch];
+    const int chunk = max(1, (total + int(gridDim.x) - 1) / int(gridDim.x));
+    if (blockIdx.x == 0) {
+        for (int i = threadIdx.x; i <= p.batch; i += blockDim.x) p.prefix[i] = s_tp[i];
+        if (threadIdx.x == 0) {
+            p.header[1] = total;
+            p.header[2] = chunk;
+            p.header[3] = gridDim.x;
+        }
+    }
+    const int lo = min(total, int(blockIdx.x) * chunk), hi = min(total, lo + chunk);
+
+    if (warp == kConsumerWarps) {
+        // ------------------------------------------------------------ producer
+        if (lane != 0) return;
+        tma_prefetch_desc(&map_k);
+        tma_prefetch_desc(&map_v);
+        uint32_t it = 0;
+        bool ok = true;
+        for (int g = lo; g < hi && ok;) {
+            const Segment sg = locate_segment(s_tp, p.batch, ng, g, hi);
+            const int32_t* table = p.block_tables + int64_t(sg.b) * p.bt_stride;
+            for (int t = sg.t0; t < sg.t1; ++t, ++it) {
+                const uint32_t s = it % kStages, ph = (it / kStages) & 1;
+                const int tok0 = t * TT;
+                const int page = table[tok0 / p.block_size];
+                const int slot0 = page * p.block_size + tok0 % p.block_size;
+                const bool page_ok = page >= 0 && page < p.num_blocks;
+                const float ks = page_ok ? p.k_scale[int64_t(page) * p.n_kv_heads + sg.hg] : 0.f;
+                const float vs = page_ok ? p.v_scale[int64_t(page) * p.n_kv_heads + sg.hg] : 0.f;
+                if (!mbar_wait(empty0 + s * 8, ph ^ 1)) { ok = false; break; }
+                s_meta[s * 2 + 0] = ks;
+                s_meta[s * 2 + 1] = vs;
+                const uint32_t bar = full0 + s * 8;
+                const uint32_t kdst = tiles_u32 + s * (2 * kTileBytes), vdst = kdst + kTileBytes;
+                mbar_expect_tx(bar, 2 * kTileBytes);      // release: the scales above are visible to the waiters
+                tma_load_3d(kdst, &map_k, bar, 0, sg.hg, slot0);
+                tma_load_3d(vdst, &map_v, bar, 0, sg.hg, slot0);
+            }
+            g += sg.t1 - sg.t0;
+        }
+        const uint32_t armed = it < uint32_t(kStages) ? it : uint32_t(kStages);
+        for (uint32_t j = 0; j < armed; ++j) {
+            const uint32_t i2 = it - 1 - j;
+            if (!mbar_wait(full0 + (i2 % kStages) * 8, (i2 / kStages) & 1)) ok = false;
+        }
+        if (!ok) atomicExch(p.header, kStatusMagic | 1);
+        return;
+    }
+
+    // ---------------------------------------------------------------- consumers: 32 tokens per warp and tile
+    const int tw = warp;
+    const int gid = lane >> 2, tig = lane & 3;
+    const int mi = lane >> 3, mr = lane & 7;
+    uint32_t it = 0;
+    bool ok = true;
+
+    for (int g = lo; g < hi;) {
+        const Segment sg = locate_segment(s_tp, p.batch, ng, g, hi);
+        const int ctx = p.context_lens[sg.b];
+        const int head = sg.hg;
+        // Query fragments in f16.  MMA k-slots (2t, 2t+1, 2t+8, 2t+9) of a 16-dim chunk carry
+        // dims (4t, 4t+1, 4t+2, 4t+3): the order in which ldmatrix hands out e4m3 bytes.
+        uint32_t qa[8][2];
+        {
+            const __nv_bfloat16* qrow = p.q + (int64_t(sg.b) * p.n_q_heads + head * p.group + gid) * kHeadDim;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                qa[c][0] = qa[c][1] = 0u;
+                if (gid < p.group) {
+                    const uint2 raw = *reinterpret_cast<const uint2*>(qrow + c * 16 + tig * 4);
+                    const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+                    const __nv_bfloat162 y = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+                    qa[c][0] = pack_f16(__low2float(x), __high2float(x));
+                    qa[c][1] = pack_f16(__low2float(y), __high2float(y));
+                }
+            }
+        }
+        float o[16][4];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+        float m_run = -INFINITY, l_run = 0.f;
+        float s_cur = 0.f;                       // V scale the accumulator is currently expressed in
+
+        for (int t = sg.t0; t < sg.t1; ++t, ++it) {
+            const uint32_t s = it % kStages, ph = (it / kStages) & 1;
+            if (ok && !mbar_wait(full0 + s * 8, ph)) ok = false;
+            const float c_k = s_meta[s * 2 + 0] * p.scale_log2;
+            const float vs = s_meta[s * 2 + 1];
+#pragma unroll
+            for (int sub = 0; sub < 2; ++sub) {
+                const int row0 = tw * 32 + sub * 16;
+                const int valid = ctx - (t * TT + row0);
+                if (!(ok && valid > 0)) continue;
+                const uint32_t kbase = tiles_u32 + s * (2 * kTileBytes);
+                const uint32_t vbase = kbase + kTileBytes;
+                float sc[2][4];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+#pragma unroll
+                for (int c2 = 0; c2 < 4; ++c2) {
+                    uint32_t r0, r1, r2, r3;     // (tokens 0-7, chunk 2c2), (0-7, 2c2+1), (8-15, 2c2), (8-15, 2c2+1)
+                    ldsm_x4(kbase + swz128(row0 + (mi >> 1) * 8 + mr, c2 * 2 + (mi & 1)), r0, r1, r2, r3);
+                    mma_f16(sc[0], qa[2 * c2][0], 0u, qa[2 * c2][1], 0u, e4m3x2_to_f16x2(r0), e4m3x2_to_f16x2(r0 >> 16));
+                    mma_f16(sc[0], qa[2 * c2 + 1][0], 0u, qa[2 * c2 + 1][1], 0u, e4m3x2_to_f16x2(r1), e4m3x2_to_f16x2(r1 >> 16));
+                    mma_f16(sc[1], qa[2 * c2][0], 0u, qa[2 * c2][1], 0u, e4m3x2_to_f16x2(r2), e4m3x2_to_f16x2(r2 >> 16));
+                    mma_f16(sc[1], qa[2 * c2 + 1][0], 0u, qa[2 * c2 + 1][1], 0u, e4m3x2_to_f16x2(r3), e4m3x2_to_f16x2(r3 >> 16));
+                }
+                if (valid < 16) {
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        if (j * 8 + 2 * tig >= valid) sc[j][0] = -INFINITY;
+                        if (j * 8 + 2 * tig + 1 >= valid) sc[j][1] = -INFINITY;
+                    }
+                }
+                float mx = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                // with c_k == 0 (all-zero page) every visible logit is 0; masked ones stay -inf
+                const float m_new = fmaxf(m_run, c_k > 0.f ? mx * c_k : 0.f);
+                float alpha = fast_exp2(m_run - m_new);
+                const float p00 = sc[0][0] == -INFINITY ? 0.f : fast_exp2(fmaf(sc[0][0], c_k, -m_new));
+                const float p01 = sc[0][1] == -INFINITY ? 0.f : fast_exp2(fmaf(sc[0][1], c_k, -m_new));
+                const float p10 = sc[1][0] == -INFINITY ? 0.f : fast_exp2(fmaf(sc[1][0], c_k, -m_new));
+                const float p11 = sc[1][1] == -INFINITY ? 0.f : fast_exp2(fmaf(sc[1][1], c_k, -m_new));
+                l_run = l_run * alpha + (p00 + p01) + (p10 + p11);
+                m_run = m_new;
+                if (vs > 0.f && vs != s_cur) {       // re-express the accumulator in this page's V scale
+                    if (s_cur > 0.f) alpha *= __fdividef(s_cur, vs);
+                    s_cur = vs;
+                }
+                const uint32_t pa0 = pack_f16(p00, p01), pa2 = pack_f16(p10, p11);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) { o[j][0] *= alpha; o[j][1] *= alpha; }
+#pragma unroll
+                for (int c2 = 0; c2 < 4; ++c2) {
+                    uint32_t r0, r1, r2, r3;     // (tokens 0-7, chunk 2c2), (8-15, 2c2), (0-7, 2c2+1), (8-15, 2c2+1)
+                    ldsm_x4_trans(vbase + swz128(row0 + (mi & 1) * 8 + mr, c2 * 2 + (mi >> 1)), r0, r1, r2, r3);
+                    if (valid < 16) {
+                        const uint32_t keep_lo = (2 * tig < valid ? 0x0000ffffu : 0u) | (2 * tig + 1 < valid ? 0xffff0000u : 0u);
+                        const uint32_t keep_hi = (8 + 2 * tig < valid ? 0x0000ffffu : 0u) | (9 + 2 * tig < valid ? 0xffff0000u : 0u);
+                        r0 &= keep_lo; r2 &= keep_lo;
+                        r1 &= keep_hi; r3 &= keep_hi;
+                    }
+                    // a transposed register holds (tok 2t, dims 2g 2g+1 | tok 2t+1, dims 2g 2g+1):
+                    // bytes (0,2) feed the even-dim tile, bytes (1,3) the odd-dim tile
+                    mma_f16(o[4 * c2 + 0], pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(__byte_perm(r0, 0, 0x0020)), e4m3x2_to_f16x2(__byte_perm(r1, 0, 0x0020)));
+                    mma_f16(o[4 * c2 + 1], pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(__byte_perm(r0, 0, 0x0031)), e4m3x2_to_f16x2(__byte_perm(r1, 0, 0x0031)));
+                    mma_f16(o[4 * c2 + 2], pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(__byte_perm(r2, 0, 0x0020)), e4m3x2_to_f16x2(__byte_perm(r3, 0, 0x0020)));
+                    mma_f16(o[4 * c2 + 3], pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(__byte_perm(r2, 0, 0x0031)), e4m3x2_to_f16x2(__byte_perm(r3, 0, 0x0031)));
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty0 + s * 8);
+        }
+        l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+        l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+        // back to true units before warps (which may sit on different pages) are merged
+#pragma unroll
+        for (int j = 0; j < 16; ++j) { o[j][0] *= s_cur; o[j][1] *= s_cur; }
+
+#pragma unroll
+        for (int stride = kConsumerWarps / 2; stride >= 1; stride >>= 1) {
+            float* slot = s_merge + (tw % stride) * kMergeSlotFloats;
+            if (tw >= stride && tw < 2 * stride) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    slot[(2 * j) * 32 + lane] = o[j][0];
+                    slot[(2 * j + 1) * 32 + lane] = o[j][1];
+                }
+                slot[32 * 32 + lane] = m_run;
+                slot[33 * 32 + lane] = l_run;
+            }
+            consumer_bar();
+            if (tw < stride) {
+                const float m2 = slot[32 * 32 + lane], l2 = slot[33 * 32 + lane];
+                const float mm = fmaxf(m_run, m2);
+                const float a1 = m_run == -INFINITY ? 0.f : fast_exp2(m_run - mm);
+                const float a2 = m2 == -INFINITY ? 0.f : fast_exp2(m2 - mm);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    o[j][0] = o[j][0] * a1 + slot[(2 * j) * 32 + lane] * a2;
+                    o[j][1] = o[j][1] * a1 + slot[(2 * j + 1) * 32 + lane] * a2;
+                }
+                l_run = l_run * a1 + l2 * a2;
+                m_run = mm;
+            }
+            consumer_bar();
+        }
+
+        if (ok && tw == 0 && gid < p.group) {
+            // accumulator tile 2c + e, column pair (2t, 2t+1) holds dims 16c + 4t + e and 16c + 4t + 2 + e
+            const bool complete = sg.t0 == 0 && sg.t1 == sg.ntiles;
+            const int qh = head * p.group + gid;
+            if (complete) {
+                const float inv = 1.f / l_run;
+                uint2* dst = reinterpret_cast<uint2*>(p.out + (int64_t(sg.b) * p.n_q_heads + qh) * kHeadDim);
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                    dst[c * 4 + tig] = make_uint2(pack_bf16(o[2 * c][0] * inv, o[2 * c + 1][0] * inv),
+                                                  pack_bf16(o[2 * c][1] * inv, o[2 * c + 1][1] * inv));
+            } else {
+                const int rows = p.group;
+                const int64_t slot = int64_t(blockIdx.x) * 2 + (sg.t0 > 0 ? 0 : 1);
+                float4* dst = reinterpret_cast<float4*>(p.ws_o + (slot * rows + gid) * kHeadDim);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) dst[c * 4 + tig] = make_float4(o[2 * c][0], o[2 * c + 1][0], o[2 * c][1], o[2 * c + 1][1]);
+                if (tig == 0) {
+                    p.ws_ml[(slot * rows + gid) * 2 + 0] = m_run;
+                    p.ws_ml[(slot * rows + gid) * 2 + 1] = l_run;
+                }
+            }
+        }
+        g += sg.t1 - sg.t0;
+    }
+    if (!ok && lane == 0) atomicExch(p.header, kStatusMagic | 2);
+}
+
 // =========================================================================== host side
 struct DecodeConfig {
     int impl;   // 1 = simple, 2 = tma
@@ -460,11 +720,14 @@ static int env_int(const char* name, int dflt) {
 static DecodeConfig decode_config(const infer_kv_pool* pool, int n_q_heads) {
     DecodeConfig c;
     const int group = n_q_heads / pool->n_kv_heads;
-    c.impl = pool->dtype == INFER_KV_BF16 ? 2 : 1;
-    const int forced = env_int("INFER_B200_DECODE_IMPL", 0);   // development switch
+    c.impl = 2;
+    const int forced = env_int("INFER_B200_DECODE_IMPL", 0);   // development switch: 1 = plain-load kernel
     if (forced == 1 || forced == 2) c.impl = forced;
-    if (pool->dtype != INFER_KV_BF16) c.impl = 1;
-    if (c.impl == 2) {
+    if (c.impl == 2 && pool->dtype == INFER_KV_E4M3) {
+        c.hpc = 1;
+        c.tile_tokens = kFp8TileTokens;
+        c.grid = pool->sm_count;
+    } else if (c.impl == 2) {
         // One kv head per tile (128 tokens x 256 B rows) measured fastest at every head count:
         // fewer, larger TMA boxes beat streaming all heads of a token row together.
         int hpc = 1;
@@ -571,7 +834,12 @@ int infer_paged_decode(const infer_kv_pool_t* pool, void* out, const void* q, co
     p.ws_ml = reinterpret_cast<float*>(ws + lay.ml_off);
     p.ws_o = reinterpret_cast<float*>(ws + lay.o_off);
 
-    if (cfg.impl == 2) {
+    if (cfg.impl == 2 && pool->dtype == INFER_KV_E4M3) {
+        const int smem = Fp8Smem::total + 1024;
+        IB_CUDA(cudaFuncSetAttribute(decode_tma_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        IB_CUDA(launch_pdl(decode_tma_fp8_kernel, dim3(cfg.grid), dim3(kTmaThreads), smem, st, p, pool->maps[4].k,
+                           pool->maps[4].v));
+    } else if (cfg.impl == 2) {
         int rc = INFER_OK;
         switch (cfg.hpc) {
             case 1: rc = launch_tma<1>(p, pool, cfg.grid, st); break;

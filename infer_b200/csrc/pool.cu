@@ -99,7 +99,7 @@ int infer_kv_pool_create(infer_kv_pool_t** out, void* k_cache, void* v_cache, fl
     const uint32_t inner = 128 / p->elem_bytes;
     const uint64_t head_pitch = uint64_t(ib::kHeadDim) * p->elem_bytes;
     const uint64_t slot_pitch = head_pitch * n_kv_heads;
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 5; ++i) {
         const uint32_t rows = 16u << i;
         int rc = ib::encode_map_3d(&p->maps[i].k, k_cache, p->elem_bytes, ib::kHeadDim, n_kv_heads, p->num_slots,
                                    head_pitch, slot_pitch, inner, 1, rows);
@@ -133,7 +133,7 @@ const char* infer_strerror(int code) {
         case INFER_ERR_DTYPE: return "pool dtype not supported by this entry point";
         case INFER_ERR_DEVICE: return "a bounded device-side wait ran out";
         case INFER_ERR_TOO_LARGE: return "problem exceeds the 2 MiB built-in scratch of infer_paged_decode_noalloc "
-                                         "(bf16 pools, batch <= 2048); use infer_paged_decode with a workspace";
+                                         "(batch <= 2048); use infer_paged_decode with a workspace";
         default: return "unknown error code";
     }
 }

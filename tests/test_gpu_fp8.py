@@ -49,7 +49,9 @@ def test_fp8_append_bit_exact(rounds):
     assert bits_equal(cpu[1], gpu[1]), "v bytes differ"
 
 
-def test_fp8_decode_step():
+@pytest.mark.parametrize("impl", ["0", "1"], ids=["tma", "plain-loads"])
+def test_fp8_decode_step(impl, monkeypatch):
+    monkeypatch.setenv("INFER_B200_DECODE_IMPL", impl)
     w = workloads.config3()
     cpu, gpu = _fill_both(w, 3)
     # the decode step's own append, then attention
@@ -61,3 +63,38 @@ def test_fp8_decode_step():
     assert bits_equal(cpu[0], gpu[0]) and torch.equal(cpu[2], gpu[2].cpu())
     want = oracle.paged_decode(w.q, cpu[0], cpu[1], cl, bt, w.scale, cpu[2], cpu[3])
     assert_close(got, want, ATOL_FP8, RTOL_FP8, "fp8 decode vs fp8 oracle")
+
+
+@pytest.mark.parametrize("impl", ["0", "1"], ids=["tma", "plain-loads"])
+def test_fp8_decode_group8_long_contexts(impl, monkeypatch):
+    """8 query heads per KV head, contexts over several pages with different scales per page,
+    lengths around the 16/32/256-token boundaries of the FP8 tile."""
+    monkeypatch.setenv("INFER_B200_DECODE_IMPL", impl)
+    gen = torch.Generator().manual_seed(91)
+    hq, hkv, nb = 16, 2, 40
+    lens = [1, 17, 255, 256, 257, 600, 1300, 33]
+    cpu = _empty_pools(nb, hkv, "cpu")
+    gpu = _empty_pools(nb, hkv, "cuda")
+    perm = torch.randperm(nb, generator=gen).tolist()
+    tables, at = [], 0
+    for n in lens:
+        need = -(-n // 256)
+        pages = perm[at:at + need]
+        at += need
+        tables.append(pages + [-1] * (6 - need))
+        # every page gets its own amplitude so that page scales differ a lot
+        k = torch.randn(n, hkv, 128, generator=gen)
+        v = torch.randn(n, hkv, 128, generator=gen)
+        amp = torch.repeat_interleave(torch.rand(need, generator=gen) * 8 + 0.1, 256)[:n]
+        k, v = (k * amp[:, None, None]).bfloat16(), (v * amp.flip(0)[:, None, None]).bfloat16()
+        slots = torch.tensor(chunk_slots(pages, 0, n, 256), dtype=torch.int32)
+        oracle.store_kvcache_fp8(k, v, *cpu, slots)
+        ops.store_kvcache(k.cuda(), v.cuda(), gpu[0], gpu[1], slots.cuda(), gpu[2], gpu[3])
+    q = torch.randn(len(lens), hq, 128, generator=gen).bfloat16()
+    cl = torch.tensor(lens, dtype=torch.int32)
+    bt = torch.tensor(tables, dtype=torch.int32)
+    got = ops.paged_attn_decode(q.cuda(), gpu[0], gpu[1], cl.cuda(), bt.cuda(), 0.09, k_scale=gpu[2], v_scale=gpu[3])
+    torch.cuda.synchronize()
+    assert bits_equal(cpu[0], gpu[0]) and bits_equal(cpu[1], gpu[1])
+    want = oracle.paged_decode(q, cpu[0], cpu[1], cl, bt, 0.09, cpu[2], cpu[3])
+    assert_close(got, want, ATOL_FP8, RTOL_FP8, f"fp8 decode, group 8, impl {impl}")

@@ -62,12 +62,5 @@ def test_noalloc_rejects_what_does_not_fit():
                                         C.c_void_p(cl.data_ptr()), C.c_void_p(bt.data_ptr()), 1, batch, 16, 0.1, None)
     assert rc == _lib.ERR_TOO_LARGE
     assert b"built-in scratch" in lib.infer_strerror(rc)
-    # an e4m3 pool needs the wider scratch of the dequantising kernel: also refused, nothing launched
-    k8 = torch.zeros(2, 256, 8, 128, dtype=torch.uint8, device=dev)
-    sc = torch.zeros(2, 8, dtype=torch.float32, device=dev)
-    pool8 = ops.pool_of(k8, k8.clone(), sc, sc.clone())
-    rc = lib.infer_paged_decode_noalloc(pool8.handle, C.c_void_p(out.data_ptr()), C.c_void_p(q.data_ptr()),
-                                        C.c_void_p(cl.data_ptr()), C.c_void_p(bt.data_ptr()), 1, 4, 16, 0.1, None)
-    assert rc == _lib.ERR_TOO_LARGE
     torch.cuda.synchronize()
-    assert bool((out == 3.0).all())
+    assert bool((out == 3.0).all())                         # nothing was launched
