@@ -115,28 +115,32 @@ __device__ __forceinline__ uint32_t rescale4(uint32_t q, float ratio) {
     return out;
 }
 
-// one CTA per (token, head, k|v); the first CTA to claim a page/head whose scale grew
-// re-encodes all of that page's rows for that head.
-__global__ void __launch_bounds__(128) fp8_rescale_kernel(Fp8Args a) {
-    __shared__ float s_ratio;
-    const int64_t item = blockIdx.x;
+// one warp per (token, head, k|v); the first warp to claim a page/head whose scale grew
+// re-encodes all of that page's rows for that head (rare: most warps leave after two loads).
+__global__ void __launch_bounds__(256) fp8_rescale_kernel(Fp8Args a) {
+    const int64_t item = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    if (item >= a.n_tokens * a.n_kv_heads * 2) return;
+    const int lane = threadIdx.x & 31;
     int which, head;
     int64_t tok, slot;
     if (!fp8_locate(a, item, which, tok, head, slot)) return;
     const int64_t page = slot / a.block_size;
     const int64_t e = page * a.n_kv_heads + head;
-    if (threadIdx.x == 0) {
-        const float old = atomicExch(a.snap[which] + e, -1.0f);
+    float ratio = -1.0f;
+    if (lane == 0) {
         const float now = a.scale[which][e];
-        s_ratio = (old > 0.0f && now > old) ? __fdiv_rn(old, now) : -1.0f;
+        const float seen = a.snap[which][e];
+        if (seen > 0.0f && now > seen) {                       // a candidate: claim it exactly once
+            const float old = atomicExch(a.snap[which] + e, -1.0f);
+            if (old > 0.0f) ratio = __fdiv_rn(old, now);
+        }
     }
-    __syncthreads();
-    const float ratio = s_ratio;
+    ratio = __shfl_sync(0xffffffffu, ratio, 0);
     if (ratio < 0.0f) return;
     // rows of this head: block_size rows of 128 bytes, pitch Hkv * 128
     uint8_t* base = a.cache[which] + (page * a.block_size * a.n_kv_heads + head) * int64_t(kHeadDim);
     const int64_t pitch = int64_t(a.n_kv_heads) * kHeadDim;
-    for (int i = threadIdx.x; i < a.block_size * 8; i += blockDim.x) {
+    for (int i = lane; i < a.block_size * 8; i += 32) {
         uint4* p = reinterpret_cast<uint4*>(base + (i >> 3) * pitch + (i & 7) * 16);
         uint4 q = *p;
         q.x = rescale4(q.x, ratio);
@@ -225,7 +229,7 @@ int infer_kv_append(const infer_kv_pool_t* pool, const void* k, const void* v, i
     if (items >= (int64_t(1) << 31)) return INFER_ERR_GEOMETRY;
     ib::fp8_snapshot_kernel<<<unsigned((items + 255) / 256), 256, 0, stream>>>(a);
     ib::fp8_amax_kernel<<<unsigned((items * 32 + 255) / 256), 256, 0, stream>>>(a);
-    ib::fp8_rescale_kernel<<<unsigned(items), 128, 0, stream>>>(a);
+    ib::fp8_rescale_kernel<<<unsigned((items * 32 + 255) / 256), 256, 0, stream>>>(a);
     ib::fp8_write_kernel<<<unsigned((items * 32 + 255) / 256), 256, 0, stream>>>(a);
     return ib::check_launch();
 }

@@ -570,67 +570,78 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_fp8_kernel(DecodePa
             if (ok && !mbar_wait(full0 + s * 8, ph)) ok = false;
             const float c_k = s_meta[s * 2 + 0] * p.scale_log2;
             const float vs = s_meta[s * 2 + 1];
-#pragma unroll
-            for (int sub = 0; sub < 2; ++sub) {
-                const int row0 = tw * 32 + sub * 16;
-                const int valid = ctx - (t * TT + row0);
-                if (!(ok && valid > 0)) continue;
+            const int row0 = tw * 32;                       // this warp's 32 tokens of the tile
+            const int valid = ctx - (t * TT + row0);
+            if (ok && valid > 0) {
                 const uint32_t kbase = tiles_u32 + s * (2 * kTileBytes);
                 const uint32_t vbase = kbase + kTileBytes;
-                float sc[2][4];
+                // S for 32 tokens: four independent accumulator tiles of 8 tokens each
+                float sc[4][4];
 #pragma unroll
-                for (int j = 0; j < 2; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+                for (int j = 0; j < 4; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
 #pragma unroll
                 for (int c2 = 0; c2 < 4; ++c2) {
-                    uint32_t r0, r1, r2, r3;     // (tokens 0-7, chunk 2c2), (0-7, 2c2+1), (8-15, 2c2), (8-15, 2c2+1)
-                    ldsm_x4(kbase + swz128(row0 + (mi >> 1) * 8 + mr, c2 * 2 + (mi & 1)), r0, r1, r2, r3);
-                    mma_f16(sc[0], qa[2 * c2][0], 0u, qa[2 * c2][1], 0u, e4m3x2_to_f16x2(r0), e4m3x2_to_f16x2(r0 >> 16));
-                    mma_f16(sc[0], qa[2 * c2 + 1][0], 0u, qa[2 * c2 + 1][1], 0u, e4m3x2_to_f16x2(r1), e4m3x2_to_f16x2(r1 >> 16));
-                    mma_f16(sc[1], qa[2 * c2][0], 0u, qa[2 * c2][1], 0u, e4m3x2_to_f16x2(r2), e4m3x2_to_f16x2(r2 >> 16));
-                    mma_f16(sc[1], qa[2 * c2 + 1][0], 0u, qa[2 * c2 + 1][1], 0u, e4m3x2_to_f16x2(r3), e4m3x2_to_f16x2(r3 >> 16));
-                }
-                if (valid < 16) {
 #pragma unroll
-                    for (int j = 0; j < 2; ++j) {
+                    for (int h = 0; h < 2; ++h) {
+                        uint32_t r0, r1, r2, r3;   // (tokens 0-7, chunk 2c2), (0-7, 2c2+1), (8-15, 2c2), (8-15, 2c2+1) of half h
+                        ldsm_x4(kbase + swz128(row0 + h * 16 + (mi >> 1) * 8 + mr, c2 * 2 + (mi & 1)), r0, r1, r2, r3);
+                        mma_f16(sc[2 * h], qa[2 * c2][0], 0u, qa[2 * c2][1], 0u, e4m3x2_to_f16x2(r0), e4m3x2_to_f16x2(r0 >> 16));
+                        mma_f16(sc[2 * h + 1], qa[2 * c2][0], 0u, qa[2 * c2][1], 0u, e4m3x2_to_f16x2(r2), e4m3x2_to_f16x2(r2 >> 16));
+                        mma_f16(sc[2 * h], qa[2 * c2 + 1][0], 0u, qa[2 * c2 + 1][1], 0u, e4m3x2_to_f16x2(r1), e4m3x2_to_f16x2(r1 >> 16));
+                        mma_f16(sc[2 * h + 1], qa[2 * c2 + 1][0], 0u, qa[2 * c2 + 1][1], 0u, e4m3x2_to_f16x2(r3), e4m3x2_to_f16x2(r3 >> 16));
+                    }
+                }
+                if (valid < 32) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
                         if (j * 8 + 2 * tig >= valid) sc[j][0] = -INFINITY;
                         if (j * 8 + 2 * tig + 1 >= valid) sc[j][1] = -INFINITY;
                     }
                 }
-                float mx = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
+                float mx = fmaxf(fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1])),
+                                 fmaxf(fmaxf(sc[2][0], sc[2][1]), fmaxf(sc[3][0], sc[3][1])));
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
                 // with c_k == 0 (all-zero page) every visible logit is 0; masked ones stay -inf
                 const float m_new = fmaxf(m_run, c_k > 0.f ? mx * c_k : 0.f);
                 float alpha = fast_exp2(m_run - m_new);
-                const float p00 = sc[0][0] == -INFINITY ? 0.f : fast_exp2(fmaf(sc[0][0], c_k, -m_new));
-                const float p01 = sc[0][1] == -INFINITY ? 0.f : fast_exp2(fmaf(sc[0][1], c_k, -m_new));
-                const float p10 = sc[1][0] == -INFINITY ? 0.f : fast_exp2(fmaf(sc[1][0], c_k, -m_new));
-                const float p11 = sc[1][1] == -INFINITY ? 0.f : fast_exp2(fmaf(sc[1][1], c_k, -m_new));
-                l_run = l_run * alpha + (p00 + p01) + (p10 + p11);
+                float pr[4][2];
+                float rs = 0.f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    pr[j][0] = sc[j][0] == -INFINITY ? 0.f : fast_exp2(fmaf(sc[j][0], c_k, -m_new));
+                    pr[j][1] = sc[j][1] == -INFINITY ? 0.f : fast_exp2(fmaf(sc[j][1], c_k, -m_new));
+                    rs += pr[j][0] + pr[j][1];
+                }
+                l_run = l_run * alpha + rs;
                 m_run = m_new;
                 if (vs > 0.f && vs != s_cur) {       // re-express the accumulator in this page's V scale
                     if (s_cur > 0.f) alpha *= __fdividef(s_cur, vs);
                     s_cur = vs;
                 }
-                const uint32_t pa0 = pack_f16(p00, p01), pa2 = pack_f16(p10, p11);
 #pragma unroll
                 for (int j = 0; j < 16; ++j) { o[j][0] *= alpha; o[j][1] *= alpha; }
 #pragma unroll
-                for (int c2 = 0; c2 < 4; ++c2) {
-                    uint32_t r0, r1, r2, r3;     // (tokens 0-7, chunk 2c2), (8-15, 2c2), (0-7, 2c2+1), (8-15, 2c2+1)
-                    ldsm_x4_trans(vbase + swz128(row0 + (mi & 1) * 8 + mr, c2 * 2 + (mi >> 1)), r0, r1, r2, r3);
-                    if (valid < 16) {
-                        const uint32_t keep_lo = (2 * tig < valid ? 0x0000ffffu : 0u) | (2 * tig + 1 < valid ? 0xffff0000u : 0u);
-                        const uint32_t keep_hi = (8 + 2 * tig < valid ? 0x0000ffffu : 0u) | (9 + 2 * tig < valid ? 0xffff0000u : 0u);
-                        r0 &= keep_lo; r2 &= keep_lo;
-                        r1 &= keep_hi; r3 &= keep_hi;
+                for (int h = 0; h < 2; ++h) {
+                    const uint32_t pa0 = pack_f16(pr[2 * h][0], pr[2 * h][1]), pa2 = pack_f16(pr[2 * h + 1][0], pr[2 * h + 1][1]);
+                    const int vh = valid - h * 16;          // tokens of this half that exist
+#pragma unroll
+                    for (int c2 = 0; c2 < 4; ++c2) {
+                        uint32_t r0, r1, r2, r3;   // (tokens 0-7, chunk 2c2), (8-15, 2c2), (0-7, 2c2+1), (8-15, 2c2+1)
+                        ldsm_x4_trans(vbase + swz128(row0 + h * 16 + (mi & 1) * 8 + mr, c2 * 2 + (mi >> 1)), r0, r1, r2, r3);
+                        if (vh < 16) {
+                            const uint32_t keep_lo = (2 * tig < vh ? 0x0000ffffu : 0u) | (2 * tig + 1 < vh ? 0xffff0000u : 0u);
+                            const uint32_t keep_hi = (8 + 2 * tig < vh ? 0x0000ffffu : 0u) | (9 + 2 * tig < vh ? 0xffff0000u : 0u);
+                            r0 &= keep_lo; r2 &= keep_lo;
+                            r1 &= keep_hi; r3 &= keep_hi;
+                        }
+                        // a transposed register holds (tok 2t, dims 2g 2g+1 | tok 2t+1, dims 2g 2g+1):
+                        // bytes (0,2) feed the even-dim tile, bytes (1,3) the odd-dim tile
+                        mma_f16(o[4 * c2 + 0], pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(__byte_perm(r0, 0, 0x0020)), e4m3x2_to_f16x2(__byte_perm(r1, 0, 0x0020)));
+                        mma_f16(o[4 * c2 + 1], pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(__byte_perm(r0, 0, 0x0031)), e4m3x2_to_f16x2(__byte_perm(r1, 0, 0x0031)));
+                        mma_f16(o[4 * c2 + 2], pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(__byte_perm(r2, 0, 0x0020)), e4m3x2_to_f16x2(__byte_perm(r3, 0, 0x0020)));
+                        mma_f16(o[4 * c2 + 3], pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(__byte_perm(r2, 0, 0x0031)), e4m3x2_to_f16x2(__byte_perm(r3, 0, 0x0031)));
                     }
-                    // a transposed register holds (tok 2t, dims 2g 2g+1 | tok 2t+1, dims 2g 2g+1):
-                    // bytes (0,2) feed the even-dim tile, bytes (1,3) the odd-dim tile
-                    mma_f16(o[4 * c2 + 0], pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(__byte_perm(r0, 0, 0x0020)), e4m3x2_to_f16x2(__byte_perm(r1, 0, 0x0020)));
-                    mma_f16(o[4 * c2 + 1], pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(__byte_perm(r0, 0, 0x0031)), e4m3x2_to_f16x2(__byte_perm(r1, 0, 0x0031)));
-                    mma_f16(o[4 * c2 + 2], pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(__byte_perm(r2, 0, 0x0020)), e4m3x2_to_f16x2(__byte_perm(r3, 0, 0x0020)));
-                    mma_f16(o[4 * c2 + 3], pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(__byte_perm(r2, 0, 0x0031)), e4m3x2_to_f16x2(__byte_perm(r3, 0, 0x0031)));
                 }
             }
             __syncwarp();
@@ -837,8 +848,7 @@ int infer_paged_decode(const infer_kv_pool_t* pool, void* out, const void* q, co
     if (cfg.impl == 2 && pool->dtype == INFER_KV_E4M3) {
         const int smem = Fp8Smem::total + 1024;
         IB_CUDA(cudaFuncSetAttribute(decode_tma_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        IB_CUDA(launch_pdl(decode_tma_fp8_kernel, dim3(cfg.grid), dim3(kTmaThreads), smem, st, p, pool->maps[4].k,
-                           pool->maps[4].v));
+        IB_CUDA(launch_pdl(decode_tma_fp8_kernel, dim3(cfg.grid), dim3(kTmaThreads), smem, st, p, pool->maps[4].k, pool->maps[4].v));
     } else if (cfg.impl == 2) {
         int rc = INFER_OK;
         switch (cfg.hpc) {

@@ -49,9 +49,11 @@ int encode_map_3d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t d
     cuuint32_t box[3] = {b0, b1, b2};
     cuuint32_t estr[3] = {1, 1, 1};
     CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    // One head's row is 256 contiguous bytes in a bf16 pool but only 128 in an e4m3 pool, where a
+    // 256-byte L2 promotion would drag in the neighbouring head's bytes and double the DRAM traffic.
+    const CUtensorMapL2promotion promo = elem_bytes == 2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B;
     CUresult r = fn(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    CU_TENSOR_MAP_SWIZZLE_128B, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         set_cuda_error(cudaErrorInvalidValue);
         return INFER_ERR_CUDA;
