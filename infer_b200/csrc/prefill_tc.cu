@@ -1,49 +1,53 @@
 // Causal attention over many query rows on the 5th-generation tensor cores (tcgen05).
 //
-// One CTA = 128 query rows of one (sequence, query head).  Per 128-key tile:
+// One CTA works on TWO query tiles of 128 rows that share every K/V tile: the two query heads
+// of a GQA pair over the same 128 rows (even group size), or two consecutive 128-row blocks
+// of one head.  Per 128-key tile and query tile:
 //   S = Q K^T        tcgen05.mma, A = Q and B = K from shared memory (K-major, 128-byte
 //                    swizzle, written by TMA), accumulator in tensor memory (128 columns)
-//   softmax          four warps, one thread per query row = one TMEM lane: tcgen05.ld of the
-//                    row, running max / sum in registers, P written back to tensor memory as
-//                    packed bf16 (two keys per 32-bit column)
-//   O += P V         tcgen05.mma, A = P from tensor memory, B = V (MN-major: dims contiguous), the
-//                    accumulator stays in tensor memory for the whole key loop
+//   softmax          one warpgroup per query tile, one thread per query row = one TMEM lane:
+//                    tcgen05.ld of the row, running max / sum in registers, P written back to
+//                    tensor memory as packed bf16 over columns of S that were already read
+//   O += P V         tcgen05.mma, A = P from tensor memory, B = V (MN-major: dims contiguous),
+//                    the accumulator stays in tensor memory for the whole key loop
+// The tensor core alternates between the two query tiles (P V of one, then its next S), so
+// while one warpgroup runs its softmax the other one's matrix products execute; the two
+// warpgroups of an SM sub-partition are independent and fill each other's latencies.
 // The softmax keeps a reference maximum per row and only moves it (rescaling the row of O in
 // tensor memory and the running sum) when the true maximum has grown by more than 2^8; the
-// result is exact because O and the sum always share the same reference.  S and P are
-// double-buffered, so S_{j+1} and P V_j run on the tensor core while the softmax of the next
-// tile proceeds.  Warp roles: 0-7 softmax (two threads per query row, each owning 64 of a
-// tile's 128 columns; they exchange their row maxima through shared memory once per tile),
-// 8 TMA producer, 9 MMA issue and TMEM allocation.  Every barrier wait is bounded; a wait that runs out raises a CTA-wide
+// result is exact because O and the sum always share the same reference.
+// Warp roles: 0-3 softmax of tile 0, 4-7 softmax of tile 1, 8 TMA producer, 9 MMA issue and
+// TMEM allocation.  Every barrier wait is bounded; a wait that runs out raises a CTA-wide
 // abort flag, every role drains to the common epilogue, TMEM is freed and a status is set.
 #include "prefill.cuh"
 
 namespace ib {
 
-constexpr int kTcRows = 128;                 // query rows per CTA
-constexpr int kTcKeys = 128;                 // keys per tile
+constexpr int kTcRows = 128;                 // query rows per query tile (= TMEM lanes)
+constexpr int kTcKeys = 128;                 // keys per K/V tile
 constexpr int kTcHalf = 128 * 128;           // bytes of one [128 rows][64 elems] swizzled sub-tile
-constexpr int kTcTile = 2 * kTcHalf;         // 32 KiB: Q, K, V or P tile
-constexpr int kTcSoftmaxWarps = 8;            // two threads per query row: columns 0-63 and 64-127 of a tile
+constexpr int kTcTile = 2 * kTcHalf;         // 32 KiB: one Q, K or V tile
+constexpr int kTcQTiles = 2;                 // query tiles per CTA, each with its own softmax warpgroup
+constexpr int kTcSoftmaxWarps = 4 * kTcQTiles;
 constexpr int kTcProducerWarp = kTcSoftmaxWarps, kTcMmaWarp = kTcSoftmaxWarps + 1;
 constexpr int kTcThreads = (kTcSoftmaxWarps + 2) * 32;
-constexpr int kTcStages = 3;                  // K and V tiles in flight
-// tensor memory columns: S0 0-127, S1 128-255, O 256-383, P0 384-447, P1 448-511
-constexpr uint32_t kTmemO = 256, kTmemP = 384;
+constexpr int kTcKStages = 3, kTcVStages = 2;
+// tensor memory columns: S of tile 0 at 0, S of tile 1 at 128, O of tile 0 at 256, O of tile 1 at 384;
+// P (bf16, two keys per column) reuses columns 64-127 of its tile's S
+constexpr uint32_t kTmemO = 256, kTmemPinS = 64;
 
 struct TcSmem {
-    static constexpr int q = 0;
-    static constexpr int k = q + kTcTile;                  // kTcStages stages
-    static constexpr int v = k + kTcStages * kTcTile;      // kTcStages stages
-    static constexpr int bars = v + kTcStages * kTcTile;   // 8-byte mbarriers
+    static constexpr int q = 0;                              // kTcQTiles tiles
+    static constexpr int k = q + kTcQTiles * kTcTile;
+    static constexpr int v = k + kTcKStages * kTcTile;
+    static constexpr int bars = v + kTcVStages * kTcTile;    // 8-byte mbarriers
     static constexpr int n_bars = 24;
-    static constexpr int misc = bars + n_bars * 8;   // tmem base, abort flag
-    static constexpr int xchg = misc + 16;           // [2 tile parities][2 column halves][128 rows] bf16 row maxima
-    static constexpr int total = xchg + 2 * 2 * 128 * 2;
+    static constexpr int misc = bars + n_bars * 8;           // tmem base, abort flag
+    static constexpr int total = misc + 16;
 };
 
-enum TcBar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 4, V_FULL = 7, V_EMPTY = 10, S_FULL = 13, S_EMPTY = 15, P_FULL = 17,
-             P_EMPTY = 19, PV_DONE = 21, DRAIN = 22 };
+enum TcBar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 4, V_FULL = 7, V_EMPTY = 9, S_FULL = 11, P_FULL = 13, PV_DONE = 15,
+             DRAIN = 17 };
 constexpr float kLazyLog2 = 8.f;              // the reference maximum may lag the true one by 2^8
 
 // ---- tcgen05 wrappers
@@ -123,8 +127,13 @@ __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile 
     return false;
 }
 
+// Which (head, row block) the two query tiles of a CTA are.
+struct TcTile {
+    int head, row0, n_kt, lq_left;   // lq_left: valid rows of the tile (<= 0: tile inactive)
+};
+
 template <bool PAGED>
-__global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams p,
+__global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams p, int pair_heads,
                                                                    const __grid_constant__ CUtensorMap map_q,
                                                                    const __grid_constant__ CUtensorMap map_k,
                                                                    const __grid_constant__ CUtensorMap map_v) {
@@ -136,48 +145,52 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
     volatile int* s_abort = reinterpret_cast<volatile int*>(smem + TcSmem::misc + 4);
     auto bar = [&](int which, int idx = 0) { return bar0 + uint32_t(which + idx) * 8; };
 
-    const int b = blockIdx.z, h = blockIdx.y;
-    const int qt = int(gridDim.x) - 1 - int(blockIdx.x);    // longest rows first
+    const int b = blockIdx.z;
+    const int xb = int(gridDim.x) - 1 - int(blockIdx.x);    // longest rows first
     int lq, lk, q0 = 0;
-    int64_t q_base;
     if (PAGED) {
         q0 = p.cu_q[b];
         lq = p.cu_q[b + 1] - q0;
         lk = p.cu_k[b + 1] - p.cu_k[b];
-        q_base = int64_t(q0) * p.q_row_stride + int64_t(h) * p.q_head_stride;
     } else {
         lq = lk = p.seq_len;
-        q_base = int64_t(b) * p.q_batch_stride + int64_t(h) * p.q_head_stride;
     }
-    if (qt * kTcRows >= lq) return;                          // whole CTA leaves before any barrier or TMEM use
     const int shift = lk - lq;
-    const int last_row = min(lq, qt * kTcRows + kTcRows) - 1;
-    const int n_kt = (shift + last_row) / kTcKeys + 1;
-    const int kvh = h / p.group;
+    TcTile tile[kTcQTiles];
+#pragma unroll
+    for (int i = 0; i < kTcQTiles; ++i) {
+        tile[i].head = pair_heads ? int(blockIdx.y) * 2 + i : int(blockIdx.y);
+        tile[i].row0 = pair_heads ? xb * kTcRows : (xb * kTcQTiles + i) * kTcRows;
+        tile[i].lq_left = lq - tile[i].row0;
+        tile[i].n_kt = tile[i].lq_left > 0 ? (shift + min(lq, tile[i].row0 + kTcRows) - 1) / kTcKeys + 1 : 0;
+    }
+    if (tile[0].n_kt == 0) return;                           // whole CTA leaves before any barrier or TMEM use
+    const int n_max = max(tile[0].n_kt, tile[1].n_kt);
+    const int kvh = tile[0].head / p.group;                  // both tiles read the same kv head
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
         mbar_init(bar(Q_FULL), 1);
-        for (int i = 0; i < kTcStages; ++i) {
+        for (int i = 0; i < kTcKStages; ++i) {
             mbar_init(bar(K_FULL, i), 1);
             mbar_init(bar(K_EMPTY, i), 1);
+        }
+        for (int i = 0; i < kTcVStages; ++i) {
             mbar_init(bar(V_FULL, i), 1);
             mbar_init(bar(V_EMPTY, i), 1);
         }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < kTcQTiles; ++i) {
             mbar_init(bar(S_FULL, i), 1);
-            mbar_init(bar(S_EMPTY, i), kTcSoftmaxWarps * 32);
-            mbar_init(bar(P_FULL, i), kTcSoftmaxWarps * 32);
-            mbar_init(bar(P_EMPTY, i), 1);
+            mbar_init(bar(P_FULL, i), 128);
+            mbar_init(bar(PV_DONE, i), 1);
         }
-        mbar_init(bar(PV_DONE), 1);
         mbar_init(bar(DRAIN), 1);
         *s_abort = 0;
         fence_mbar_init();
         fence_proxy_async();
     }
     if (warp == kTcMmaWarp) {
-        // all 512 columns: S0, S1, O, P0, P1 (one CTA per SM by shared-memory use)
+        // all 512 columns (one CTA per SM by shared-memory use)
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(base + uint32_t(TcSmem::misc)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -194,11 +207,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
             tma_prefetch_desc(&map_q);
             tma_prefetch_desc(&map_k);
             tma_prefetch_desc(&map_v);
-            mbar_expect_tx(bar(Q_FULL), kTcTile);
-            for (int half = 0; half < 2; ++half) {
-                if (PAGED) tma_load_3d(base + TcSmem::q + half * kTcHalf, &map_q, bar(Q_FULL), half * 64, h, q0 + qt * kTcRows);
-                else tma_load_3d(base + TcSmem::q + half * kTcHalf, &map_q, bar(Q_FULL), half * 64, qt * kTcRows, b * p.n_q_heads + h);
-            }
+            const int n_q = tile[1].n_kt > 0 ? 2 : 1;
+            mbar_expect_tx(bar(Q_FULL), n_q * kTcTile);
+            for (int i = 0; i < n_q; ++i)
+                for (int half = 0; half < 2; ++half) {
+                    const uint32_t dst = base + TcSmem::q + i * kTcTile + half * kTcHalf;
+                    if (PAGED) tma_load_3d(dst, &map_q, bar(Q_FULL), half * 64, tile[i].head, q0 + tile[i].row0);
+                    else tma_load_3d(dst, &map_q, bar(Q_FULL), half * 64, tile[i].row0, b * p.n_q_heads + tile[i].head);
+                }
             auto load_tile = [&](const CUtensorMap* map, uint32_t dst, uint32_t full, int j) {
                 int c1, c2;
                 if (PAGED) {
@@ -216,58 +232,62 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
             };
             int k_issued = 0, v_issued = 0;
             // order K0, K1, V0, K2, V1, ...: K of the next tile is needed before V of this one
-            for (int j = 0; j <= n_kt && ok; ++j) {
-                if (j < n_kt) {
-                    if (tc_wait(bar(K_EMPTY, j % kTcStages), ((j / kTcStages) & 1) ^ 1, s_abort)) {
-                        load_tile(&map_k, base + TcSmem::k + (j % kTcStages) * kTcTile, bar(K_FULL, j % kTcStages), j);
+            for (int j = 0; j <= n_max && ok; ++j) {
+                if (j < n_max) {
+                    if (tc_wait(bar(K_EMPTY, j % kTcKStages), ((j / kTcKStages) & 1) ^ 1, s_abort)) {
+                        load_tile(&map_k, base + TcSmem::k + (j % kTcKStages) * kTcTile, bar(K_FULL, j % kTcKStages), j);
                         ++k_issued;
                     } else ok = false;
                 }
                 if (j >= 1 && ok) {
                     const int jv = j - 1;
-                    if (tc_wait(bar(V_EMPTY, jv % kTcStages), ((jv / kTcStages) & 1) ^ 1, s_abort)) {
-                        load_tile(&map_v, base + TcSmem::v + (jv % kTcStages) * kTcTile, bar(V_FULL, jv % kTcStages), jv);
+                    if (tc_wait(bar(V_EMPTY, jv % kTcVStages), ((jv / kTcVStages) & 1) ^ 1, s_abort)) {
+                        load_tile(&map_v, base + TcSmem::v + (jv % kTcVStages) * kTcTile, bar(V_FULL, jv % kTcVStages), jv);
                         ++v_issued;
                     } else ok = false;
                 }
             }
             // never leave with a copy in flight: wait (bounded) for everything that was armed
             mbar_wait(bar(Q_FULL), 0);
-            for (int j = max(0, k_issued - kTcStages); j < k_issued; ++j) mbar_wait(bar(K_FULL, j % kTcStages), (j / kTcStages) & 1);
-            for (int j = max(0, v_issued - kTcStages); j < v_issued; ++j) mbar_wait(bar(V_FULL, j % kTcStages), (j / kTcStages) & 1);
+            for (int j = max(0, k_issued - kTcKStages); j < k_issued; ++j) mbar_wait(bar(K_FULL, j % kTcKStages), (j / kTcKStages) & 1);
+            for (int j = max(0, v_issued - kTcVStages); j < v_issued; ++j) mbar_wait(bar(V_FULL, j % kTcVStages), (j / kTcVStages) & 1);
         }
     } else if (warp == kTcMmaWarp) {
         // ================================================================= MMA issue
+        // Order on the tensor core: S_0(0) S_1(0), then per key tile j: PV_0(j) S_0(j+1) PV_1(j) S_1(j+1).
+        // tcgen05 operations of one thread execute in order, which is what lets P reuse columns
+        // of S (S_i(j+1) is behind PV_i(j)) and makes the final commit cover everything.
         constexpr uint32_t idesc_s = tc_idesc(false), idesc_pv = tc_idesc(true);
-        const uint32_t q_addr = base + TcSmem::q;
-        auto issue_s = [&](int j) {      // S[j&1] = Q K_j^T
-            if (!tc_wait(bar(K_FULL, j % kTcStages), (j / kTcStages) & 1, s_abort)) return false;
-            if (!tc_wait(bar(S_EMPTY, j & 1), ((j >> 1) & 1) ^ 1, s_abort)) return false;
-            tc_fence_after();
+        auto issue_s = [&](int i, int j) {       // S_i = Q_i K_j^T  (K_FULL of tile j already awaited)
             if (lane == 0) {
-                const uint32_t k_addr = base + TcSmem::k + (j % kTcStages) * kTcTile;
+                const uint32_t q_addr = base + TcSmem::q + i * kTcTile;
+                const uint32_t k_addr = base + TcSmem::k + (j % kTcKStages) * kTcTile;
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
                     const uint32_t off = (kk >> 2) * kTcHalf + (kk & 3) * 32;
-                    tc_mma(tmem + (j & 1) * 128, tc_desc(q_addr + off, 16), tc_desc(k_addr + off, 16), idesc_s, kk > 0);
+                    tc_mma(tmem + i * 128, tc_desc(q_addr + off, 16), tc_desc(k_addr + off, 16), idesc_s, kk > 0);
                 }
-                tc_commit(bar(S_FULL, j & 1));
-                tc_commit(bar(K_EMPTY, j % kTcStages));
+                tc_commit(bar(S_FULL, i));
             }
             __syncwarp();
-            return true;
         };
         if (!tc_wait(bar(Q_FULL), 0, s_abort)) ok = false;
-        if (ok) ok = issue_s(0);
-        for (int j = 0; j < n_kt && ok; ++j) {
-            if (j + 1 < n_kt) ok = issue_s(j + 1);
-            if (ok && !tc_wait(bar(V_FULL, j % kTcStages), (j / kTcStages) & 1, s_abort)) ok = false;
-            if (ok && PAGED && j == n_kt - 1) {
+        if (ok && !tc_wait(bar(K_FULL, 0), 0, s_abort)) ok = false;
+        if (ok) {
+            tc_fence_after();
+            for (int i = 0; i < kTcQTiles; ++i)
+                if (tile[i].n_kt > 0) issue_s(i, 0);
+            if (lane == 0) tc_commit(bar(K_EMPTY, 0));
+            __syncwarp();
+        }
+        for (int j = 0; j < n_max && ok; ++j) {
+            if (!tc_wait(bar(V_FULL, j % kTcVStages), (j / kTcVStages) & 1, s_abort)) { ok = false; break; }
+            if (PAGED && j == n_max - 1) {
                 // keys past the end of the context: P is 0 there, but 0 * (stale bytes) must not
                 // produce NaN, so clear those V rows before the tensor core reads them
                 const int valid = lk - j * kTcKeys;
                 if (valid < kTcKeys) {
-                    uint8_t* vt = smem + TcSmem::v + (j % kTcStages) * kTcTile;
+                    uint8_t* vt = smem + TcSmem::v + (j % kTcVStages) * kTcTile;
                     for (int i = valid * 8 + lane; i < kTcKeys * 8; i += 32) {
                         *reinterpret_cast<uint4*>(vt + i * 16) = make_uint4(0, 0, 0, 0);
                         *reinterpret_cast<uint4*>(vt + kTcHalf + i * 16) = make_uint4(0, 0, 0, 0);
@@ -276,22 +296,27 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
                     __syncwarp();
                 }
             }
-            if (ok && !tc_wait(bar(P_FULL, j & 1), (j >> 1) & 1, s_abort)) ok = false;
-            if (!ok) break;
-            tc_fence_after();
-            if (lane == 0) {
-                const uint32_t v_addr = base + TcSmem::v + (j % kTcStages) * kTcTile;
-                const uint32_t pj_tmem = tmem + kTmemP + (j & 1) * 64;
+            const bool next = j + 1 < n_max;
+            if (next && !tc_wait(bar(K_FULL, (j + 1) % kTcKStages), ((j + 1) / kTcKStages) & 1, s_abort)) { ok = false; break; }
+            for (int i = 0; i < kTcQTiles && ok; ++i) {
+                if (j >= tile[i].n_kt) continue;
+                if (!tc_wait(bar(P_FULL, i), j & 1, s_abort)) { ok = false; break; }
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t v_addr = base + TcSmem::v + (j % kTcVStages) * kTcTile;
+                    const uint32_t p_tmem = tmem + i * 128 + kTmemPinS;
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    const uint32_t b_off = ks * 16 * 128;                         // 16 key rows of V
-                    // 16 keys of P = 8 packed columns
-                    tc_mma_ts(tmem + kTmemO, pj_tmem + ks * 8, tc_desc(v_addr + b_off, kTcHalf), idesc_pv,
-                              (j > 0 || ks > 0) ? 1u : 0u);
+                    for (int ks = 0; ks < 8; ++ks)     // 16 keys: 8 packed columns of P, 16 rows of V
+                        tc_mma_ts(tmem + kTmemO + i * 128, p_tmem + ks * 8, tc_desc(v_addr + ks * 16 * 128, kTcHalf), idesc_pv,
+                                  (j > 0 || ks > 0) ? 1u : 0u);
+                    tc_commit(bar(PV_DONE, i));
                 }
-                tc_commit(bar(PV_DONE));
-                tc_commit(bar(V_EMPTY, j % kTcStages));
-                tc_commit(bar(P_EMPTY, j & 1));
+                __syncwarp();
+                if (j + 1 < tile[i].n_kt) issue_s(i, j + 1);
+            }
+            if (ok && lane == 0) {
+                tc_commit(bar(V_EMPTY, j % kTcVStages));
+                if (next) tc_commit(bar(K_EMPTY, (j + 1) % kTcKStages));
             }
             __syncwarp();
         }
@@ -300,53 +325,51 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
         __syncwarp();
         mbar_wait(bar(DRAIN), 0);
     } else {
-        // ================================================================= softmax, two threads per row
+        // ================================================================= softmax, one row per thread
+        const int g = warp >> 2;                                   // query tile of this warpgroup
         const int r = (warp & 3) * 32 + lane;                      // row in the tile == TMEM lane
-        const int ch = warp >> 2;                                  // column half: keys / dims [64 ch, 64 ch + 64)
         const uint32_t lane_sel = uint32_t((warp & 3) * 32) << 16;
-        const int row = qt * kTcRows + r;
+        const int n_kt = tile[g].n_kt;
+        const int row = tile[g].row0 + r;
         const int pos = shift + row;
-        const int cta_first_pos = shift + qt * kTcRows;
-        const uint32_t o_addr = tmem + lane_sel + kTmemO + ch * 64;
-        __nv_bfloat16* s_xchg = reinterpret_cast<__nv_bfloat16*>(smem + TcSmem::xchg);
-        float m_ref = -INFINITY, l_run = 0.f;                      // reference maximum (log2 domain), partial row sum
-        auto softmax_bar = [] { asm volatile("bar.sync 2, 256;" ::: "memory"); };
+        const int tile_first_pos = shift + tile[g].row0;
+        const uint32_t s_addr = tmem + lane_sel + g * 128;
+        const uint32_t o_addr = tmem + lane_sel + kTmemO + g * 128;
+        float m_ref = -INFINITY, l_run = 0.f;                      // reference maximum (log2 domain), row sum
 
-        // Every thread executes exactly one softmax_bar() per tile, whatever happened to its
-        // waits: the named barrier is not bounded, so nobody may skip it.
         for (int j = 0; j < n_kt; ++j) {
-            if (ok && !tc_wait(bar(S_FULL, j & 1), (j >> 1) & 1, s_abort)) ok = false;
-            uint32_t sv[64];
-            float mx = -INFINITY;
-            const int key0 = j * kTcKeys + ch * 64;
-            const int limit = pos - key0;                            // local columns <= limit are visible
-            if (ok) {
-                tc_fence_after();
-                const uint32_t s_addr = tmem + lane_sel + (j & 1) * 128 + ch * 64;
-                tc_ld32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
-                tc_ld32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
+            if (ok && !tc_wait(bar(S_FULL, g), j & 1, s_abort)) ok = false;
+            if (!ok) continue;
+            tc_fence_after();
+            const int limit = pos - j * kTcKeys;                     // columns <= limit are visible
+            const bool masked = j * kTcKeys + kTcKeys - 1 > tile_first_pos;
+            // row maximum: first half of the row (dropped again), then the second half, which stays
+            // in registers
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+            uint32_t sb[64];
+            {
+                uint32_t sa[64];
+                tc_ld32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&sa[0]));
+                tc_ld32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&sa[32]));
+                tc_ld32(s_addr + 64, *reinterpret_cast<uint32_t(*)[32]>(&sb[0]));
+                tc_ld32(s_addr + 96, *reinterpret_cast<uint32_t(*)[32]>(&sb[32]));
                 tc_wait_ld();
-                tc_fence_before();
-                mbar_arrive(bar(S_EMPTY, j & 1));                    // S_{j+2} may overwrite this buffer
-                if (j * kTcKeys + kTcKeys - 1 > cta_first_pos) {     // tile touches the diagonal or the context end
+                if (masked) {
 #pragma unroll
                     for (int i = 0; i < 64; ++i) {
-                        if (i > limit) sv[i] = 0xff800000u;          // -inf
-                        mx = fmaxf(mx, __uint_as_float(sv[i]));
+                        if (i > limit) sa[i] = 0xff800000u;          // -inf
+                        if (i + 64 > limit) sb[i] = 0xff800000u;
                     }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
                 }
-                // The two threads of a row must agree on the maximum bit for bit: both use the
-                // two halves' maxima rounded up to bf16 (any upper-ish reference is valid).
-                const __nv_bfloat16 mxr = __float2bfloat16_ru(mx);
-                s_xchg[((j & 1) * 2 + ch) * 128 + r] = mxr;
-                mx = __bfloat162float(mxr);
+#pragma unroll
+                for (int i = 0; i < 64; i += 4) {
+                    mx0 = fmaxf(mx0, fmaxf(__uint_as_float(sa[i]), __uint_as_float(sa[i + 1])));
+                    mx1 = fmaxf(mx1, fmaxf(__uint_as_float(sa[i + 2]), __uint_as_float(sa[i + 3])));
+                    mx2 = fmaxf(mx2, fmaxf(__uint_as_float(sb[i]), __uint_as_float(sb[i + 1])));
+                    mx3 = fmaxf(mx3, fmaxf(__uint_as_float(sb[i + 2]), __uint_as_float(sb[i + 3])));
+                }
             }
-            softmax_bar();
-            if (!ok) continue;
-            mx = fmaxf(mx, __bfloat162float(s_xchg[((j & 1) * 2 + (ch ^ 1)) * 128 + r])) * p.scale_log2;
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
             // move the reference only when the maximum outgrew it by more than 2^kLazyLog2
             const bool move = mx > m_ref + kLazyLog2 || (m_ref == -INFINITY && mx > -INFINITY);
             if (__any_sync(0xffffffffu, move)) {
@@ -354,10 +377,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
                 const float alpha = m_ref == -INFINITY ? 0.f : fast_exp2(m_ref - m_new);
                 if (j > 0) {
                     // O holds tiles < j once P V_{j-1} has retired; P V_j cannot start before P_FULL below
-                    if (!tc_wait(bar(PV_DONE), (j - 1) & 1, s_abort)) { ok = false; continue; }
+                    if (!tc_wait(bar(PV_DONE, g), (j - 1) & 1, s_abort)) { ok = false; continue; }
                     tc_fence_after();
 #pragma unroll
-                    for (int c = 0; c < 2; ++c) {
+                    for (int c = 0; c < 4; ++c) {
                         uint32_t v[32];
                         tc_ld32(o_addr + c * 32, v);
                         tc_wait_ld();
@@ -371,42 +394,61 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
                 m_ref = m_new;
             }
             const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-
-            if (!tc_wait(bar(P_EMPTY, j & 1), ((j >> 1) & 1) ^ 1, s_abort)) { ok = false; continue; }
-            uint32_t pk[32];                                         // this thread's 64 keys, two per column
-            float rs0 = 0.f, rs1 = 0.f;
+            // P = exp2(S * c - m) as packed bf16 over columns 64-127 of S.  Keys 64-127 come from
+            // registers and land on columns 96-127; then columns 0-63 of S (untouched by P) are
+            // read again and their P lands on columns 64-95, whose S values are already consumed.
+            float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
+            {
+                uint32_t pk[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                const float e0 = fast_exp2(fmaf(__uint_as_float(sv[2 * i]), p.scale_log2, -m_use));
-                const float e1 = fast_exp2(fmaf(__uint_as_float(sv[2 * i + 1]), p.scale_log2, -m_use));
-                rs0 += e0;
-                rs1 += e1;
-                pk[i] = pack_bf16(e0, e1);
+                for (int i = 0; i < 32; ++i) {
+                    const float e0 = fast_exp2(fmaf(__uint_as_float(sb[2 * i]), p.scale_log2, -m_use));
+                    const float e1 = fast_exp2(fmaf(__uint_as_float(sb[2 * i + 1]), p.scale_log2, -m_use));
+                    rs2 += e0;
+                    rs3 += e1;
+                    pk[i] = pack_bf16(e0, e1);
+                }
+                tc_st32(s_addr + kTmemPinS + 32, pk);
             }
-            l_run += rs0 + rs1;
-            tc_st32(tmem + lane_sel + kTmemP + (j & 1) * 64 + ch * 32, pk);
+            {
+                uint32_t sa[64], pk[32];
+                tc_ld32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&sa[0]));
+                tc_ld32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&sa[32]));
+                tc_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float e0 = fast_exp2(fmaf(__uint_as_float(sa[2 * i]), p.scale_log2, -m_use));
+                    float e1 = fast_exp2(fmaf(__uint_as_float(sa[2 * i + 1]), p.scale_log2, -m_use));
+                    if (masked) {
+                        if (2 * i > limit) e0 = 0.f;
+                        if (2 * i + 1 > limit) e1 = 0.f;
+                    }
+                    rs0 += e0;
+                    rs1 += e1;
+                    pk[i] = pack_bf16(e0, e1);
+                }
+                tc_st32(s_addr + kTmemPinS, pk);
+            }
+            l_run += (rs0 + rs1) + (rs2 + rs3);
             tc_wait_st();
             tc_fence_before();
-            mbar_arrive(bar(P_FULL, j & 1));
+            mbar_arrive(bar(P_FULL, g));
         }
         // O is complete once the last P V has retired
-        if (ok && !tc_wait(bar(PV_DONE), (n_kt - 1) & 1, s_abort)) ok = false;
-        // row sum = the two halves' partial sums (same reference maximum in both); every
-        // tensor-core read of the tiles has retired, so the Q tile's memory is free for the exchange
-        float* s_sum = reinterpret_cast<float*>(smem + TcSmem::q);
-        s_sum[ch * 128 + r] = l_run;
-        softmax_bar();
-        l_run += s_sum[(ch ^ 1) * 128 + r];
-        if (ok) {
+        if (n_kt > 0 && ok && !tc_wait(bar(PV_DONE, g), (n_kt - 1) & 1, s_abort)) ok = false;
+        if (n_kt > 0 && ok) {
             tc_fence_after();
             const float inv = 1.f / l_run;
-            __nv_bfloat16* dst = p.out + q_base + int64_t(row) * p.q_row_stride + ch * 64;
+            int64_t q_base;
+            if (PAGED) q_base = int64_t(q0) * p.q_row_stride + int64_t(tile[g].head) * p.q_head_stride;
+            else q_base = int64_t(b) * p.q_batch_stride + int64_t(tile[g].head) * p.q_head_stride;
+            __nv_bfloat16* dst = p.out + q_base + int64_t(row) * p.q_row_stride;
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
+            for (int c = 0; c < 4; ++c) {
                 uint32_t v[32];
                 tc_ld32(o_addr + c * 32, v);
                 tc_wait_ld();
-                if (row < lq) {
+                if (r < tile[g].lq_left) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
                         uint4 w;
@@ -435,14 +477,18 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
 int launch_prefill_tc(bool paged, const PrefillParams& p, const CUtensorMap& mq, const CUtensorMap& mk,
                       const CUtensorMap& mv, int max_q, int batch, cudaStream_t st) {
     if (max_q <= 0 || batch <= 0) return INFER_OK;
-    dim3 grid((max_q + kTcRows - 1) / kTcRows, p.n_q_heads, batch);
+    // an even group lets the two query tiles of a CTA be the two heads of a GQA pair (same rows,
+    // same kv head); otherwise they are two consecutive row blocks of one head
+    const int pair_heads = p.group % 2 == 0 ? 1 : 0;
+    dim3 grid = pair_heads ? dim3((max_q + kTcRows - 1) / kTcRows, p.n_q_heads / 2, batch)
+                           : dim3((max_q + kTcQTiles * kTcRows - 1) / (kTcQTiles * kTcRows), p.n_q_heads, batch);
     const int smem = TcSmem::total + 1024;
     if (paged) {
         IB_CUDA(cudaFuncSetAttribute(prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        prefill_tc_kernel<true><<<grid, kTcThreads, smem, st>>>(p, mq, mk, mv);
+        prefill_tc_kernel<true><<<grid, kTcThreads, smem, st>>>(p, pair_heads, mq, mk, mv);
     } else {
         IB_CUDA(cudaFuncSetAttribute(prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        prefill_tc_kernel<false><<<grid, kTcThreads, smem, st>>>(p, mq, mk, mv);
+        prefill_tc_kernel<false><<<grid, kTcThreads, smem, st>>>(p, pair_heads, mq, mk, mv);
     }
     return check_launch();
 }
