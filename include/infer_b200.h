@@ -73,6 +73,24 @@ INFER_API int infer_kv_append(const infer_kv_pool_t* pool, const void* k, const 
                     int64_t n_tokens, void* workspace, size_t workspace_bytes, void* stream);
 INFER_API size_t infer_kv_append_workspace_bytes(const infer_kv_pool_t* pool);
 
+/* Fused per-head RMSNorm + rotary embedding + KV append: one pass over the fused qkv rows
+ * instead of the four the reference model makes before attention (q_norm and k_norm,
+ * infer/models/Qwen3.py:116-121 with infer/ops/norm.py:63-73; the in-place rotary embedding of
+ * q and k, infer/models/Qwen3.py:127 with src/operators/rope/rope.cu:109-133, GPT-NeoX
+ * pairing, rot_dim = 128; store_kvcache, infer/ops/attention.py:109).  q, k, v: bf16
+ * [n_tokens, heads, 128] with free row strides (ELEMENTS); q_out bf16 [n_tokens, n_q_heads, 128]
+ * (may be q itself); weights bf16 [128]; positions int64 [n_tokens]; cos_sin_cache bf16
+ * [max_position, 128] = 64 cosines then 64 sines per position, as the reference builds it
+ * (infer/ops/rope.py:108-115).  k is written normalised and rotated to its slot, v is copied;
+ * bf16 pools only.  Rounding follows the reference step by step (fp32 variance and scaling,
+ * bf16 before the weight multiply, bf16 products and sum in the rotation). */
+INFER_API int infer_qk_norm_rope_append(const infer_kv_pool_t* pool, void* q_out, int64_t q_out_row_stride,
+                              const void* q, const void* k, const void* v, int64_t q_row_stride,
+                              int64_t k_row_stride, int64_t v_row_stride, const void* q_norm_weight,
+                              const void* k_norm_weight, float eps, const int64_t* positions,
+                              const void* cos_sin_cache, int64_t max_position,
+                              const int32_t* slot_mapping, int64_t n_tokens, int n_q_heads, void* stream);
+
 /* Paged decode attention.  Replaces the decode branch of Attention.forward
  * (flash_attn_with_kvcache(q[:,None], k_cache, v_cache, cache_seqlens, block_table,
  * softmax_scale, causal=True), infer/ops/attention.py:117-121) and fills the empty

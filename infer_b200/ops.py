@@ -123,6 +123,39 @@ def store_kvcache(key, value, k_cache, v_cache, slot_mapping, k_scale=None, v_sc
     _lib.check(rc, "store_kvcache")
 
 
+def qk_norm_rope_append(q, k, v, q_norm_weight, k_norm_weight, eps, positions, cos_sin_cache, k_cache, v_cache,
+                        slot_mapping, q_out=None):
+    """Fused per-head RMSNorm (q, k) + NeoX rotary embedding (q, k) + KV append, one kernel.
+
+    Replaces, for the attention block of the reference model (infer/models/Qwen3.py:112-131):
+    ``q = q_norm(q); k = k_norm(k); rotary_emb(positions, q, k); store_kvcache(k, v, ...)``.
+    q, k, v are ``[T, H, 128]`` views (column slices of the fused qkv output are fine);
+    returns the normalised, rotated q as a contiguous ``[T, Hq, 128]`` tensor (or writes it into
+    ``q_out``, which may be ``q``)."""
+    t, hq, d = q.shape
+    for name, x in (("q", q), ("k", k), ("v", v)):
+        if x.dtype != torch.bfloat16 or x.stride(-1) != 1 or x.stride(1) != d:
+            raise RuntimeError(f"qk_norm_rope_append: {name} must be bf16 [T, H, 128] with contiguous heads")
+    if positions.dtype != torch.int64 or slot_mapping.dtype != torch.int32:
+        raise RuntimeError("qk_norm_rope_append: positions must be int64 and slot_mapping int32")
+    if cos_sin_cache.dtype != torch.bfloat16 or cos_sin_cache.shape[-1] != d or not cos_sin_cache.is_contiguous():
+        raise RuntimeError("qk_norm_rope_append: cos_sin_cache must be contiguous bf16 [max_position, 128]")
+    if q_out is None:
+        q_out = torch.empty(t, hq, d, dtype=q.dtype, device=q.device)
+    if t == 0:
+        return q_out
+    pool = pool_of(k_cache, v_cache)
+    pitch = lambda x: x.stride(0) if t > 1 else x.shape[1] * d
+    lib = _lib.load()
+    with torch.cuda.device(pool.device):
+        rc = lib.infer_qk_norm_rope_append(pool.handle, _ptr(q_out), pitch(q_out), _ptr(q), _ptr(k), _ptr(v), pitch(q),
+                                           pitch(k), pitch(v), _ptr(q_norm_weight), _ptr(k_norm_weight), float(eps),
+                                           _ptr(positions), _ptr(cos_sin_cache), cos_sin_cache.shape[0],
+                                           _ptr(slot_mapping), t, hq, _stream())
+    _lib.check(rc, "qk_norm_rope_append")
+    return q_out
+
+
 # --------------------------------------------------------------------------- decode
 def paged_attn_decode(q, k_cache, v_cache, cache_seqlens, block_table, softmax_scale,
                       out=None, k_scale=None, v_scale=None):

@@ -90,6 +90,39 @@ def store_kvcache_fp8(key, value, k_cache, v_cache, k_scale, v_scale, slot_mappi
         bytes_.view(-1, hkv, d).view(torch.uint8).index_copy_(0, slots, _to_e4m3(q).view(torch.uint8))
 
 
+# --------------------------------------------------------------------------- fused pre-attention step
+def rms_norm_heads(x, weight, eps):
+    """Per-head RMSNorm as the reference computes it (RMSNorm.rms_forward,
+    infer/ops/norm.py:63-73): fp32 variance and scaling, round to the input dtype, then a
+    multiply by the weight in that dtype."""
+    dt = x.dtype
+    xf = x.to(torch.float32)
+    var = xf.pow(2).mean(dim=-1, keepdim=True)
+    xf = xf * torch.rsqrt(var + eps)
+    return xf.to(dt) * weight
+
+
+def rope_neox(x, cos, sin):
+    """GPT-NeoX rotary embedding in the tensor's own dtype, the arithmetic of
+    _apply_rotary_emb_torch (infer/ops/rope.py:46-64) and of the CUDA op
+    (src/operators/rope/rope.cu:43-66): x [T, H, d], cos/sin [T, d/2]."""
+    cos = cos.unsqueeze(-2).to(x.dtype)
+    sin = sin.unsqueeze(-2).to(x.dtype)
+    x1, x2 = torch.chunk(x, 2, dim=-1)
+    return torch.cat((x1 * cos - x2 * sin, x2 * cos + x1 * sin), dim=-1)
+
+
+def qk_norm_rope_append(q, k, v, q_weight, k_weight, eps, positions, cos_sin_cache, k_cache, v_cache, slot_mapping):
+    """What the reference model does between the qkv projection and attention
+    (infer/models/Qwen3.py:112-131): norm q and k per head, rotate both in place, store k and v.
+    Returns the rotated q; the pools are updated in place."""
+    cos, sin = cos_sin_cache.index_select(0, positions).chunk(2, dim=-1)
+    qn = rope_neox(rms_norm_heads(q, q_weight, eps), cos, sin)
+    kn = rope_neox(rms_norm_heads(k, k_weight, eps), cos, sin)
+    store_kvcache(kn, v, k_cache, v_cache, slot_mapping)
+    return qn
+
+
 # --------------------------------------------------------------------------- gather
 def gather_tokens(cache, table_row, length, scale=None):
     """Rows [0, length) of one sequence, found by walking its page list.

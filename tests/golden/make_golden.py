@@ -178,10 +178,41 @@ def golden_attention():
     return out
 
 
+def golden_norm_rope():
+    """Per-head RMSNorm followed by the NeoX rotary embedding, computed by the reference's own
+    Python code: RMSNorm.rms_forward (infer/ops/norm.py:63-73, the function under its
+    torch.compile decorator, run eagerly) and _apply_rotary_emb_torch (infer/ops/rope.py:46-64).
+    The cos/sin cache is an input: it is built here with the reference's formula
+    (infer/ops/rope.py:100-115) on the CPU."""
+    from infer.ops.norm import RMSNorm
+    from infer.ops.rope import _apply_rotary_emb_torch
+    g = torch.Generator().manual_seed(31337)
+    t, h, d = 7, 3, 128
+    x = (torch.randn(t, h, d, generator=g) * 1.7).bfloat16()
+    weight = (1.0 + 0.1 * torch.randn(d, generator=g)).bfloat16()
+    positions = torch.tensor([0, 1, 2, 100, 255, 257, 1023], dtype=torch.int64)
+    inv_freq = 1.0 / (100000.0 ** (torch.arange(0, d, 2, dtype=torch.bfloat16) / d))
+    freqs = torch.einsum("i,j -> ij", torch.arange(1024, dtype=torch.bfloat16), inv_freq)
+    cache = torch.cat((freqs.cos(), freqs.sin()), dim=-1)
+    norm = RMSNorm(d)
+    norm.weight.data.copy_(weight)
+    eager = getattr(RMSNorm.rms_forward, "_torchdynamo_orig_callable", None)
+    assert eager is not None, "cannot reach the undecorated rms_forward"
+    with torch.no_grad():
+        xn = eager(norm, x.clone())
+        cos, sin = cache.index_select(0, positions).chunk(2, dim=-1)
+        out = _apply_rotary_emb_torch(xn, cos, sin, True)
+    np.save(HERE / "norm_rope_out.npy", bits(out))
+    np.save(HERE / "norm_only_out.npy", bits(xn))
+    return {"seed": 31337, "t": t, "h": h, "positions": positions.tolist(), "theta": 100000.0, "max_position": 1024,
+            "eps": 1e-6, "inputs_digest": digest(torch.cat([x.flatten(), weight])), "cache_digest": digest(cache)}
+
+
 def main():
     root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
     BlockManager, ModelRunner, Sequence, SamplingParams, store_kvcache, get_context = import_reference(root)
     result = {
+        "norm_rope": golden_norm_rope(),
         "allocator": golden_allocator(BlockManager, ModelRunner, Sequence, SamplingParams, get_context),
         "append": golden_append(store_kvcache),
         "attention": golden_attention(),

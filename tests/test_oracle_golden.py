@@ -210,3 +210,46 @@ def test_fp8_append_rule():
     k3 = (torch.randn(1, hkv, 128, generator=gen) * 0.1).bfloat16()
     oracle.store_kvcache_fp8(k3, k3, kc, vc, ks, vs, torch.tensor([11], dtype=torch.int32))
     assert torch.equal(s_before, ks) and torch.equal(before[0, :11], kc[0, :11])
+
+
+def _norm_rope_inputs(g):
+    gen = torch.Generator().manual_seed(g["seed"])
+    t, h, d = g["t"], g["h"], 128
+    x = (torch.randn(t, h, d, generator=gen) * 1.7).bfloat16()
+    weight = (1.0 + 0.1 * torch.randn(d, generator=gen)).bfloat16()
+    inv_freq = 1.0 / (g["theta"] ** (torch.arange(0, d, 2, dtype=torch.bfloat16) / d))
+    freqs = torch.einsum("i,j -> ij", torch.arange(g["max_position"], dtype=torch.bfloat16), inv_freq)
+    cache = torch.cat((freqs.cos(), freqs.sin()), dim=-1)
+    assert digest(torch.cat([x.flatten(), weight])) == g["inputs_digest"]
+    assert digest(cache) == g["cache_digest"]
+    return x, weight, cache, torch.tensor(g["positions"], dtype=torch.int64)
+
+
+def test_norm_and_rope_match_reference_functions(golden):
+    """rms_norm_heads and rope_neox against what the reference's RMSNorm.rms_forward and
+    _apply_rotary_emb_torch produced on the same bits: bit-exact."""
+    g = golden["norm_rope"]
+    x, weight, cache, positions = _norm_rope_inputs(g)
+    want_norm = torch.from_numpy(np.load(GOLD / "norm_only_out.npy")).view(torch.bfloat16)
+    want = torch.from_numpy(np.load(GOLD / "norm_rope_out.npy")).view(torch.bfloat16)
+    xn = oracle.rms_norm_heads(x, weight, g["eps"])
+    assert torch.equal(xn.view(torch.int16), want_norm.view(torch.int16))
+    cos, sin = cache.index_select(0, positions).chunk(2, dim=-1)
+    got = oracle.rope_neox(xn, cos, sin)
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+
+
+def test_fused_oracle_equals_separate_steps(golden):
+    g = golden["norm_rope"]
+    x, weight, cache, positions = _norm_rope_inputs(g)
+    t, h = g["t"], g["h"]
+    q, k, v = x, x.flip(0)[:, :1].contiguous(), (x * 0.5)[:, :1].contiguous()
+    kc = torch.zeros(2, 256, 1, 128, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    slots = torch.tensor([5, 6, 300, -1, 8, 511, 0], dtype=torch.int32)
+    qn = oracle.qk_norm_rope_append(q, k, v, weight, weight, g["eps"], positions, cache, kc, vc, slots)
+    want = torch.from_numpy(np.load(GOLD / "norm_rope_out.npy")).view(torch.bfloat16)
+    assert torch.equal(qn.view(torch.int16), want.view(torch.int16))
+    keep = slots >= 0
+    assert torch.equal(vc.view(-1, 1, 128)[slots[keep].long()], v[keep])
+    assert int((kc.view(-1, 128).abs().sum(-1) > 0).sum()) == int(keep.sum())
