@@ -91,6 +91,16 @@ INFER_API int infer_qk_norm_rope_append(const infer_kv_pool_t* pool, void* q_out
                               const void* cos_sin_cache, int64_t max_position,
                               const int32_t* slot_mapping, int64_t n_tokens, int n_q_heads, void* stream);
 
+/* Advances the decode-step metadata on the device: every row with context_lens[b] > 0 grows by
+ * one token, slot_mapping[b] becomes the slot of that token (read off block_tables, -1 if the
+ * page is missing), positions[b] (optional) its position + position_base; rows with
+ * context_lens[b] <= 0 get slot -1.  Replaces the per-step host loops and uploads of
+ * ModelRunner.prepare_decode (infer/engine/model_runner.py:110-126), whose position value is
+ * len(seq), i.e. position_base = 1. */
+INFER_API int infer_decode_step_advance(int32_t* context_lens, int32_t* slot_mapping, int64_t* positions,
+                              const int32_t* block_tables, int64_t bt_stride, int batch,
+                              int block_size, int position_base, void* stream);
+
 /* Paged decode attention.  Replaces the decode branch of Attention.forward
  * (flash_attn_with_kvcache(q[:,None], k_cache, v_cache, cache_seqlens, block_table,
  * softmax_scale, causal=True), infer/ops/attention.py:117-121) and fills the empty

@@ -26,6 +26,7 @@ SIGNATURES = {
     "infer_kv_append_workspace_bytes": (_sz, [_vp]),
     "infer_qk_norm_rope_append": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _f32, _vp, _vp, _i64,
                                          _vp, _i64, _i32, _vp]),
+    "infer_decode_step_advance": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp]),
     "infer_paged_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _f32, _vp, _sz, _vp]),
     "infer_paged_decode_workspace_bytes": (_sz, [_vp, _i32, _i32]),
     "infer_paged_decode_noalloc": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _f32, _vp]),

@@ -106,3 +106,64 @@ def prepare_chunk(block_tables: list[list[int]], prefix_lens: list[int], chunk_l
                 max(chunk_lens), max(p + c for p, c in zip(prefix_lens, chunk_lens)),
                 _to(torch.tensor(slots, dtype=torch.int32), device),
                 None, _to(torch.tensor(rows, dtype=torch.int32), device))
+
+
+class DecodeState:
+    """Decode-step metadata kept on the device between steps.
+
+    ``prepare_decode`` rebuilds and uploads everything every step; this class uploads once and
+    then lets ``advance()`` (one small kernel) grow every live sequence by one token and compute
+    the new slots and positions from the block tables already on the device.  The host only
+    writes a block-table entry when a sequence enters a new page.  All tensors keep their
+    address, so they can be the static inputs of a captured decode graph
+    (infer/engine/model_runner.py:163-198 uses the same static-buffer scheme)."""
+
+    def __init__(self, max_batch: int, max_pages: int, block_size: int, device, position_base: int = 1):
+        self.block_size, self.position_base, self.device = block_size, position_base, torch.device(device)
+        self.context_lens = torch.zeros(max_batch, dtype=torch.int32, device=device)
+        self.slot_mapping = torch.full((max_batch,), -1, dtype=torch.int32, device=device)
+        self.positions = torch.zeros(max_batch, dtype=torch.int64, device=device)
+        self.block_tables = torch.full((max_batch, max_pages), -1, dtype=torch.int32, device=device)
+        self.host_lens = [0] * max_batch
+        self.host_pages = [0] * max_batch          # pages known to the device per row
+
+    def load(self, seqs: list[Sequence]):
+        """Full upload for a new batch composition; lengths are those BEFORE the next step's token."""
+        n, width = len(seqs), self.block_tables.shape[1]
+        if n > self.context_lens.numel() or any(len(s.block_table) > width for s in seqs):
+            raise ValueError("batch or page list exceeds the static buffers")
+        lens = [len(s) for s in seqs] + [0] * (self.context_lens.numel() - n)
+        rows = [s.block_table + [-1] * (width - len(s.block_table)) for s in seqs]
+        rows += [[-1] * width] * (self.context_lens.numel() - n)
+        self.context_lens.copy_(torch.tensor(lens, dtype=torch.int32), non_blocking=True)
+        self.block_tables.copy_(torch.tensor(rows, dtype=torch.int32), non_blocking=True)
+        self.host_lens = lens
+        self.host_pages = [len(s.block_table) for s in seqs] + [0] * (self.context_lens.numel() - n)
+
+    def publish_new_pages(self, seqs: list[Sequence]):
+        """After the allocator ran ``may_append`` for the coming step: upload only the
+        block-table entries that did not exist yet."""
+        for b, s in enumerate(seqs):
+            have = self.host_pages[b]
+            if len(s.block_table) > have:
+                new = torch.tensor(s.block_table[have:], dtype=torch.int32)
+                self.block_tables[b, have:len(s.block_table)].copy_(new, non_blocking=True)
+                self.host_pages[b] = len(s.block_table)
+
+    def advance(self):
+        """One kernel: context_lens += 1 for live rows, slot_mapping and positions follow."""
+        if self.device.type != "cuda":
+            raise RuntimeError("DecodeState.advance launches a CUDA kernel; the state must live on a GPU")
+        import ctypes as C
+        from . import _lib
+        lib = _lib.load()
+        p = lambda t: C.c_void_p(t.data_ptr())
+        with torch.cuda.device(self.device):
+            rc = lib.infer_decode_step_advance(p(self.context_lens), p(self.slot_mapping), p(self.positions),
+                                               p(self.block_tables), self.block_tables.stride(0),
+                                               self.context_lens.numel(), self.block_size, self.position_base,
+                                               C.c_void_p(torch.cuda.current_stream().cuda_stream))
+        _lib.check(rc, "decode_step_advance")
+        self.host_lens = [n + 1 if n > 0 else 0 for n in self.host_lens]
+        set_context(False, slot_mapping=self.slot_mapping, context_lens=self.context_lens,
+                    block_tables=self.block_tables)
