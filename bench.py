@@ -327,11 +327,32 @@ def main():
     h2d = sum(v.numel() * v.element_size() for v in src.values())
     d2h = out_host.numel() * out_host.element_size()
 
-    def e2e_step():
+    def e2e_body():
         stage.upload()                                        # one copy for q, k, v and the step metadata
         ops.store_kvcache(dev["k"], dev["v"], w.k_cache, w.v_cache, dev["slots"])
         ops.paged_attn_decode(dev["q"], w.k_cache, w.v_cache, dev["cl"], dev["bt"], w.scale, out=out)
         out_host.copy_(out, non_blocking=True)
+
+    # The step is captured once in a CUDA graph (upload, append, decode, reduce, read-back) and
+    # replayed, the way the reference replays its decode graphs (infer/engine/model_runner.py:135-152).
+    e2e_graph = None
+    if not args.profile and os.environ.get("INFER_B200_BENCH_EAGER") != "1":
+        try:
+            e2e_body()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                e2e_body()
+            e2e_graph = g
+        except Exception as exc:                              # pragma: no cover - falls back to eager launches
+            print(f"[bench] CUDA-graph capture of the end-to-end step failed ({exc}); timing eager launches", file=sys.stderr)
+            torch.cuda.synchronize()
+
+    def e2e_step():
+        if e2e_graph is not None:
+            e2e_graph.replay()
+        else:
+            e2e_body()
         torch.cuda.current_stream().synchronize()       # the caller reads the result every step
 
     e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -391,7 +412,8 @@ def main():
                        "l2": "KV per step (1.1 GB per GPU) exceeds L2 (126 MB); no flush needed",
                        "parallelism": f"kv-head-shard{world}"},
             "e2e": {"value": job_bytes / (e2e_ms / args.steps * 1e-3) / 1e9, "unit": UNIT,
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps},
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps,
+                    "launch": "cuda graph replay" if e2e_graph is not None else "eager"},
             "gpu_launches": 3 * args.steps,
             "roofline": {"bound": "hbm", "kernel": "decode_tma_kernel + decode_reduce_kernel", "achieved": achieved,
                          "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",

@@ -15,6 +15,7 @@ __global__ void __launch_bounds__(256) append_bf16_kernel(
     uint4* __restrict__ k_cache, uint4* __restrict__ v_cache, const int32_t* __restrict__ slot_mapping,
     int64_t n_tokens, int chunks, int64_t num_slots) {
     pdl_launch_dependents();   // an attention kernel behind this one may run its prologue already
+    pdl_wait();                // launched programmatically itself: the kernel in front may still be reading the pools
     const int64_t total = n_tokens * chunks;
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
     for (int64_t u0 = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; u0 < total; u0 += 2 * stride) {
@@ -200,10 +201,19 @@ int infer_kv_append(const infer_kv_pool_t* pool, const void* k, const void* v, i
         int64_t blocks = (total + 511) / 512;   // two chunks per thread
         const int64_t cap = int64_t(pool->sm_count) * 32;
         if (blocks > cap) blocks = cap;
-        ib::append_bf16_kernel<<<unsigned(blocks), 256, 0, stream>>>(
-            static_cast<const uint4*>(k), static_cast<const uint4*>(v), k_row_stride / 8, v_row_stride / 8,
-            static_cast<uint4*>(pool->k_cache), static_cast<uint4*>(pool->v_cache), slot_mapping, n_tokens, chunks,
-            pool->num_slots);
+        // programmatic launch: the CTAs may become resident while the previous kernel drains
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(unsigned(blocks));
+        cfg.blockDim = dim3(256);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        IB_CUDA(cudaLaunchKernelEx(&cfg, ib::append_bf16_kernel, static_cast<const uint4*>(k), static_cast<const uint4*>(v),
+                                   int64_t(k_row_stride / 8), int64_t(v_row_stride / 8), static_cast<uint4*>(pool->k_cache),
+                                   static_cast<uint4*>(pool->v_cache), slot_mapping, n_tokens, chunks, pool->num_slots));
         return ib::check_launch();
     }
 

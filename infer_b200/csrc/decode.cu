@@ -148,6 +148,7 @@ __global__ void __launch_bounds__(128) decode_simple_kernel(DecodeParams p) {
 // =========================================================================== reduce kernel
 // grid = batch * NG, 128 threads: warp w merges rows w, w + 4, ...; a lane owns 4 output dims.
 __global__ void __launch_bounds__(128) decode_reduce_kernel(DecodeParams p, int rows) {
+    pdl_launch_dependents();   // the next step's append may become resident; it waits for this grid itself
     pdl_wait();
     const int ng = p.n_kv_heads / p.hpc;
     const int b = blockIdx.x / ng, hg = blockIdx.x - b * ng;
