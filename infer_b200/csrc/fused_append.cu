@@ -10,8 +10,9 @@
 // bf16 before the bf16 multiply by the weight, and the rotation is three bf16 operations per
 // output (two products, one sum), as rope.cu computes it in its scalar type.
 //
-// One warp per (token, head): a lane owns dims {2l, 2l+1, 64+2l, 65+2l}, i.e. two rotation
-// pairs, so the pairing (i, i + 64) never leaves the thread.
+// Eight lanes per (token, head), four heads per warp: a lane owns dims [8l, 8l+8) and
+// [64+8l, 64+8l+8) (two 16-byte loads), i.e. eight rotation pairs, so the pairing (i, i + 64)
+// never leaves the thread and the sum of squares needs three shuffles.
 #include "common.cuh"
 
 namespace ib {
@@ -40,67 +41,89 @@ struct FusedArgs {
 __device__ __forceinline__ float bf(__nv_bfloat16 x) { return __bfloat162float(x); }
 __device__ __forceinline__ __nv_bfloat16 rb(float x) { return __float2bfloat16_rn(x); }
 
-// normalise + rotate the four values of this lane; returns them as two packed bf16 pairs
-__device__ __forceinline__ void norm_rope(const __nv_bfloat16* row, const __nv_bfloat16* weight, const __nv_bfloat16* cs,
-                                          float eps, int lane, uint32_t& lo_out, uint32_t& hi_out) {
-    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(row + 2 * lane);
-    const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(row + 64 + 2 * lane);
-    const float x0 = __low2float(lo), x1 = __high2float(lo), y0 = __low2float(hi), y1 = __high2float(hi);
-    float ss = x0 * x0 + x1 * x1 + y0 * y0 + y1 * y1;
+__device__ __forceinline__ void unpack8(const uint4& r, float (&x)[8]) {
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&r);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    for (int i = 0; i < 4; ++i) {
+        x[2 * i] = __low2float(p[i]);
+        x[2 * i + 1] = __high2float(p[i]);
+    }
+}
+__device__ __forceinline__ uint4 pack8(const __nv_bfloat16 (&x)[8]) {
+    uint4 r;
+    __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        p[i].x = x[2 * i];
+        p[i].y = x[2 * i + 1];
+    }
+    return r;
+}
+
+// normalise + rotate the sixteen values of this lane (sub = lane within the head's group of 8)
+__device__ __forceinline__ void norm_rope(const __nv_bfloat16* row, const __nv_bfloat16* weight, const __nv_bfloat16* cs,
+                                          float eps, int sub, uint4& lo_out, uint4& hi_out) {
+    float x[8], y[8], wl[8], wh[8], c[8], sn[8];
+    unpack8(*reinterpret_cast<const uint4*>(row + 8 * sub), x);
+    unpack8(*reinterpret_cast<const uint4*>(row + 64 + 8 * sub), y);
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += x[i] * x[i] + y[i] * y[i];
+    // only the eight lanes of this head's group take part: other groups of the warp may be V heads
+    const uint32_t group_mask = 0xffu << ((threadIdx.x & 31) & ~7);
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) ss += __shfl_xor_sync(group_mask, ss, o);
     const float inv = rsqrtf(ss * (1.0f / kHeadDim) + eps);
-    const __nv_bfloat162 wl = *reinterpret_cast<const __nv_bfloat162*>(weight + 2 * lane);
-    const __nv_bfloat162 wh = *reinterpret_cast<const __nv_bfloat162*>(weight + 64 + 2 * lane);
-    // bf16(bf16(x * inv) * w)
-    const __nv_bfloat16 a0 = rb(bf(rb(x0 * inv)) * __low2float(wl)), a1 = rb(bf(rb(x1 * inv)) * __high2float(wl));
-    const __nv_bfloat16 b0 = rb(bf(rb(y0 * inv)) * __low2float(wh)), b1 = rb(bf(rb(y1 * inv)) * __high2float(wh));
-    const __nv_bfloat162 c = *reinterpret_cast<const __nv_bfloat162*>(cs + 2 * lane);
-    const __nv_bfloat162 s = *reinterpret_cast<const __nv_bfloat162*>(cs + 64 + 2 * lane);
-    const float c0 = __low2float(c), c1 = __high2float(c), s0 = __low2float(s), s1 = __high2float(s);
-    // out_x = bf16(bf16(x c) - bf16(y s)),  out_y = bf16(bf16(y c) + bf16(x s))
-    const __nv_bfloat16 ox0 = rb(bf(rb(bf(a0) * c0)) - bf(rb(bf(b0) * s0)));
-    const __nv_bfloat16 ox1 = rb(bf(rb(bf(a1) * c1)) - bf(rb(bf(b1) * s1)));
-    const __nv_bfloat16 oy0 = rb(bf(rb(bf(b0) * c0)) + bf(rb(bf(a0) * s0)));
-    const __nv_bfloat16 oy1 = rb(bf(rb(bf(b1) * c1)) + bf(rb(bf(a1) * s1)));
-    __nv_bfloat162 plo, phi;
-    plo.x = ox0; plo.y = ox1;
-    phi.x = oy0; phi.y = oy1;
-    lo_out = *reinterpret_cast<uint32_t*>(&plo);
-    hi_out = *reinterpret_cast<uint32_t*>(&phi);
+    unpack8(*reinterpret_cast<const uint4*>(weight + 8 * sub), wl);
+    unpack8(*reinterpret_cast<const uint4*>(weight + 64 + 8 * sub), wh);
+    unpack8(*reinterpret_cast<const uint4*>(cs + 8 * sub), c);
+    unpack8(*reinterpret_cast<const uint4*>(cs + 64 + 8 * sub), sn);
+    __nv_bfloat16 ox[8], oy[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        // bf16(bf16(x * inv) * w)
+        const float a = bf(rb(bf(rb(x[i] * inv)) * wl[i]));
+        const float b = bf(rb(bf(rb(y[i] * inv)) * wh[i]));
+        // out_x = bf16(bf16(x c) - bf16(y s)),  out_y = bf16(bf16(y c) + bf16(x s))
+        ox[i] = rb(bf(rb(a * c[i])) - bf(rb(b * sn[i])));
+        oy[i] = rb(bf(rb(b * c[i])) + bf(rb(a * sn[i])));
+    }
+    lo_out = pack8(ox);
+    hi_out = pack8(oy);
 }
 
 __global__ void __launch_bounds__(256) fused_norm_rope_append_kernel(FusedArgs a) {
     pdl_launch_dependents();
     const int heads = a.n_q_heads + 2 * a.n_kv_heads;
-    const int64_t item = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-    if (item >= a.n_tokens * heads) return;
-    const int lane = threadIdx.x & 31;
-    const int64_t tok = item / heads;
-    const int h = int(item - tok * heads);
-    if (h < a.n_q_heads) {
-        const int64_t pos = min(max(a.positions[tok], int64_t(0)), a.max_position - 1);
-        uint32_t lo, hi;
-        norm_rope(a.q + tok * a.q_pitch + h * kHeadDim, a.q_weight, a.cos_sin + pos * kHeadDim, a.eps, lane, lo, hi);
-        __nv_bfloat16* dst = a.q_out + tok * a.q_out_pitch + h * kHeadDim;
-        *reinterpret_cast<uint32_t*>(dst + 2 * lane) = lo;
-        *reinterpret_cast<uint32_t*>(dst + 64 + 2 * lane) = hi;
-        return;
-    }
+    const int64_t total = a.n_tokens * heads;
+    const int64_t item = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 3;
+    const int sub = threadIdx.x & 7;
+    // a group past the end still takes part in the shuffles of its warp
+    const bool live = item < total;
+    const int64_t it = live ? item : total - 1;
+    const int64_t tok = it / heads;
+    const int h = int(it - tok * heads);
     const int64_t slot = a.slot_mapping[tok];
-    if (slot < 0 || slot >= a.num_slots) return;             // padding row of a captured batch
+    const bool slot_ok = slot >= 0 && slot < a.num_slots;      // false: padding row of a captured batch
     if (h < a.n_q_heads + a.n_kv_heads) {
+        const bool is_q = h < a.n_q_heads;
         const int kh = h - a.n_q_heads;
         const int64_t pos = min(max(a.positions[tok], int64_t(0)), a.max_position - 1);
-        uint32_t lo, hi;
-        norm_rope(a.k + tok * a.k_pitch + kh * kHeadDim, a.k_weight, a.cos_sin + pos * kHeadDim, a.eps, lane, lo, hi);
-        __nv_bfloat16* dst = a.k_cache + (slot * a.n_kv_heads + kh) * int64_t(kHeadDim);
-        *reinterpret_cast<uint32_t*>(dst + 2 * lane) = lo;
-        *reinterpret_cast<uint32_t*>(dst + 64 + 2 * lane) = hi;
+        const __nv_bfloat16* src = is_q ? a.q + tok * a.q_pitch + h * kHeadDim : a.k + tok * a.k_pitch + kh * kHeadDim;
+        uint4 lo, hi;
+        norm_rope(src, is_q ? a.q_weight : a.k_weight, a.cos_sin + pos * kHeadDim, a.eps, sub, lo, hi);
+        if (!live || (!is_q && !slot_ok)) return;
+        __nv_bfloat16* dst = is_q ? a.q_out + tok * a.q_out_pitch + h * kHeadDim
+                                  : a.k_cache + (slot * a.n_kv_heads + kh) * int64_t(kHeadDim);
+        *reinterpret_cast<uint4*>(dst + 8 * sub) = lo;
+        *reinterpret_cast<uint4*>(dst + 64 + 8 * sub) = hi;
     } else {
+        if (!live || !slot_ok) return;
         const int vh = h - a.n_q_heads - a.n_kv_heads;
-        const uint2 raw = *reinterpret_cast<const uint2*>(a.v + tok * a.v_pitch + vh * kHeadDim + lane * 4);
-        *reinterpret_cast<uint2*>(a.v_cache + (slot * a.n_kv_heads + vh) * int64_t(kHeadDim) + lane * 4) = raw;
+        const __nv_bfloat16* src = a.v + tok * a.v_pitch + vh * kHeadDim;
+        __nv_bfloat16* dst = a.v_cache + (slot * a.n_kv_heads + vh) * int64_t(kHeadDim);
+        *reinterpret_cast<uint4*>(dst + 8 * sub) = *reinterpret_cast<const uint4*>(src + 8 * sub);
+        *reinterpret_cast<uint4*>(dst + 64 + 8 * sub) = *reinterpret_cast<const uint4*>(src + 64 + 8 * sub);
     }
 }
 
@@ -122,7 +145,7 @@ extern "C" int infer_qk_norm_rope_append(const infer_kv_pool_t* pool, void* q_ou
     const int64_t qrow = int64_t(n_q_heads) * kHeadDim, kvrow = int64_t(pool->n_kv_heads) * kHeadDim;
     if (q_row_stride < qrow || q_out_row_stride < qrow || k_row_stride < kvrow || v_row_stride < kvrow) return INFER_ERR_STRIDE;
     if (!aligned16(q_out) || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(cos_sin_cache) ||
-        (reinterpret_cast<uintptr_t>(q_norm_weight) & 3) || (reinterpret_cast<uintptr_t>(k_norm_weight) & 3) ||
+        !aligned16(q_norm_weight) || !aligned16(k_norm_weight) ||
         q_row_stride % 8 || q_out_row_stride % 8 || k_row_stride % 8 || v_row_stride % 8)
         return INFER_ERR_ALIGN;
     FusedArgs a;
@@ -147,8 +170,8 @@ extern "C" int infer_qk_norm_rope_append(const infer_kv_pool_t* pool, void* q_ou
     a.n_q_heads = n_q_heads;
     a.n_kv_heads = pool->n_kv_heads;
     a.eps = eps;
-    const int64_t warps = n_tokens * (n_q_heads + 2 * pool->n_kv_heads);
-    const int64_t blocks = (warps + 7) / 8;
+    const int64_t groups = n_tokens * (n_q_heads + 2 * pool->n_kv_heads);   // eight lanes each
+    const int64_t blocks = (groups + 31) / 32;
     if (blocks >= (int64_t(1) << 31)) return INFER_ERR_GEOMETRY;
     fused_norm_rope_append_kernel<<<unsigned(blocks), 256, 0, static_cast<cudaStream_t>(stream_)>>>(a);
     return check_launch();
