@@ -17,7 +17,9 @@
 // tensor memory and the running sum) when the true maximum has grown by more than 2^8; the
 // result is exact because O and the sum always share the same reference.
 // Warp roles: 0-3 softmax of tile 0, 4-7 softmax of tile 1, 8 TMA producer, 9 MMA issue and
-// TMEM allocation.  Every barrier wait is bounded; a wait that runs out raises a CTA-wide
+// TMEM allocation, 10-11 idle (they complete the third warpgroup, which hands 64 registers per
+// thread to the softmax warpgroups with setmaxnreg so that a whole 128-column row of S fits in
+// registers).  The softmax arithmetic uses packed f32x2 instructions and 3-input max.  Every barrier wait is bounded; a wait that runs out raises a CTA-wide
 // abort flag, every role drains to the common epilogue, TMEM is freed and a status is set.
 #include "prefill.cuh"
 
@@ -30,7 +32,7 @@ constexpr int kTcTile = 2 * kTcHalf;         // 32 KiB: one Q, K or V tile
 constexpr int kTcQTiles = 2;                 // query tiles per CTA, each with its own softmax warpgroup
 constexpr int kTcSoftmaxWarps = 4 * kTcQTiles;
 constexpr int kTcProducerWarp = kTcSoftmaxWarps, kTcMmaWarp = kTcSoftmaxWarps + 1;
-constexpr int kTcThreads = (kTcSoftmaxWarps + 2) * 32;
+constexpr int kTcThreads = (kTcSoftmaxWarps + 4) * 32;   // third warpgroup: producer, MMA issue, two idle warps
 constexpr int kTcKStages = 3, kTcVStages = 2;
 // tensor memory columns: S of tile 0 at 0, S of tile 1 at 128, O of tile 0 at 256, O of tile 1 at 384;
 // P (bf16, two keys per column) reuses columns 64-127 of its tile's S
@@ -114,6 +116,30 @@ constexpr uint32_t tc_idesc(bool b_mn_major) {
     return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
 }
 
+// packed pairs of f32 (sm_100 executes add/mul/fma on two floats per instruction)
+__device__ __forceinline__ uint64_t pk2(float a, float b) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void upk2(uint64_t v, float& a, float& b) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
 // Bounded wait that also gives up as soon as another thread raised the abort flag.
 __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     for (uint32_t i = 0; i < (1u << 22); ++i) {
@@ -201,6 +227,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
     const uint32_t tmem = *s_tmem;
     bool ok = true;
 
+    // Register budget: 384 threads x 168 at launch.  The third warpgroup gives 64 registers per
+    // thread back, the two softmax warpgroups grow to 200: they hold a 128-column row of S.
+    // (each role adjusts its own budget first thing in its branch, so that the compiler sees it)
+    if (warp >= kTcSoftmaxWarps) {
+    // one instruction for the whole third warpgroup, before its warps take their roles
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 104;" ::: "memory");
     if (warp == kTcProducerWarp) {
         // ================================================================= TMA producer
         if (lane == 0) {
@@ -324,8 +356,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
         if (lane == 0) tc_commit(bar(DRAIN));
         __syncwarp();
         mbar_wait(bar(DRAIN), 0);
+    }
     } else {
         // ================================================================= softmax, one row per thread
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 200;" ::: "memory");
         const int g = warp >> 2;                                   // query tile of this warpgroup
         const int r = (warp & 3) * 32 + lane;                      // row in the tile == TMEM lane
         const uint32_t lane_sel = uint32_t((warp & 3) * 32) << 16;
@@ -343,31 +377,25 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
             tc_fence_after();
             const int limit = pos - j * kTcKeys;                     // columns <= limit are visible
             const bool masked = j * kTcKeys + kTcKeys - 1 > tile_first_pos;
-            // row maximum: first half of the row (dropped again), then the second half, which stays
-            // in registers
+            // the whole row of S in registers
             float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-            uint32_t sb[64];
-            {
-                uint32_t sa[64];
-                tc_ld32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&sa[0]));
-                tc_ld32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&sa[32]));
-                tc_ld32(s_addr + 64, *reinterpret_cast<uint32_t(*)[32]>(&sb[0]));
-                tc_ld32(s_addr + 96, *reinterpret_cast<uint32_t(*)[32]>(&sb[32]));
-                tc_wait_ld();
-                if (masked) {
+            uint32_t sv[128];
+            tc_ld32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+            tc_ld32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
+            tc_ld32(s_addr + 64, *reinterpret_cast<uint32_t(*)[32]>(&sv[64]));
+            tc_ld32(s_addr + 96, *reinterpret_cast<uint32_t(*)[32]>(&sv[96]));
+            tc_wait_ld();
+            if (masked) {
 #pragma unroll
-                    for (int i = 0; i < 64; ++i) {
-                        if (i > limit) sa[i] = 0xff800000u;          // -inf
-                        if (i + 64 > limit) sb[i] = 0xff800000u;
-                    }
-                }
+                for (int i = 0; i < 128; ++i)
+                    if (i > limit) sv[i] = 0xff800000u;              // -inf
+            }
 #pragma unroll
-                for (int i = 0; i < 64; i += 4) {
-                    mx0 = fmaxf(mx0, fmaxf(__uint_as_float(sa[i]), __uint_as_float(sa[i + 1])));
-                    mx1 = fmaxf(mx1, fmaxf(__uint_as_float(sa[i + 2]), __uint_as_float(sa[i + 3])));
-                    mx2 = fmaxf(mx2, fmaxf(__uint_as_float(sb[i]), __uint_as_float(sb[i + 1])));
-                    mx3 = fmaxf(mx3, fmaxf(__uint_as_float(sb[i + 2]), __uint_as_float(sb[i + 3])));
-                }
+            for (int i = 0; i < 128; i += 8) {
+                mx0 = fmax3(mx0, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
+                mx1 = fmax3(mx1, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
+                mx2 = fmax3(mx2, __uint_as_float(sv[i + 4]), __uint_as_float(sv[i + 5]));
+                mx3 = fmax3(mx3, __uint_as_float(sv[i + 6]), __uint_as_float(sv[i + 7]));
             }
             const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
             // move the reference only when the maximum outgrew it by more than 2^kLazyLog2
@@ -394,41 +422,28 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
                 m_ref = m_new;
             }
             const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-            // P = exp2(S * c - m) as packed bf16 over columns 64-127 of S.  Keys 64-127 come from
-            // registers and land on columns 96-127; then columns 0-63 of S (untouched by P) are
-            // read again and their P lands on columns 64-95, whose S values are already consumed.
-            float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
-            {
+            // P = exp2(S * c - m) as packed bf16 over columns 64-127 of S (all of S is in registers)
+            uint64_t rsa = pk2(0.f, 0.f), rsb = pk2(0.f, 0.f);
+            const uint64_t c2 = pk2(p.scale_log2, p.scale_log2), nm2 = pk2(-m_use, -m_use);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
                 uint32_t pk[32];
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
-                    const float e0 = fast_exp2(fmaf(__uint_as_float(sb[2 * i]), p.scale_log2, -m_use));
-                    const float e1 = fast_exp2(fmaf(__uint_as_float(sb[2 * i + 1]), p.scale_log2, -m_use));
-                    rs2 += e0;
-                    rs3 += e1;
+                    const int c = h * 64 + 2 * i;
+                    const uint64_t x2 = ffma2(pk2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), c2, nm2);
+                    float e0, e1;
+                    upk2(x2, e0, e1);
+                    e0 = fast_exp2(e0);
+                    e1 = fast_exp2(e1);
+                    if (i & 1) rsb = fadd2(rsb, pk2(e0, e1)); else rsa = fadd2(rsa, pk2(e0, e1));
                     pk[i] = pack_bf16(e0, e1);
                 }
-                tc_st32(s_addr + kTmemPinS + 32, pk);
+                tc_st32(s_addr + kTmemPinS + h * 32, pk);
             }
-            {
-                uint32_t sa[64], pk[32];
-                tc_ld32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&sa[0]));
-                tc_ld32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&sa[32]));
-                tc_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float e0 = fast_exp2(fmaf(__uint_as_float(sa[2 * i]), p.scale_log2, -m_use));
-                    float e1 = fast_exp2(fmaf(__uint_as_float(sa[2 * i + 1]), p.scale_log2, -m_use));
-                    if (masked) {
-                        if (2 * i > limit) e0 = 0.f;
-                        if (2 * i + 1 > limit) e1 = 0.f;
-                    }
-                    rs0 += e0;
-                    rs1 += e1;
-                    pk[i] = pack_bf16(e0, e1);
-                }
-                tc_st32(s_addr + kTmemPinS, pk);
-            }
+            float rs0, rs1, rs2, rs3;
+            upk2(rsa, rs0, rs1);
+            upk2(rsb, rs2, rs3);
             l_run += (rs0 + rs1) + (rs2 + rs3);
             tc_wait_st();
             tc_fence_before();
