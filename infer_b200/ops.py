@@ -33,8 +33,9 @@ def _ptr(t):
 
 class KVPool:
     """Handle on a pair of page pools ``[num_blocks, block_size, Hkv, 128]`` (bf16, or uint8
-    holding e4m3 bytes together with fp32 ``[num_blocks, Hkv]`` scales).  Owns no memory;
-    keeps the tensors alive and carries the TMA descriptors built once by the library."""
+    holding e4m3 bytes together with fp32 ``[num_blocks, Hkv]`` scales).  Owns no memory and
+    keeps no reference to the tensors (the caller keeps them alive, as the reference's runner
+    does with ``self.kv_cache``); carries the TMA descriptors built once by the library."""
 
     def __init__(self, k_cache, v_cache, k_scale=None, v_scale=None):
         for t in (k_cache, v_cache):
@@ -50,7 +51,8 @@ class KVPool:
             for s in (k_scale, v_scale):
                 if s is None or s.dtype != torch.float32 or tuple(s.shape) != (nb, hkv) or not s.is_contiguous():
                     raise ValueError("e4m3 pools need contiguous fp32 scales [num_blocks, Hkv]")
-        self.k_cache, self.v_cache, self.k_scale, self.v_scale = k_cache, v_cache, k_scale, v_scale
+        # The handle only borrows the tensors' memory (addresses and geometry): it keeps no
+        # reference, so a cached handle never pins gigabytes of pool memory.
         self.fp8 = fp8
         self.num_blocks, self.block_size, self.n_kv_heads, self.head_dim = k_cache.shape
         self.device = k_cache.device
@@ -73,7 +75,9 @@ class KVPool:
 def pool_of(k_cache, v_cache, k_scale=None, v_scale=None) -> KVPool:
     """Pool handle for these cache tensors, created on first use (one per layer in practice)."""
     key = (k_cache.data_ptr(), v_cache.data_ptr(), tuple(k_cache.shape), k_cache.dtype,
-           k_scale.data_ptr() if k_scale is not None else 0)
+           k_scale.data_ptr() if k_scale is not None else 0, v_scale.data_ptr() if v_scale is not None else 0)
+    # A handle is valid for any tensor with the same addresses, shape and dtype, whatever Python
+    # object presents them (a layer view sliced again every step, or new memory at an old address).
     pool = _POOLS.get(key)
     if pool is None:
         pool = _POOLS[key] = KVPool(k_cache, v_cache, k_scale, v_scale)

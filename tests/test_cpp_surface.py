@@ -79,3 +79,62 @@ def test_cpp_surface_on_gpu(surface_binary, tmp_path):
     want = oracle.paged_decode(q, kc, vc, torch.tensor(lens, dtype=torch.int32), bt, 128 ** -0.5)
     assert_close(got, want, ATOL_BF16, RTOL_BF16, "C++ surface: append + paged decode")
     assert_close(dense, oracle.dense_causal(Q, K, V), ATOL_BF16, RTOL_BF16, "C++ surface: UnifiedOp::attention")
+
+
+@pytest.fixture(scope="module")
+def block_manager_binary(tmp_path_factory):
+    if shutil.which("g++") is None:
+        pytest.skip("g++ is not available")
+    out = tmp_path_factory.mktemp("cppbm") / "block_manager_test"
+    res = subprocess.run(["g++", "-std=c++17", "-O2", "-Wall", f"-I{ROOT / 'include'}",
+                          str(ROOT / "tests" / "cpp" / "block_manager_test.cpp"), "-o", str(out)], capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
+    return out
+
+
+def test_native_xxh64_matches_xxhash(block_manager_binary):
+    """The header's XXH64 against the xxhash package the reference uses, on the exact byte
+    strings its BlockManager hashes (int64 token ids, optional 8-byte prefix) and odd lengths."""
+    import xxhash
+    rng = np.random.default_rng(3)
+    cases, want = [], []
+    for n in (0, 1, 3, 4, 5, 31, 256, 257):
+        toks = rng.integers(0, 2 ** 40, size=n).tolist()
+        for prefix in (None, int(rng.integers(0, 2 ** 63)) * 2 + 1):
+            h = xxhash.xxh64()
+            if prefix is not None:
+                h.update(prefix.to_bytes(8, "little"))
+            h.update(np.array(toks, dtype=np.int64).tobytes())
+            want.append(h.intdigest())
+            cases.append(" ".join(map(str, [n] + toks + ([prefix] if prefix is not None else []))))
+    res = subprocess.run([str(block_manager_binary), "hash"], input="\n".join(cases) + "\n", capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
+    assert [int(x) for x in res.stdout.split()] == want
+
+
+def test_native_block_manager_matches_reference(block_manager_binary, golden, tmp_path):
+    """The same scripted engine life as tests/golden (prefill with shared prefixes, decode growth
+    across page boundaries, frees, digest revival) through the C++ allocator: page lists, cache
+    hits, reference counts and free-list order equal the reference's at every snapshot."""
+    import json
+    g = golden["allocator"]
+    lines = [f"N {g['num_blocks']} {g['block_size']}"]
+    for p in g["prompts"]:
+        lines.append("A " + " ".join(map(str, [len(p)] + p)))
+    lines.append("S")
+    for toks in g["new_tokens"]:
+        for i, t in enumerate(toks):
+            lines.append(f"T {i} {t}")
+        lines.append("S")
+    lines += ["D 0", "D 2", "S"]
+    late = g["late_prompt"]
+    lines += ["A " + " ".join(map(str, [len(late)] + late)), "S"]
+    scen = tmp_path / "scenario.txt"
+    scen.write_text("\n".join(lines) + "\n")
+    res = subprocess.run([str(block_manager_binary), str(scen)], capture_output=True, text=True, timeout=60)
+    assert res.returncode == 0, res.stderr
+    snaps = [json.loads(l) for l in res.stdout.splitlines()]
+    assert len(snaps) == len(g["events"])
+    for got, want in zip(snaps, g["events"]):
+        for key in ("tables", "cached", "lens", "ref_counts", "free"):
+            assert got[key] == want[key], (want["tag"], key)
