@@ -2,9 +2,11 @@
 //
 // bf16 pools: a pure byte copy, one 16-byte load and one 16-byte store per thread and
 // row chunk, K and V in the same thread, two chunks in flight per thread.
-// e4m3 pools: four small kernels (snapshot scales, raise scales by the new rows' amax,
+// e4m3 pools: four kernels (snapshot scales, raise scales by the new rows' amax,
 // re-encode pages whose scale grew, write the new rows) so that the result depends on no
-// scheduling order and matches the CPU oracle bit for bit.
+// scheduling order and matches the CPU oracle bit for bit.  The three row kernels work on
+// strips of 8 tokens per warp: 16-byte loads, 8 in flight per lane, one atomic per run of
+// tokens that share a page.
 #include "common.cuh"
 
 namespace ib {
@@ -82,96 +84,184 @@ __global__ void fp8_snapshot_kernel(Fp8Args a) {
     a.snap[which][e] = a.scale[which][e];
 }
 
-// one warp per (token, head, k|v): scale = max(scale, amax(row) / 448)
-__global__ void fp8_amax_kernel(Fp8Args a) {
-    const int64_t item = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-    if (item >= a.n_tokens * a.n_kv_heads * 2) return;
-    const int lane = threadIdx.x & 31;
-    int which, head;
-    int64_t tok, slot;
-    if (!fp8_locate(a, item, which, tok, head, slot)) return;
-    const uint2 raw = *reinterpret_cast<const uint2*>(a.src[which] + tok * a.pitch[which] + head * kHeadDim + lane * 4);
-    const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
-    const __nv_bfloat162 p1 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-    float m = fmaxf(fmaxf(fabsf(__low2float(p0)), fabsf(__high2float(p0))),
-                    fmaxf(fabsf(__low2float(p1)), fabsf(__high2float(p1))));
+// Work unit of the three row kernels below: kStrip consecutive tokens x (k|v) x a pair of KV
+// heads.  One warp per unit: lane / 16 picks the head of the pair, lane % 16 the 16-byte chunk
+// of its 128-element row, so a warp reads 512 contiguous bytes per token and keeps kStrip
+// loads in flight per lane.  Consecutive tokens mostly share a page, which lets the half-warp
+// issue one atomic (amax) or one claim test (rescale) per run of equal pages, not per row.
+constexpr int kStrip = 8;
+
+struct StripUnit {
+    int which, head, sub;
+    int64_t tok0;
+    bool active;
+};
+
+__device__ __forceinline__ int64_t strip_units(const Fp8Args& a) {
+    return ((a.n_tokens + kStrip - 1) / kStrip) * 2 * ((a.n_kv_heads + 1) / 2);
+}
+
+__device__ __forceinline__ StripUnit strip_locate(const Fp8Args& a, int64_t unit, int lane) {
+    const int pairs = (a.n_kv_heads + 1) / 2;
+    StripUnit u;
+    u.which = int(unit & 1);
+    const int64_t sp = unit >> 1;
+    const int64_t strip = sp / pairs;
+    u.head = int(sp - strip * pairs) * 2 + (lane >> 4);
+    u.sub = lane & 15;
+    u.tok0 = strip * kStrip;
+    u.active = u.head < a.n_kv_heads;
+    return u;
+}
+
+__device__ __forceinline__ float amax8(const uint4& r) {
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+    float m = 0.0f;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    if (lane == 0) {
-        const float s = __fdiv_rn(m, 448.0f);
-        // non-negative floats order like their bit patterns
-        atomicMax(reinterpret_cast<int*>(a.scale[which] + (slot / a.block_size) * a.n_kv_heads + head),
-                  __float_as_int(s));
+    for (int i = 0; i < 4; ++i) {
+        // a bf16 is the upper half of the fp32 with the same value
+        m = fmaxf(m, fmaxf(fabsf(__uint_as_float(w[i] << 16)), fabsf(__uint_as_float(w[i] & 0xffff0000u))));
+    }
+    return m;
+}
+
+// scale[page, head] = max(scale, amax(rows of this call on that page) / 448)
+__global__ void __launch_bounds__(256) fp8_amax_kernel(Fp8Args a) {
+    const int64_t unit = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    if (unit >= strip_units(a)) return;
+    const int lane = threadIdx.x & 31;
+    const StripUnit u = strip_locate(a, unit, lane);
+    int64_t page[kStrip];
+    uint4 raw[kStrip];
+#pragma unroll
+    for (int t = 0; t < kStrip; ++t) {
+        const int64_t tok = u.tok0 + t;
+        int64_t slot = -1;
+        if (tok < a.n_tokens) slot = a.slot_mapping[tok];
+        const bool ok = u.active && slot >= 0 && slot < a.num_slots;
+        page[t] = ok ? slot / a.block_size : -1;
+        raw[t] = make_uint4(0, 0, 0, 0);
+        if (ok) raw[t] = __ldg(reinterpret_cast<const uint4*>(a.src[u.which] + tok * a.pitch[u.which] + u.head * kHeadDim) + u.sub);
+    }
+    float m[kStrip];
+#pragma unroll
+    for (int t = 0; t < kStrip; ++t) {
+        m[t] = amax8(raw[t]);
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) m[t] = fmaxf(m[t], __shfl_xor_sync(0xffffffffu, m[t], o));
+    }
+    if (u.sub != 0 || !u.active) return;
+    int64_t cur = -1;
+    float best = 0.0f;
+#pragma unroll
+    for (int t = 0; t <= kStrip; ++t) {
+        const int64_t p = t < kStrip ? page[t] : -2;
+        if (p != cur) {
+            if (cur >= 0)   // non-negative floats order like their bit patterns
+                atomicMax(reinterpret_cast<int*>(a.scale[u.which] + cur * a.n_kv_heads + u.head),
+                          __float_as_int(__fdiv_rn(best, 448.0f)));
+            cur = p;
+            best = 0.0f;
+        }
+        if (t < kStrip) best = fmaxf(best, m[t]);
     }
 }
 
 __device__ __forceinline__ uint32_t rescale4(uint32_t q, float ratio) {
     uint32_t out = 0;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>((q >> (8 * i)) & 0xff), __NV_E4M3);
-        const float x = __fmul_rn(__half2float(*reinterpret_cast<const __half*>(&h)), ratio);
-        out |= uint32_t(__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
+    for (int i = 0; i < 2; ++i) {
+        const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>((q >> (16 * i)) & 0xffff), __NV_E4M3);
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h));
+        out |= uint32_t(__nv_cvt_float2_to_fp8x2(make_float2(__fmul_rn(f.x, ratio), __fmul_rn(f.y, ratio)),
+                                                 __NV_SATFINITE, __NV_E4M3)) << (16 * i);
     }
     return out;
 }
 
-// one warp per (token, head, k|v); the first warp to claim a page/head whose scale grew
-// re-encodes all of that page's rows for that head (rare: most warps leave after two loads).
+// The first half-warp to claim a (page, head) whose scale grew re-encodes all of that page's
+// rows for that head (rare: most half-warps leave after two loads per distinct page).
 __global__ void __launch_bounds__(256) fp8_rescale_kernel(Fp8Args a) {
-    const int64_t item = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-    if (item >= a.n_tokens * a.n_kv_heads * 2) return;
+    const int64_t unit = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    if (unit >= strip_units(a)) return;
     const int lane = threadIdx.x & 31;
-    int which, head;
-    int64_t tok, slot;
-    if (!fp8_locate(a, item, which, tok, head, slot)) return;
-    const int64_t page = slot / a.block_size;
-    const int64_t e = page * a.n_kv_heads + head;
-    float ratio = -1.0f;
-    if (lane == 0) {
-        const float now = a.scale[which][e];
-        const float seen = a.snap[which][e];
-        if (seen > 0.0f && now > seen) {                       // a candidate: claim it exactly once
-            const float old = atomicExch(a.snap[which] + e, -1.0f);
-            if (old > 0.0f) ratio = __fdiv_rn(old, now);
+    const StripUnit u = strip_locate(a, unit, lane);
+    const unsigned half_mask = 0xffffu << (lane & 16);
+    int64_t cur = -1;
+    for (int t = 0; t < kStrip; ++t) {
+        const int64_t tok = u.tok0 + t;
+        int64_t slot = -1;
+        if (tok < a.n_tokens) slot = a.slot_mapping[tok];
+        const bool ok = u.active && slot >= 0 && slot < a.num_slots;
+        const int64_t page = ok ? slot / a.block_size : -1;
+        if (page == cur || page < 0) continue;        // uniform within the half-warp
+        cur = page;
+        const int64_t e = page * a.n_kv_heads + u.head;
+        float ratio = -1.0f;
+        if (u.sub == 0) {
+            const float now = a.scale[u.which][e];
+            const float seen = a.snap[u.which][e];
+            if (seen > 0.0f && now > seen) {                       // a candidate: claim it exactly once
+                const float old = atomicExch(a.snap[u.which] + e, -1.0f);
+                if (old > 0.0f) ratio = __fdiv_rn(old, now);
+            }
         }
-    }
-    ratio = __shfl_sync(0xffffffffu, ratio, 0);
-    if (ratio < 0.0f) return;
-    // rows of this head: block_size rows of 128 bytes, pitch Hkv * 128
-    uint8_t* base = a.cache[which] + (page * a.block_size * a.n_kv_heads + head) * int64_t(kHeadDim);
-    const int64_t pitch = int64_t(a.n_kv_heads) * kHeadDim;
-    for (int i = lane; i < a.block_size * 8; i += 32) {
-        uint4* p = reinterpret_cast<uint4*>(base + (i >> 3) * pitch + (i & 7) * 16);
-        uint4 q = *p;
-        q.x = rescale4(q.x, ratio);
-        q.y = rescale4(q.y, ratio);
-        q.z = rescale4(q.z, ratio);
-        q.w = rescale4(q.w, ratio);
-        *p = q;
+        ratio = __shfl_sync(half_mask, ratio, lane & 16);
+        if (ratio < 0.0f) continue;
+        // rows of this head: block_size rows of 128 bytes, pitch Hkv * 128
+        uint8_t* base = a.cache[u.which] + (page * a.block_size * a.n_kv_heads + u.head) * int64_t(kHeadDim);
+        const int64_t pitch = int64_t(a.n_kv_heads) * kHeadDim;
+        for (int i = u.sub; i < a.block_size * 8; i += 16) {
+            uint4* p = reinterpret_cast<uint4*>(base + (i >> 3) * pitch + (i & 7) * 16);
+            uint4 q = *p;
+            q.x = rescale4(q.x, ratio);
+            q.y = rescale4(q.y, ratio);
+            q.z = rescale4(q.z, ratio);
+            q.w = rescale4(q.w, ratio);
+            *p = q;
+        }
     }
 }
 
-// one warp per (token, head, k|v): quantise the row with the page's final scale
-__global__ void fp8_write_kernel(Fp8Args a) {
-    const int64_t item = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-    if (item >= a.n_tokens * a.n_kv_heads * 2) return;
+// quantise the new rows with their page's final scale
+__global__ void __launch_bounds__(256) fp8_write_kernel(Fp8Args a) {
+    const int64_t unit = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    if (unit >= strip_units(a)) return;
     const int lane = threadIdx.x & 31;
-    int which, head;
-    int64_t tok, slot;
-    if (!fp8_locate(a, item, which, tok, head, slot)) return;
-    const float s = a.scale[which][(slot / a.block_size) * a.n_kv_heads + head];
-    const uint2 raw = *reinterpret_cast<const uint2*>(a.src[which] + tok * a.pitch[which] + head * kHeadDim + lane * 4);
-    const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
-    const __nv_bfloat162 p1 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-    const float x[4] = {__low2float(p0), __high2float(p0), __low2float(p1), __high2float(p1)};
-    uint32_t out = 0;
-    if (s > 0.0f) {
+    const StripUnit u = strip_locate(a, unit, lane);
+    if (!u.active) return;
+    int64_t slot[kStrip];
+    uint4 raw[kStrip];
+    float s[kStrip];
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
-            out |= uint32_t(__nv_cvt_float_to_fp8(__fdiv_rn(x[i], s), __NV_SATFINITE, __NV_E4M3)) << (8 * i);
+    for (int t = 0; t < kStrip; ++t) {
+        const int64_t tok = u.tok0 + t;
+        slot[t] = -1;
+        if (tok < a.n_tokens) slot[t] = a.slot_mapping[tok];
+        if (slot[t] >= a.num_slots) slot[t] = -1;
+        raw[t] = make_uint4(0, 0, 0, 0);
+        s[t] = 0.0f;
+        if (slot[t] >= 0) {
+            raw[t] = __ldg(reinterpret_cast<const uint4*>(a.src[u.which] + tok * a.pitch[u.which] + u.head * kHeadDim) + u.sub);
+            s[t] = a.scale[u.which][(slot[t] / a.block_size) * a.n_kv_heads + u.head];
+        }
     }
-    *reinterpret_cast<uint32_t*>(a.cache[which] + (slot * a.n_kv_heads + head) * int64_t(kHeadDim) + lane * 4) = out;
+#pragma unroll
+    for (int t = 0; t < kStrip; ++t) {
+        if (slot[t] < 0) continue;
+        const uint32_t w[4] = {raw[t].x, raw[t].y, raw[t].z, raw[t].w};
+        uint32_t out[2] = {0, 0};
+        if (s[t] > 0.0f) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float lo = __fdiv_rn(__uint_as_float(w[i] << 16), s[t]);
+                const float hi = __fdiv_rn(__uint_as_float(w[i] & 0xffff0000u), s[t]);
+                out[i >> 1] |= uint32_t(__nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3)) << (16 * (i & 1));
+            }
+        }
+        *reinterpret_cast<uint2*>(a.cache[u.which] + (slot[t] * a.n_kv_heads + u.head) * int64_t(kHeadDim) + u.sub * 8) =
+            make_uint2(out[0], out[1]);
+    }
 }
 
 }  // namespace ib
@@ -238,9 +328,11 @@ int infer_kv_append(const infer_kv_pool_t* pool, const void* k, const void* v, i
     const int64_t items = n_tokens * pool->n_kv_heads * 2;
     if (items >= (int64_t(1) << 31)) return INFER_ERR_GEOMETRY;
     ib::fp8_snapshot_kernel<<<unsigned((items + 255) / 256), 256, 0, stream>>>(a);
-    ib::fp8_amax_kernel<<<unsigned((items * 32 + 255) / 256), 256, 0, stream>>>(a);
-    ib::fp8_rescale_kernel<<<unsigned((items * 32 + 255) / 256), 256, 0, stream>>>(a);
-    ib::fp8_write_kernel<<<unsigned((items * 32 + 255) / 256), 256, 0, stream>>>(a);
+    const int64_t units = ((n_tokens + ib::kStrip - 1) / ib::kStrip) * 2 * ((pool->n_kv_heads + 1) / 2);
+    const unsigned strip_blocks = unsigned((units * 32 + 255) / 256);
+    ib::fp8_amax_kernel<<<strip_blocks, 256, 0, stream>>>(a);
+    ib::fp8_rescale_kernel<<<strip_blocks, 256, 0, stream>>>(a);
+    ib::fp8_write_kernel<<<strip_blocks, 256, 0, stream>>>(a);
     return ib::check_launch();
 }
 

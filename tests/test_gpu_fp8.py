@@ -49,6 +49,32 @@ def test_fp8_append_bit_exact(rounds):
     assert bits_equal(cpu[1], gpu[1]), "v bytes differ"
 
 
+@pytest.mark.parametrize("hkv,n_tokens", [(1, 5), (3, 37), (2, 8), (8, 1001)])
+def test_fp8_append_odd_heads_skips_and_strided_rows(hkv, n_tokens):
+    """Head counts that do not fill a warp's head pair, token counts off the 8-token strip,
+    skipped rows (-1) inside a strip, slots in random order over few pages (many rows per page
+    in one call), rows that are column slices of a wider buffer; two calls so scales grow."""
+    gen = torch.Generator().manual_seed(500 + hkv * 31 + n_tokens)
+    nb = max(2, -(-2 * n_tokens // 200))
+    cpu = _empty_pools(nb, hkv, "cpu")
+    gpu = _empty_pools(nb, hkv, "cuda")
+    all_slots = torch.randperm(nb * 256, generator=gen)[:2 * n_tokens]
+    for call in range(2):
+        slots = all_slots[call * n_tokens:(call + 1) * n_tokens].to(torch.int32)
+        slots[torch.rand(n_tokens, generator=gen) < 0.15] = -1
+        qkv = (torch.randn(n_tokens, 3 * hkv * 128 + 64, generator=gen) * (1 + 4 * call)).bfloat16()
+        k = qkv[:, 64:64 + hkv * 128].view(n_tokens, hkv, 128)
+        v = qkv[:, 64 + hkv * 128:64 + 2 * hkv * 128].view(n_tokens, hkv, 128)
+        oracle.store_kvcache_fp8(k, v, *cpu, slots)
+        qkv_d = qkv.cuda()
+        ops.store_kvcache(qkv_d[:, 64:64 + hkv * 128].view(n_tokens, hkv, 128),
+                          qkv_d[:, 64 + hkv * 128:64 + 2 * hkv * 128].view(n_tokens, hkv, 128),
+                          gpu[0], gpu[1], slots.cuda(), gpu[2], gpu[3])
+    torch.cuda.synchronize()
+    assert torch.equal(cpu[2], gpu[2].cpu()) and torch.equal(cpu[3], gpu[3].cpu()), "scales differ"
+    assert bits_equal(cpu[0], gpu[0]) and bits_equal(cpu[1], gpu[1]), "bytes differ"
+
+
 @pytest.mark.parametrize("impl", ["0", "1"], ids=["tma", "plain-loads"])
 def test_fp8_decode_step(impl, monkeypatch):
     monkeypatch.setenv("INFER_B200_DECODE_IMPL", impl)
