@@ -2,11 +2,11 @@
 //
 // bf16 pools: a pure byte copy, one 16-byte load and one 16-byte store per thread and
 // row chunk, K and V in the same thread, two chunks in flight per thread.
-// e4m3 pools: four kernels (snapshot scales, raise scales by the new rows' amax,
-// re-encode pages whose scale grew, write the new rows) so that the result depends on no
-// scheduling order and matches the CPU oracle bit for bit.  The three row kernels work on
-// strips of 8 tokens per warp: 16-byte loads, 8 in flight per lane, one atomic per run of
-// tokens that share a page.
+// e4m3 pools: a cleared workspace and three kernels (collect the new rows' amax / 448 per
+// (page, head); raise the scales and re-encode pages whose scale grew; write the new rows) so
+// that the result depends on no scheduling order and matches the CPU oracle bit for bit.  The
+// kernels work on strips of 8 tokens per warp: 16-byte loads, 8 in flight per lane, one atomic
+// per run of tokens that share a page.
 #include "common.cuh"
 
 namespace ib {
@@ -50,120 +50,154 @@ __global__ void __launch_bounds__(256) append_bf16_kernel(
 }
 
 // --------------------------------------------------------------------------- e4m3
+struct Fp8Side {
+    const __nv_bfloat16* src;      // new rows
+    int64_t pitch;                 // elements
+    uint8_t* cache;
+    float* scale;                  // [num_blocks, Hkv]
+    float* cand;                   // workspace [num_blocks, Hkv]: this call's amax / 448 per (page, head)
+};
+
 struct Fp8Args {
-    const __nv_bfloat16* src[2];   // k, v
-    int64_t pitch[2];              // elements
-    uint8_t* cache[2];
-    float* scale[2];
-    float* snap[2];                // workspace copies of the scales of touched pages
+    Fp8Side k, v;
     const int32_t* slot_mapping;
     int64_t n_tokens;
     int64_t num_slots;
     int n_kv_heads;
     int block_size;
+    uint64_t page_magic;           // ceil(2^64 / block_size): page = mulhi(slot, page_magic), exact for slot < 2^32
+
+    __device__ __forceinline__ int64_t page_of(int64_t slot) const {
+        return int64_t(__umul64hi(uint64_t(slot), page_magic));
+    }
 };
 
-__device__ __forceinline__ bool fp8_locate(const Fp8Args& a, int64_t item, int& which, int64_t& tok, int& head,
-                                           int64_t& slot) {
-    // item = (tok * Hkv + head) * 2 + which
-    which = int(item & 1);
-    const int64_t th = item >> 1;
-    tok = th / a.n_kv_heads;
-    head = int(th - tok * a.n_kv_heads);
-    slot = a.slot_mapping[tok];
-    return slot >= 0 && slot < a.num_slots;
-}
-
-__global__ void fp8_snapshot_kernel(Fp8Args a) {
-    const int64_t item = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (item >= a.n_tokens * a.n_kv_heads * 2) return;
-    int which, head;
-    int64_t tok, slot;
-    if (!fp8_locate(a, item, which, tok, head, slot)) return;
-    const int64_t e = (slot / a.block_size) * a.n_kv_heads + head;
-    a.snap[which][e] = a.scale[which][e];
-}
-
-// Work unit of the three row kernels below: kStrip consecutive tokens x (k|v) x a pair of KV
-// heads.  One warp per unit: lane / 16 picks the head of the pair, lane % 16 the 16-byte chunk
-// of its 128-element row, so a warp reads 512 contiguous bytes per token and keeps kStrip
-// loads in flight per lane.  Consecutive tokens mostly share a page, which lets the half-warp
-// issue one atomic (amax) or one claim test (rescale) per run of equal pages, not per row.
+// Work unit of the three kernels below: a strip of kStrip consecutive tokens x (k|v) x a pair
+// of KV heads.  blockIdx.y fixes (k|v, head pair); the warps of a grid row walk the strips with
+// a warp stride.  lane / 16 picks the head of the pair, lane % 16 the 16-byte chunk of its
+// 128-element row, so a warp reads 512 contiguous bytes per token and keeps kStrip loads in
+// flight per lane, and fetches the next strip's slots while the current strip's rows are in
+// flight.  All lanes of a warp see the same tokens, so every branch on a page number is
+// warp-uniform; consecutive tokens mostly share a page, which lets the warp do one reduction
+// and one atomic (amax), one claim (rescale) or one reciprocal (write) per run of equal
+// pages, not per row.
 constexpr int kStrip = 8;
+constexpr int kWarpsPerCta = 8;
 
-struct StripUnit {
-    int which, head, sub;
-    int64_t tok0;
-    bool active;
+struct StripLane {
+    Fp8Side side;
+    const __nv_bfloat16* src;      // this lane's 8 elements of token 0
+    int head, sub;
+    bool active;                   // false: the odd head of the last pair when Hkv is odd
 };
 
-__device__ __forceinline__ int64_t strip_units(const Fp8Args& a) {
-    return ((a.n_tokens + kStrip - 1) / kStrip) * 2 * ((a.n_kv_heads + 1) / 2);
-}
-
-__device__ __forceinline__ StripUnit strip_locate(const Fp8Args& a, int64_t unit, int lane) {
-    const int pairs = (a.n_kv_heads + 1) / 2;
-    StripUnit u;
-    u.which = int(unit & 1);
-    const int64_t sp = unit >> 1;
-    const int64_t strip = sp / pairs;
-    u.head = int(sp - strip * pairs) * 2 + (lane >> 4);
+__device__ __forceinline__ StripLane strip_lane(const Fp8Args& a, int lane) {
+    StripLane u;
+    u.side = (blockIdx.y & 1) ? a.v : a.k;          // selected by value: no indexed access to the parameter block
+    u.head = int(blockIdx.y >> 1) * 2 + (lane >> 4);
     u.sub = lane & 15;
-    u.tok0 = strip * kStrip;
     u.active = u.head < a.n_kv_heads;
+    u.src = u.side.src + u.head * kHeadDim + u.sub * 8;
     return u;
 }
 
-__device__ __forceinline__ float amax8(const uint4& r) {
-    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
-    float m = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        // a bf16 is the upper half of the fp32 with the same value
-        m = fmaxf(m, fmaxf(fabsf(__uint_as_float(w[i] << 16)), fabsf(__uint_as_float(w[i] & 0xffff0000u))));
+// Raw slots of a strip's tokens (not yet range-checked); -1 for rows or strips beyond the call.
+// Full strips of a 16-byte aligned slot_mapping come in as two 16-byte loads.
+__device__ __forceinline__ void strip_slots(const Fp8Args& a, int64_t strip, int64_t strips, int (&slot)[kStrip]) {
+    const int64_t tok0 = strip * kStrip;
+    if (strip < strips && tok0 + kStrip <= a.n_tokens && (reinterpret_cast<uintptr_t>(a.slot_mapping) & 15) == 0) {
+        const int4 lo = __ldg(reinterpret_cast<const int4*>(a.slot_mapping + tok0));
+        const int4 hi = __ldg(reinterpret_cast<const int4*>(a.slot_mapping + tok0) + 1);
+        slot[0] = lo.x; slot[1] = lo.y; slot[2] = lo.z; slot[3] = lo.w;
+        slot[4] = hi.x; slot[5] = hi.y; slot[6] = hi.z; slot[7] = hi.w;
+        return;
     }
-    return m;
+#pragma unroll
+    for (int t = 0; t < kStrip; ++t) {
+        slot[t] = -1;
+        if (strip < strips && tok0 + t < a.n_tokens) slot[t] = __ldg(a.slot_mapping + tok0 + t);
+    }
 }
 
-// scale[page, head] = max(scale, amax(rows of this call on that page) / 448)
-__global__ void __launch_bounds__(256) fp8_amax_kernel(Fp8Args a) {
-    const int64_t unit = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-    if (unit >= strip_units(a)) return;
+// True when the strip's tokens go to kStrip consecutive slots of one page (the usual case in
+// a prefill chunk); page receives that page.  Warp-uniform.
+__device__ __forceinline__ bool strip_is_one_run(const Fp8Args& a, const int (&slot)[kStrip], int64_t& page) {
+    bool run = slot[0] >= 0 && int64_t(slot[0]) + kStrip <= a.num_slots;
+#pragma unroll
+    for (int t = 1; t < kStrip; ++t) run = run && slot[t] == slot[0] + t;
+    if (!run) return false;
+    page = a.page_of(slot[0]);
+    return a.page_of(slot[0] + kStrip - 1) == page;
+}
+
+// general path: out-of-range slots become -1
+__device__ __forceinline__ void strip_normalise(const Fp8Args& a, int (&slot)[kStrip]) {
+#pragma unroll
+    for (int t = 0; t < kStrip; ++t) slot[t] = (slot[t] >= 0 && slot[t] < a.num_slots) ? slot[t] : -1;
+}
+
+__device__ __forceinline__ uint4 strip_row(const StripLane& u, int64_t tok) {
+    return __ldg(reinterpret_cast<const uint4*>(u.src + tok * u.side.pitch));
+}
+
+// largest magnitude of 8 bf16 values, as a bf16 pair (maxNum semantics: a NaN operand is dropped)
+__device__ __forceinline__ __nv_bfloat162 amax8(const uint4& r) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+    return __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
+}
+
+// half-warp reduction of a row maximum, then one atomic per (page, head) by the half-warp's leader
+__device__ __forceinline__ void amax_flush(const Fp8Args& a, const StripLane& u, int64_t page, __nv_bfloat162 best) {
+    float m = fmaxf(__low2float(best), __high2float(best));
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (u.sub == 0 && u.active && m > 0.0f)   // non-negative floats order like their bit patterns
+        atomicMax(reinterpret_cast<int*>(u.side.cand + page * a.n_kv_heads + u.head), __float_as_int(__fdiv_rn(m, 448.0f)));
+}
+
+// cand[page, head] = max over this call's rows on that page of amax(row) / 448
+__global__ void __launch_bounds__(256, 3) fp8_amax_kernel(Fp8Args a) {
+    const int64_t strips = (a.n_tokens + kStrip - 1) / kStrip;
+    const int64_t stride = int64_t(gridDim.x) * kWarpsPerCta;
     const int lane = threadIdx.x & 31;
-    const StripUnit u = strip_locate(a, unit, lane);
-    int64_t page[kStrip];
-    uint4 raw[kStrip];
+    const StripLane u = strip_lane(a, lane);
+    int64_t strip = int64_t(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
+    int next[kStrip];
+    strip_slots(a, strip, strips, next);
+    for (; strip < strips; strip += stride) {
+        int slot[kStrip];
 #pragma unroll
-    for (int t = 0; t < kStrip; ++t) {
-        const int64_t tok = u.tok0 + t;
-        int64_t slot = -1;
-        if (tok < a.n_tokens) slot = a.slot_mapping[tok];
-        const bool ok = u.active && slot >= 0 && slot < a.num_slots;
-        page[t] = ok ? slot / a.block_size : -1;
-        raw[t] = make_uint4(0, 0, 0, 0);
-        if (ok) raw[t] = __ldg(reinterpret_cast<const uint4*>(a.src[u.which] + tok * a.pitch[u.which] + u.head * kHeadDim) + u.sub);
-    }
-    float m[kStrip];
+        for (int t = 0; t < kStrip; ++t) slot[t] = next[t];
+        int64_t page;
+        const bool one_run = strip_is_one_run(a, slot, page);
+        if (!one_run) strip_normalise(a, slot);
+        uint4 raw[kStrip];
 #pragma unroll
-    for (int t = 0; t < kStrip; ++t) {
-        m[t] = amax8(raw[t]);
-#pragma unroll
-        for (int o = 8; o > 0; o >>= 1) m[t] = fmaxf(m[t], __shfl_xor_sync(0xffffffffu, m[t], o));
-    }
-    if (u.sub != 0 || !u.active) return;
-    int64_t cur = -1;
-    float best = 0.0f;
-#pragma unroll
-    for (int t = 0; t <= kStrip; ++t) {
-        const int64_t p = t < kStrip ? page[t] : -2;
-        if (p != cur) {
-            if (cur >= 0)   // non-negative floats order like their bit patterns
-                atomicMax(reinterpret_cast<int*>(a.scale[u.which] + cur * a.n_kv_heads + u.head),
-                          __float_as_int(__fdiv_rn(best, 448.0f)));
-            cur = p;
-            best = 0.0f;
+        for (int t = 0; t < kStrip; ++t) {
+            raw[t] = make_uint4(0, 0, 0, 0);
+            if (u.active && (one_run || slot[t] >= 0)) raw[t] = strip_row(u, strip * kStrip + t);
         }
-        if (t < kStrip) best = fmaxf(best, m[t]);
+        strip_slots(a, strip + stride, strips, next);
+        const __nv_bfloat162 zero = __float2bfloat162_rn(0.0f);
+        if (one_run) {
+            __nv_bfloat162 best = zero;
+#pragma unroll
+            for (int t = 0; t < kStrip; ++t) best = __hmax2(best, amax8(raw[t]));
+            amax_flush(a, u, page, best);
+            continue;
+        }
+        int64_t cur = -1;
+        __nv_bfloat162 best = zero;
+#pragma unroll
+        for (int t = 0; t <= kStrip; ++t) {
+            const int64_t p = t < kStrip ? (slot[t] >= 0 ? a.page_of(slot[t]) : -1) : -2;
+            if (p != cur) {                            // warp-uniform
+                if (cur >= 0) amax_flush(a, u, cur, best);
+                cur = p;
+                best = zero;
+            }
+            if (t < kStrip) best = __hmax2(best, amax8(raw[t]));
+        }
     }
 }
 
@@ -179,88 +213,170 @@ __device__ __forceinline__ uint32_t rescale4(uint32_t q, float ratio) {
     return out;
 }
 
-// The first half-warp to claim a (page, head) whose scale grew re-encodes all of that page's
-// rows for that head (rare: most half-warps leave after two loads per distinct page).
-__global__ void __launch_bounds__(256) fp8_rescale_kernel(Fp8Args a) {
-    const int64_t unit = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-    if (unit >= strip_units(a)) return;
-    const int lane = threadIdx.x & 31;
-    const StripUnit u = strip_locate(a, unit, lane);
-    const unsigned half_mask = 0xffffu << (lane & 16);
-    int64_t cur = -1;
-    for (int t = 0; t < kStrip; ++t) {
-        const int64_t tok = u.tok0 + t;
-        int64_t slot = -1;
-        if (tok < a.n_tokens) slot = a.slot_mapping[tok];
-        const bool ok = u.active && slot >= 0 && slot < a.num_slots;
-        const int64_t page = ok ? slot / a.block_size : -1;
-        if (page == cur || page < 0) continue;        // uniform within the half-warp
-        cur = page;
-        const int64_t e = page * a.n_kv_heads + u.head;
-        float ratio = -1.0f;
-        if (u.sub == 0) {
-            const float now = a.scale[u.which][e];
-            const float seen = a.snap[u.which][e];
-            if (seen > 0.0f && now > seen) {                       // a candidate: claim it exactly once
-                const float old = atomicExch(a.snap[u.which] + e, -1.0f);
-                if (old > 0.0f) ratio = __fdiv_rn(old, now);
+// The start of a run of tokens on `page`: the half-warp whose leader takes the candidate out
+// of the workspace (exactly one per touched (page, head), however many runs the page has)
+// raises the scale and, when a positive scale grew, re-encodes that page's rows for that head.
+__device__ __forceinline__ void rescale_claim(const Fp8Args& a, const StripLane& u, int64_t page, int lane) {
+    const int64_t e = page * a.n_kv_heads + u.head;
+    float ratio = -1.0f;
+    if (u.sub == 0 && u.active) {
+        const float c = atomicExch(u.side.cand + e, 0.0f);
+        if (c > 0.0f) {
+            const float old = u.side.scale[e];
+            if (c > old) {
+                u.side.scale[e] = c;
+                if (old > 0.0f) ratio = __fdiv_rn(old, c);
             }
         }
-        ratio = __shfl_sync(half_mask, ratio, lane & 16);
-        if (ratio < 0.0f) continue;
-        // rows of this head: block_size rows of 128 bytes, pitch Hkv * 128
-        uint8_t* base = a.cache[u.which] + (page * a.block_size * a.n_kv_heads + u.head) * int64_t(kHeadDim);
-        const int64_t pitch = int64_t(a.n_kv_heads) * kHeadDim;
-        for (int i = u.sub; i < a.block_size * 8; i += 16) {
-            uint4* p = reinterpret_cast<uint4*>(base + (i >> 3) * pitch + (i & 7) * 16);
-            uint4 q = *p;
-            q.x = rescale4(q.x, ratio);
-            q.y = rescale4(q.y, ratio);
-            q.z = rescale4(q.z, ratio);
-            q.w = rescale4(q.w, ratio);
-            *p = q;
+    }
+    ratio = __shfl_sync(0xffffu << (lane & 16), ratio, lane & 16);
+    if (ratio < 0.0f) return;
+    // rows of this head: block_size rows of 128 bytes, pitch Hkv * 128
+    uint8_t* base = u.side.cache + (page * a.block_size * a.n_kv_heads + u.head) * int64_t(kHeadDim);
+    const int64_t pitch = int64_t(a.n_kv_heads) * kHeadDim;
+    for (int i = u.sub; i < a.block_size * 8; i += 16) {
+        uint4* p = reinterpret_cast<uint4*>(base + (i >> 3) * pitch + (i & 7) * 16);
+        uint4 q = *p;
+        q.x = rescale4(q.x, ratio);
+        q.y = rescale4(q.y, ratio);
+        q.z = rescale4(q.z, ratio);
+        q.w = rescale4(q.w, ratio);
+        *p = q;
+    }
+}
+
+// Raises scale[page, head] to the call's candidate; a warp looks at a page only where a run
+// of tokens on that page starts (the token in front maps elsewhere).
+__global__ void __launch_bounds__(256) fp8_rescale_kernel(Fp8Args a) {
+    const int64_t strips = (a.n_tokens + kStrip - 1) / kStrip;
+    const int64_t stride = int64_t(gridDim.x) * kWarpsPerCta;
+    const int lane = threadIdx.x & 31;
+    const StripLane u = strip_lane(a, lane);
+    for (int64_t strip = int64_t(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5); strip < strips; strip += stride) {
+        int slot[kStrip];
+        strip_slots(a, strip, strips, slot);
+        int64_t cur = -1;                              // page of the token in front of the strip
+        if (strip > 0) {
+            const int s = __ldg(a.slot_mapping + strip * kStrip - 1);
+            if (s >= 0 && s < a.num_slots) cur = a.page_of(s);
+        }
+        int64_t page;
+        if (strip_is_one_run(a, slot, page)) {
+            if (page != cur) rescale_claim(a, u, page, lane);
+            continue;
+        }
+        strip_normalise(a, slot);
+#pragma unroll
+        for (int t = 0; t < kStrip; ++t) {
+            page = slot[t] >= 0 ? a.page_of(slot[t]) : -1;
+            const bool starts = page >= 0 && page != cur;   // warp-uniform
+            cur = page;
+            if (starts) rescale_claim(a, u, page, lane);
         }
     }
 }
 
-// quantise the new rows with their page's final scale
-__global__ void __launch_bounds__(256) fp8_write_kernel(Fp8Args a) {
-    const int64_t unit = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-    if (unit >= strip_units(a)) return;
-    const int lane = threadIdx.x & 31;
-    const StripUnit u = strip_locate(a, unit, lane);
-    if (!u.active) return;
-    int64_t slot[kStrip];
-    uint4 raw[kStrip];
-    float s[kStrip];
-#pragma unroll
-    for (int t = 0; t < kStrip; ++t) {
-        const int64_t tok = u.tok0 + t;
-        slot[t] = -1;
-        if (tok < a.n_tokens) slot[t] = a.slot_mapping[tok];
-        if (slot[t] >= a.num_slots) slot[t] = -1;
-        raw[t] = make_uint4(0, 0, 0, 0);
-        s[t] = 0.0f;
-        if (slot[t] >= 0) {
-            raw[t] = __ldg(reinterpret_cast<const uint4*>(a.src[u.which] + tok * a.pitch[u.which] + u.head * kHeadDim) + u.sub);
-            s[t] = a.scale[u.which][(slot[t] / a.block_size) * a.n_kv_heads + u.head];
+__device__ __forceinline__ uint64_t pk2(float a, float b) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t fmul2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
+// x / s, correctly rounded, for numerators that are bf16 values.  With r = RN(1 / s) the
+// sequence q0 = RN(x r), q = RN(q0 + RN(x - s q0) r) returns RN(x / s) for every one of the
+// 128 significands of x and all 2^23 significands of s (checked exhaustively on the host);
+// scales outside [2^-64, 2^64] take the general division.  Quotients too small for the
+// sequence's intermediate results to be normal numbers round to zero in e4m3 either way.
+// Two quotients per instruction (packed fp32 pairs, each half rounded like the scalar form).
+struct Divisor {
+    float s;
+    uint64_t r2, neg_s2;
+    bool fast;
+    __device__ __forceinline__ explicit Divisor(float s_) : s(s_), r2(0), neg_s2(0), fast(s_ >= 0x1p-64f && s_ <= 0x1p64f) {
+        if (fast) {
+            const float r = __frcp_rn(s_);
+            r2 = pk2(r, r);
+            neg_s2 = pk2(-s_, -s_);
         }
     }
-#pragma unroll
-    for (int t = 0; t < kStrip; ++t) {
-        if (slot[t] < 0) continue;
-        const uint32_t w[4] = {raw[t].x, raw[t].y, raw[t].z, raw[t].w};
-        uint32_t out[2] = {0, 0};
-        if (s[t] > 0.0f) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float lo = __fdiv_rn(__uint_as_float(w[i] << 16), s[t]);
-                const float hi = __fdiv_rn(__uint_as_float(w[i] & 0xffff0000u), s[t]);
-                out[i >> 1] |= uint32_t(__nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3)) << (16 * (i & 1));
-            }
+    // a 32-bit word holding two bf16 values -> the two e4m3 bytes of their quotients
+    __device__ __forceinline__ uint32_t quantise2(uint32_t w) const {
+        const float lo = __uint_as_float(w << 16), hi = __uint_as_float(w & 0xffff0000u);
+        float2 q;
+        if (fast) {
+            const uint64_t x2 = pk2(lo, hi);
+            const uint64_t q0 = fmul2(x2, r2);
+            const uint64_t q2 = ffma2(ffma2(neg_s2, q0, x2), r2, q0);
+            asm("mov.b64 {%0, %1}, %2;" : "=f"(q.x), "=f"(q.y) : "l"(q2));
+        } else {
+            q = make_float2(__fdiv_rn(lo, s), __fdiv_rn(hi, s));
         }
-        *reinterpret_cast<uint2*>(a.cache[u.which] + (slot[t] * a.n_kv_heads + u.head) * int64_t(kHeadDim) + u.sub * 8) =
-            make_uint2(out[0], out[1]);
+        return uint32_t(__nv_cvt_float2_to_fp8x2(q, __NV_SATFINITE, __NV_E4M3));
+    }
+    __device__ __forceinline__ uint2 quantise8(const uint4& raw) const {
+        if (!(s > 0.0f)) return make_uint2(0, 0);
+        return make_uint2(quantise2(raw.x) | (quantise2(raw.y) << 16), quantise2(raw.z) | (quantise2(raw.w) << 16));
+    }
+};
+
+// quantise the new rows with their page's final scale
+__global__ void __launch_bounds__(256, 3) fp8_write_kernel(Fp8Args a) {
+    const int64_t strips = (a.n_tokens + kStrip - 1) / kStrip;
+    const int64_t stride = int64_t(gridDim.x) * kWarpsPerCta;
+    const int lane = threadIdx.x & 31;
+    const StripLane u = strip_lane(a, lane);
+    uint8_t* const dst = u.side.cache + u.head * kHeadDim + u.sub * 8;
+    const int64_t dst_pitch = int64_t(a.n_kv_heads) * kHeadDim;
+    int64_t strip = int64_t(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
+    int next[kStrip];
+    strip_slots(a, strip, strips, next);
+    for (; strip < strips; strip += stride) {
+        int slot[kStrip];
+#pragma unroll
+        for (int t = 0; t < kStrip; ++t) slot[t] = next[t];
+        int64_t page;
+        const bool one_run = strip_is_one_run(a, slot, page);
+        if (!one_run) strip_normalise(a, slot);
+        uint4 raw[kStrip];
+#pragma unroll
+        for (int t = 0; t < kStrip; ++t) {
+            raw[t] = make_uint4(0, 0, 0, 0);
+            if (u.active && (one_run || slot[t] >= 0)) raw[t] = strip_row(u, strip * kStrip + t);
+        }
+        // the scale of the strip's first page travels with the rows; later pages (rare) load theirs in the loop
+        int64_t cur = one_run ? page : (slot[0] >= 0 ? a.page_of(slot[0]) : -1);
+        float s = (cur >= 0 && u.active) ? u.side.scale[cur * a.n_kv_heads + u.head] : 0.0f;
+        strip_slots(a, strip + stride, strips, next);
+        Divisor div(s);
+        if (one_run) {
+            if (u.active) {
+                uint8_t* row = dst + slot[0] * dst_pitch;
+#pragma unroll
+                for (int t = 0; t < kStrip; ++t) *reinterpret_cast<uint2*>(row + t * dst_pitch) = div.quantise8(raw[t]);
+            }
+            continue;
+        }
+#pragma unroll
+        for (int t = 0; t < kStrip; ++t) {
+            if (slot[t] < 0) continue;                 // warp-uniform
+            page = a.page_of(slot[t]);
+            if (page != cur) {                         // warp-uniform
+                cur = page;
+                s = u.active ? u.side.scale[cur * a.n_kv_heads + u.head] : 0.0f;
+                div = Divisor(s);
+            }
+            if (u.active) *reinterpret_cast<uint2*>(dst + slot[t] * dst_pitch) = div.quantise8(raw[t]);
+        }
     }
 }
 
@@ -310,29 +426,28 @@ int infer_kv_append(const infer_kv_pool_t* pool, const void* k, const void* v, i
     const size_t need = infer_kv_append_workspace_bytes(pool);
     if (!workspace || workspace_bytes < need || !ib::aligned16(workspace)) return INFER_ERR_WORKSPACE;
     ib::Fp8Args a;
-    a.src[0] = static_cast<const __nv_bfloat16*>(k);
-    a.src[1] = static_cast<const __nv_bfloat16*>(v);
-    a.pitch[0] = k_row_stride;
-    a.pitch[1] = v_row_stride;
-    a.cache[0] = static_cast<uint8_t*>(pool->k_cache);
-    a.cache[1] = static_cast<uint8_t*>(pool->v_cache);
-    a.scale[0] = pool->k_scale;
-    a.scale[1] = pool->v_scale;
-    a.snap[0] = static_cast<float*>(workspace);
-    a.snap[1] = a.snap[0] + pool->num_blocks * pool->n_kv_heads;
+    float* cand = static_cast<float*>(workspace);
+    a.k = {static_cast<const __nv_bfloat16*>(k), k_row_stride, static_cast<uint8_t*>(pool->k_cache), pool->k_scale, cand};
+    a.v = {static_cast<const __nv_bfloat16*>(v), v_row_stride, static_cast<uint8_t*>(pool->v_cache), pool->v_scale,
+           cand + pool->num_blocks * pool->n_kv_heads};
     a.slot_mapping = slot_mapping;
     a.n_tokens = n_tokens;
     a.num_slots = pool->num_slots;
     a.n_kv_heads = pool->n_kv_heads;
     a.block_size = pool->block_size;
-    const int64_t items = n_tokens * pool->n_kv_heads * 2;
-    if (items >= (int64_t(1) << 31)) return INFER_ERR_GEOMETRY;
-    ib::fp8_snapshot_kernel<<<unsigned((items + 255) / 256), 256, 0, stream>>>(a);
-    const int64_t units = ((n_tokens + ib::kStrip - 1) / ib::kStrip) * 2 * ((pool->n_kv_heads + 1) / 2);
-    const unsigned strip_blocks = unsigned((units * 32 + 255) / 256);
-    ib::fp8_amax_kernel<<<strip_blocks, 256, 0, stream>>>(a);
-    ib::fp8_rescale_kernel<<<strip_blocks, 256, 0, stream>>>(a);
-    ib::fp8_write_kernel<<<strip_blocks, 256, 0, stream>>>(a);
+    a.page_magic = ~uint64_t(0) / uint64_t(pool->block_size) + 1;
+    if (pool->num_slots >= (int64_t(1) << 32)) return INFER_ERR_GEOMETRY;
+    const int64_t strips = (n_tokens + ib::kStrip - 1) / ib::kStrip;
+    const int rows = 2 * ((pool->n_kv_heads + 1) / 2);             // grid rows: (k|v) x head pair
+    int64_t per_row = (strips + ib::kWarpsPerCta - 1) / ib::kWarpsPerCta;
+    const int64_t cap = (int64_t(pool->sm_count) * 12 + rows - 1) / rows;
+    if (per_row > cap) per_row = cap;
+    if (rows > 65535) return INFER_ERR_GEOMETRY;
+    const dim3 blocks{unsigned(per_row), unsigned(rows), 1u};
+    IB_CUDA(cudaMemsetAsync(workspace, 0, need, stream));
+    ib::fp8_amax_kernel<<<blocks, 256, 0, stream>>>(a);
+    ib::fp8_rescale_kernel<<<blocks, 256, 0, stream>>>(a);
+    ib::fp8_write_kernel<<<blocks, 256, 0, stream>>>(a);
     return ib::check_launch();
 }
 

@@ -75,6 +75,33 @@ def test_fp8_append_odd_heads_skips_and_strided_rows(hkv, n_tokens):
     assert bits_equal(cpu[0], gpu[0]) and bits_equal(cpu[1], gpu[1]), "bytes differ"
 
 
+def test_fp8_append_extreme_magnitudes():
+    """Rows whose scale lies outside the range of the kernel's short division sequence (tiny,
+    subnormal and huge amplitudes), all-zero rows, and quotients that fall on e4m3 rounding ties."""
+    gen = torch.Generator().manual_seed(77)
+    hkv, nb = 2, 8
+    cpu = _empty_pools(nb, hkv, "cpu")
+    gpu = _empty_pools(nb, hkv, "cuda")
+    amps = [2.0 ** -140, 2.0 ** -120, 2.0 ** -70, 2.0 ** -30, 1.0, 2.0 ** 40, 2.0 ** 70, 2.0 ** 110]
+    for call in range(2):
+        ks, vs, slots = [], [], []
+        for page, amp in enumerate(amps):
+            n = 40
+            grid = torch.randint(-448, 449, (n, hkv, 128), generator=gen).float() / 2     # many exact ties
+            grid[0] = 448.0 if call else 300.0                                            # pins amax; grows on call 2
+            grid[5] = 0.0
+            ks.append((grid * (amp / 448.0)).bfloat16())
+            vs.append((torch.randn(n, hkv, 128, generator=gen) * amp).bfloat16())
+            slots.extend(range(page * 256 + call * 100, page * 256 + call * 100 + n))
+        k, v = torch.cat(ks), torch.cat(vs)
+        s32 = torch.tensor(slots, dtype=torch.int32)
+        oracle.store_kvcache_fp8(k, v, *cpu, s32)
+        ops.store_kvcache(k.cuda(), v.cuda(), gpu[0], gpu[1], s32.cuda(), gpu[2], gpu[3])
+    torch.cuda.synchronize()
+    assert torch.equal(cpu[2], gpu[2].cpu()) and torch.equal(cpu[3], gpu[3].cpu()), "scales differ"
+    assert bits_equal(cpu[0], gpu[0]) and bits_equal(cpu[1], gpu[1]), "bytes differ"
+
+
 @pytest.mark.parametrize("impl", ["0", "1"], ids=["tma", "plain-loads"])
 def test_fp8_decode_step(impl, monkeypatch):
     monkeypatch.setenv("INFER_B200_DECODE_IMPL", impl)
