@@ -248,6 +248,8 @@ __device__ __forceinline__ void rescale_claim(const Fp8Args& a, const StripLane&
 // Raises scale[page, head] to the call's candidate; a warp looks at a page only where a run
 // of tokens on that page starts (the token in front maps elsewhere).
 __global__ void __launch_bounds__(256) fp8_rescale_kernel(Fp8Args a) {
+    pdl_launch_dependents();
+    pdl_wait();                // the candidates of the kernel in front
     const int64_t strips = (a.n_tokens + kStrip - 1) / kStrip;
     const int64_t stride = int64_t(gridDim.x) * kWarpsPerCta;
     const int lane = threadIdx.x & 31;
@@ -331,6 +333,8 @@ struct Divisor {
 
 // quantise the new rows with their page's final scale
 __global__ void __launch_bounds__(256, 3) fp8_write_kernel(Fp8Args a) {
+    pdl_launch_dependents();
+    pdl_wait();                // the final scales and re-encoded pages of the kernel in front
     const int64_t strips = (a.n_tokens + kStrip - 1) / kStrip;
     const int64_t stride = int64_t(gridDim.x) * kWarpsPerCta;
     const int lane = threadIdx.x & 31;
@@ -446,8 +450,8 @@ int infer_kv_append(const infer_kv_pool_t* pool, const void* k, const void* v, i
     const dim3 blocks{unsigned(per_row), unsigned(rows), 1u};
     IB_CUDA(cudaMemsetAsync(workspace, 0, need, stream));
     ib::fp8_amax_kernel<<<blocks, 256, 0, stream>>>(a);
-    ib::fp8_rescale_kernel<<<blocks, 256, 0, stream>>>(a);
-    ib::fp8_write_kernel<<<blocks, 256, 0, stream>>>(a);
+    IB_CUDA(ib::launch_pdl(ib::fp8_rescale_kernel, blocks, dim3(256), 0, stream, a));
+    IB_CUDA(ib::launch_pdl(ib::fp8_write_kernel, blocks, dim3(256), 0, stream, a));
     return ib::check_launch();
 }
 

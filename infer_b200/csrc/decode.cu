@@ -757,24 +757,6 @@ static DecodeConfig decode_config(const infer_kv_pool* pool, int n_q_heads) {
     return c;
 }
 
-// Launch with the programmatic-serialization attribute: the kernel may begin while the one in
-// front of it in the stream drains; it synchronises itself with pdl_wait().
-template <typename... KArgs, typename... Args>
-static cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
-                              Args&&... args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = block;
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
-}
-
 template <int G, bool FP8>
 static void launch_simple(const DecodeParams& p, int grid, cudaStream_t st) {
     set_cuda_error_if(launch_pdl(decode_simple_kernel<G, FP8>, dim3(grid), dim3(128), 0, st, p));
