@@ -1,6 +1,7 @@
 """Host-side logic: workload generators, KV-head sharding, and the 2-rank gather of
 per-shard outputs (gloo on CPU, the oracle standing in for the kernels)."""
 import os
+import socket
 
 import pytest
 import torch
@@ -92,7 +93,9 @@ def _rank_main(rank, world, port, result):
 def test_two_rank_head_sharding_over_gloo():
     ctx = mp.get_context("spawn")
     result = ctx.Queue()
-    port = 29500 + os.getpid() % 2000
+    with socket.socket() as sock:            # a port the kernel reports free right now
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
     procs = [ctx.Process(target=_rank_main, args=(r, 2, port, result)) for r in range(2)]
     for p in procs:
         p.start()
