@@ -41,6 +41,11 @@ sys.path.insert(0, str(ROOT))
 METRIC = "paged decode-attn KV GB/s"
 UNIT = "GB/s"
 BASE_BATCH = 64
+# DRAM traffic figures from the ncu captures summarised under profiles/ (dram__bytes_read.sum +
+# dram__bytes_write.sum of one launch of a small case; each tile is read once, so traffic grows with the
+# units processed): decode_tma_kernel 259.5 MB for 249.9 MB of KV; prefill_tc_kernel 119.0 MB for 4 sequences.
+DECODE_TRAFFIC_PER_KV_BYTE = 259.5 / 249.9
+PREFILL_TRAFFIC_PER_SEQUENCE = 119.0e6 / 4
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -220,7 +225,10 @@ def run_prefill(args):
                    "flops_per_step": flops, "l2": "q + KV read per step exceed L2"},
         "gpu_launches": 2 * args.steps,
         "roofline": {"bound": "tensor", "kernel": "prefill attention kernel", "achieved": achieved, "peak": peak,
-                     "unit": "TFLOP/s", "frac": achieved / peak, "peak_kind": kind, "attn_ms": attn_ms, "traffic": None},
+                     "unit": "TFLOP/s", "frac": achieved / peak, "peak_kind": kind, "attn_ms": attn_ms,
+                     "traffic": PREFILL_TRAFFIC_PER_SEQUENCE * n_seqs,
+                     "traffic_note": "DRAM bytes per launch: ncu capture of a 4-sequence case (103.9 MB read + 15.1 MB "
+                                     "written), scaled by the number of sequences"},
         "append": {"rows": n_tok, "ms": append_ms, "tok_s": n_tok / (append_ms * 1e-3),
                    "gbs": n_tok * w.n_kv_heads * 128 * 2 * 4 / (append_ms * 1e-3) / 1e9},
         "clocks": clocks.summary(),
@@ -417,7 +425,10 @@ def main():
             "gpu_launches": 3 * args.steps,
             "roofline": {"bound": "hbm", "kernel": "decode_tma_kernel + decode_reduce_kernel", "achieved": achieved,
                          "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
-                         "frac_of_8000": achieved / 8000.0, "decode_ms": decode_ms, "traffic": None},
+                         "frac_of_8000": achieved / 8000.0, "decode_ms": decode_ms,
+                         "traffic": kv_bytes * DECODE_TRAFFIC_PER_KV_BYTE,
+                         "traffic_note": "DRAM bytes per decode launch: ncu capture of a batch-16 case (259.5 MB read + "
+                                         "written for 249.9 MB of KV), scaled by KV bytes"},
             "append": {"decode_shape_us": append_ms * 1e3, "decode_shape_tok_s": args.batch * world / (append_ms * 1e-3),
                        "bulk_rows": n_bulk, "bulk_tok_s": n_bulk / (bulk_ms * 1e-3),
                        "bulk_gbs": bulk_bytes / (bulk_ms * 1e-3) / 1e9, "bulk_frac": bulk_bytes / (bulk_ms * 1e-3) / 1e9 / peak},
