@@ -185,6 +185,20 @@ public:
         }
     }
 
+    // A page without token ids (no digest, never shared): for callers that track lengths only.
+    int32_t take_anonymous() {
+        if (free_.empty()) throw std::runtime_error("BlockManager: out of pages");
+        const int32_t id = free_.front();
+        take(id);
+        return id;
+    }
+    // Drops one reference; the page returns to the back of the free list at zero.
+    void release(int32_t block_id) {
+        Block& page = blocks_.at(block_id);
+        if (page.ref_count <= 0) throw std::runtime_error("BlockManager::release: page is not in use");
+        if (--page.ref_count == 0) where_[block_id] = free_.insert(free_.end(), block_id);
+    }
+
     size_t block_size() const { return block_size_; }
     size_t num_free() const { return free_.size(); }
     const std::list<int32_t>& free_block_ids() const { return free_; }

@@ -10,17 +10,24 @@
 // Method names and the config struct follow the reference; every public method takes the
 // pool mutex once (the reference's extend_sequence/prefetch_sequence lock it recursively and
 // deadlock, src/kvcache.cc:73-80,143-149).
+//
+// Pages come from the native BlockManager (block_manager.hpp), so the pool also offers what the
+// reference's Python engine does with its allocator (infer/engine/block_mannager.py:76-133,
+// infer/engine/scheduler.py:24-61): a prompt given by its token ids shares the pages of a known
+// prefix (allocate_prompt), a decoded token seals or opens pages (append_token), and a
+// sequence can give its pages up and take them back later (preempt / resume).
 #pragma once
 
 #include <algorithm>
-#include <deque>
 #include <iostream>
+#include <memory>
 #include <mutex>
 #include <stdexcept>
 #include <string>
 #include <unordered_map>
 #include <vector>
 
+#include "block_manager.hpp"
 #include "infer_b200.h"
 #include "tensor.hpp"
 
@@ -49,7 +56,7 @@ public:
         if (config.block_size == 0 || config.block_size % 256 != 0)
             throw std::invalid_argument("KVCachePool: block_size must be a multiple of 256");
         if (config.head_size != 128) throw std::invalid_argument("KVCachePool: head_size must be 128");
-        for (size_t i = 0; i < config.num_blocks; ++i) free_pages_.push_back(static_cast<int32_t>(i));
+        if (config.num_blocks > 0) pages_.reset(new BlockManager(config.num_blocks, config.block_size));
     }
     ~KVCachePool() {
         for (auto& l : layers_)
@@ -106,8 +113,76 @@ public:
         std::lock_guard<std::mutex> lock(mutex_);
         auto it = sequences_.find(sequence_id);
         if (it == sequences_.end()) return;
-        for (auto p = it->second.pages.rbegin(); p != it->second.pages.rend(); ++p) free_pages_.push_back(*p);
+        give_back(it->second);
         sequences_.erase(it);
+    }
+
+    // ---- sequences known by their token ids: prefix sharing, sealing, preemption
+    // True when a prompt of these tokens fits (counted without sharing, as the reference's
+    // scheduler does before it admits a request, infer/engine/scheduler.py:31).
+    bool can_allocate(const std::vector<int64_t>& token_ids) const {
+        std::lock_guard<std::mutex> lock(mutex_);
+        return pages_ && pages_->num_free() >= (token_ids.size() + config_.block_size - 1) / config_.block_size;
+    }
+    // Creates a sequence from its prompt.  Leading full pages whose content is already cached
+    // are shared; returns the number of tokens whose KV is therefore already in the pool (the
+    // reference's num_cached_tokens: those rows need no append and no prefill compute).
+    size_t allocate_prompt(size_t sequence_id, const std::vector<int64_t>& token_ids) {
+        std::lock_guard<std::mutex> lock(mutex_);
+        if (sequences_.count(sequence_id)) throw std::runtime_error("KVCachePool: sequence exists: " + std::to_string(sequence_id));
+        if (token_ids.empty()) throw std::invalid_argument("KVCachePool::allocate_prompt: empty prompt");
+        Sequence s;
+        s.tokens.token_ids = token_ids;
+        if (!pages_ || !pages_->can_allocate(s.tokens)) throw std::runtime_error("KVCachePool: out of pages");
+        pages_->allocate(s.tokens);
+        s.by_tokens = true;
+        s.length = token_ids.size();
+        const size_t cached = s.tokens.num_cached_tokens;
+        sequences_.emplace(sequence_id, std::move(s));
+        return cached;
+    }
+    bool can_append(size_t sequence_id) const {
+        std::lock_guard<std::mutex> lock(mutex_);
+        const Sequence& s = find(sequence_id);
+        // the next token opens a new page exactly when the current length fills its pages
+        return !(s.length % config_.block_size == 0) || pages_->num_free() >= 1;
+    }
+    // One decoded token: opens a page when the token is the first of one, seals the page with
+    // its digest when the token fills it.
+    void append_token(size_t sequence_id, int64_t token_id) {
+        std::lock_guard<std::mutex> lock(mutex_);
+        Sequence& s = find(sequence_id);
+        if (!s.by_tokens || s.preempted) throw std::runtime_error("KVCachePool::append_token: sequence holds no token pages");
+        if (s.length % config_.block_size == 0 && pages_->num_free() == 0) throw std::runtime_error("KVCachePool: out of pages");
+        s.tokens.append_token(token_id);
+        pages_->may_append(s.tokens);
+        s.length = s.tokens.size();
+    }
+    // Gives up the pages but keeps the tokens (the scheduler's preemption,
+    // infer/engine/scheduler.py:57-61); sealed pages keep their digests while they sit in
+    // the free list, so resume() finds them again unless they were handed out meanwhile.
+    void preempt(size_t sequence_id) {
+        std::lock_guard<std::mutex> lock(mutex_);
+        Sequence& s = find(sequence_id);
+        if (!s.by_tokens) throw std::runtime_error("KVCachePool::preempt: sequence was not created from token ids");
+        if (s.preempted) return;
+        pages_->deallocate(s.tokens);
+        s.preempted = true;
+    }
+    // Takes pages again for a preempted sequence; returns the tokens found cached.
+    size_t resume(size_t sequence_id) {
+        std::lock_guard<std::mutex> lock(mutex_);
+        Sequence& s = find(sequence_id);
+        if (!s.preempted) throw std::runtime_error("KVCachePool::resume: sequence is not preempted");
+        if (!pages_->can_allocate(s.tokens)) throw std::runtime_error("KVCachePool: out of pages");
+        pages_->allocate(s.tokens);
+        s.preempted = false;
+        return s.tokens.num_cached_tokens;
+    }
+    int page_ref_count(int32_t page) const {
+        std::lock_guard<std::mutex> lock(mutex_);
+        if (!pages_) throw std::runtime_error("KVCachePool: no pages");
+        return pages_->ref_count(page);
     }
     // Returns pages a sequence holds beyond ceil(length / block_size) (none are ever taken in
     // advance here, so this only matters after truncate()).
@@ -118,13 +193,14 @@ public:
     void truncate(size_t sequence_id, size_t new_length) {
         std::lock_guard<std::mutex> lock(mutex_);
         Sequence& s = find(sequence_id);
+        if (s.by_tokens) throw std::runtime_error("KVCachePool::truncate: sequence was created from token ids");
         if (new_length < s.length) s.length = new_length;
     }
 
     // ---- paged accessors used to build the step metadata
     std::vector<int32_t> block_table(size_t sequence_id) const {
         std::lock_guard<std::mutex> lock(mutex_);
-        return find(sequence_id).pages;
+        return find(sequence_id).tokens.block_table;
     }
     size_t length(size_t sequence_id) const {
         std::lock_guard<std::mutex> lock(mutex_);
@@ -134,8 +210,8 @@ public:
     int32_t slot_of(size_t sequence_id, size_t pos) const {
         std::lock_guard<std::mutex> lock(mutex_);
         const Sequence& s = find(sequence_id);
-        if (pos >= s.length) throw std::out_of_range("KVCachePool::slot_of: position beyond the sequence");
-        return static_cast<int32_t>(s.pages[pos / config_.block_size] * config_.block_size + pos % config_.block_size);
+        if (pos >= s.length || s.preempted) throw std::out_of_range("KVCachePool::slot_of: position beyond the sequence");
+        return static_cast<int32_t>(s.tokens.block_table[pos / config_.block_size] * config_.block_size + pos % config_.block_size);
     }
     infer_kv_pool_t* handle(size_t layer_idx) const {
         std::lock_guard<std::mutex> lock(mutex_);
@@ -145,7 +221,7 @@ public:
     }
     size_t free_blocks() const {
         std::lock_guard<std::mutex> lock(mutex_);
-        return free_pages_.size();
+        return free_count();
     }
     size_t active_sequences() const {
         std::lock_guard<std::mutex> lock(mutex_);
@@ -156,7 +232,7 @@ public:
 
     void print_memory_stats(std::ostream& os = std::cout) const {
         std::lock_guard<std::mutex> lock(mutex_);
-        const size_t used = config_.num_blocks - free_pages_.size();
+        const size_t used = config_.num_blocks - free_count();
         const size_t page_bytes = config_.block_size * config_.num_heads * config_.head_size * sizeof(T) *
                                   (config_.use_mla ? 1 : 2) * config_.num_layers;
         size_t total_len = 0, max_len = 0;
@@ -175,8 +251,10 @@ public:
 
 private:
     struct Sequence {
-        std::vector<int32_t> pages;
+        PagedSequence tokens;        // block_table always; token_ids only for sequences created from a prompt
         size_t length = 0;
+        bool by_tokens = false;
+        bool preempted = false;
     };
     struct Layer {
         T* k = nullptr;
@@ -201,25 +279,36 @@ private:
         if (it == sequences_.end()) throw std::runtime_error("Sequence ID not found: " + std::to_string(id));
         return it->second;
     }
+    size_t free_count() const { return pages_ ? pages_->num_free() : 0; }
+    void give_back(Sequence& s) {
+        if (s.by_tokens) {
+            if (!s.preempted) pages_->deallocate(s.tokens);
+            return;
+        }
+        std::vector<int32_t>& pages = s.tokens.block_table;
+        for (auto p = pages.rbegin(); p != pages.rend(); ++p) pages_->release(*p);
+        pages.clear();
+    }
     void grow(size_t id, size_t new_length) {
         Sequence& s = sequences_[id];
+        if (s.by_tokens) throw std::runtime_error("KVCachePool: sequence was created from token ids; use append_token");
         if (new_length <= s.length) return;
+        std::vector<int32_t>& pages = s.tokens.block_table;
         const size_t need = (new_length + config_.block_size - 1) / config_.block_size;
-        if (need > s.pages.size() && need - s.pages.size() > free_pages_.size()) {
-            if (s.pages.empty() && s.length == 0) sequences_.erase(id);
+        if (need > pages.size() && need - pages.size() > free_count()) {
+            if (pages.empty() && s.length == 0) sequences_.erase(id);
             throw std::runtime_error("KVCachePool: out of pages");
         }
-        while (s.pages.size() < need) {
-            s.pages.push_back(free_pages_.front());
-            free_pages_.pop_front();
-        }
+        while (pages.size() < need) pages.push_back(pages_->take_anonymous());
         s.length = new_length;
     }
     void trim(Sequence& s) {
+        if (s.by_tokens) return;
+        std::vector<int32_t>& pages = s.tokens.block_table;
         const size_t need = (s.length + config_.block_size - 1) / config_.block_size;
-        while (s.pages.size() > need) {
-            free_pages_.push_back(s.pages.back());
-            s.pages.pop_back();
+        while (pages.size() > need) {
+            pages_->release(pages.back());
+            pages.pop_back();
         }
     }
 
@@ -227,7 +316,7 @@ private:
     void* stream_;
     std::vector<Layer> layers_;
     std::unordered_map<size_t, Sequence> sequences_;
-    std::deque<int32_t> free_pages_;
+    std::unique_ptr<BlockManager> pages_;
     mutable std::mutex mutex_;
 };
 

@@ -109,6 +109,44 @@ static int run_cpu() {
         });
     for (auto& t : ts) t.join();
     EXPECT(big.free_blocks() == 4096 && big.active_sequences() == 0);
+    // ---- pages by token ids: prefix sharing, sealing, preemption (the reference engine's allocator behaviour)
+    {
+        KVCachePool<bfloat16> shared(KVCachePoolConfig(256, 128, 8, 1, false, 8));
+        std::vector<int64_t> prompt(600);
+        for (size_t i = 0; i < prompt.size(); ++i) prompt[i] = int64_t(i * 7 + 3);
+        EXPECT(shared.can_allocate(prompt));
+        EXPECT(shared.allocate_prompt(1, prompt) == 0);
+        EXPECT(shared.allocate_prompt(2, prompt) == 512);                            // two full pages found by digest
+        EXPECT((shared.block_table(1) == std::vector<int32_t>{0, 1, 2}));
+        EXPECT((shared.block_table(2) == std::vector<int32_t>{0, 1, 3}));            // the open tail page is never shared
+        EXPECT(shared.page_ref_count(0) == 2 && shared.page_ref_count(1) == 2 && shared.page_ref_count(2) == 1);
+        EXPECT(shared.free_blocks() == 4 && shared.length(2) == 600);
+        EXPECT(throws([&] { shared.allocate_prompt(2, prompt); }, "exists"));
+        EXPECT(throws([&] { shared.extend_sequence(1, 700); }, "token ids"));
+        // decode: 168 tokens fill page 3 (sealed at 768), the 169th opens a new page
+        for (int i = 0; i < 168; ++i) shared.append_token(2, 9000 + i);
+        EXPECT(shared.length(2) == 768 && shared.block_table(2).size() == 3);
+        EXPECT(shared.can_append(2));
+        shared.append_token(2, 1);
+        EXPECT(shared.block_table(2).size() == 4 && shared.block_table(2)[3] == 4 && shared.free_blocks() == 3);
+        EXPECT(shared.slot_of(2, 768) == 4 * 256);
+        // preemption gives the pages up; shared pages stay with sequence 1; resuming finds all three sealed pages again
+        shared.preempt(2);
+        EXPECT(shared.free_blocks() == 5 && shared.page_ref_count(0) == 1);
+        EXPECT(throws([&] { shared.slot_of(2, 0); }, "beyond"));
+        EXPECT(shared.resume(2) == 768);
+        EXPECT((shared.block_table(2)[0] == 0) && (shared.block_table(2)[1] == 1) && (shared.block_table(2)[2] == 3));
+        EXPECT(shared.page_ref_count(0) == 2 && shared.free_blocks() == 3);
+        // a different prompt that fits nowhere
+        std::vector<int64_t> big_prompt(256 * 4, 5);
+        EXPECT(!shared.can_allocate(big_prompt));
+        EXPECT(throws([&] { shared.allocate_prompt(3, big_prompt); }, "out of pages"));
+        shared.free_sequence(1);
+        shared.free_sequence(2);
+        EXPECT(shared.free_blocks() == 8 && shared.active_sequences() == 0);
+        // digests survive in the free list: the same prompt is served from cache again
+        EXPECT(shared.allocate_prompt(4, prompt) == 512);
+    }
     std::printf("surface cpu ok\n");
     return 0;
 }
