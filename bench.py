@@ -109,8 +109,13 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def build_workload(world: int, rank: int, device, base_batch: int = BASE_BATCH):
+def build_workload(world: int, rank: int, device, base_batch: int = BASE_BATCH, kind: str = "decode"):
     from infer_b200 import workloads
+    if kind == "long":
+        # the long-context scale-out configuration: batch 256 on every GPU count, the 8 KV heads
+        # (and their 8 query heads each) sharded world ways, page ids replicated
+        return workloads.config4(device=device, seed=1004, n_kv_heads=8 // world, n_q_heads=64 // world,
+                                 tensor_seed=1004 + rank)
     return workloads.config1(device=device, seed=1001, batch=base_batch * world, n_kv_heads=8 // world,
                              n_q_heads=32 // world, tensor_seed=1001 + rank)
 
@@ -246,9 +251,11 @@ def main():
     ap.add_argument("--profile", action="store_true",
                     help="short run for profiler captures: no end-to-end leg, no CPU baseline, no padding of the "
                          "clock-sampling window, 3 bulk appends")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "long"],
                     help="decode = the headline append + paged decode step; prefill = the paged chunked-prefill "
-                         "configuration (16 sequences, prefix U[0,4096], chunk 2048), single GPU")
+                         "configuration (16 sequences, prefix U[0,4096], chunk 2048), single GPU; long = the "
+                         "long-context scale-out configuration (batch 256, 64q/8kv heads, ctx lognormal capped at "
+                         "32768, half the batch sharing a 2048-token prefix), strong scaling over KV heads")
     ap.add_argument("--batch", type=int, default=BASE_BATCH,
                     help="sequences per GPU share (default 64 = the benchmark configuration; smaller values "
                          "give the small case used for profiler captures)")
@@ -279,7 +286,7 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
 
-    w = build_workload(world, rank, device, args.batch)
+    w = build_workload(world, rank, device, args.batch, args.workload)
     cl = w.context_lens_tensor().to(device)
     bt = w.block_tables_tensor().to(device)
     slots = w.slot_mapping.to(device)
@@ -395,14 +402,33 @@ def main():
     torch.cuda.synchronize()
     bulk_ms = a0.elapsed_time(a1) / reps
     bulk_bytes = n_bulk * hkv * 128 * 2 * (2 + 2)
+    del bk, bv, bslots
+
+    # ---- a second bulk point: 262144 rows (every row of 1024 pages), when the pool has them
+    n_bulk2, bulk2_ms = 262144, 0.0
+    if not args.profile and w.num_blocks * 256 >= n_bulk2:
+        bk = torch.randn(n_bulk2, hkv, 128, generator=gen, device=device).bfloat16()
+        bv = torch.randn(n_bulk2, hkv, 128, generator=gen, device=device).bfloat16()
+        bslots = torch.randperm(w.num_blocks * 256, generator=gen, device=device)[:n_bulk2].to(torch.int32)
+        for _ in range(2):
+            ops.store_kvcache(bk, bv, w.k_cache, w.v_cache, bslots)
+        torch.cuda.synchronize()
+        a0.record(stream)
+        for _ in range(5):
+            ops.store_kvcache(bk, bv, w.k_cache, w.v_cache, bslots)
+        a1.record(stream)
+        torch.cuda.synchronize()
+        bulk2_ms = a0.elapsed_time(a1) / 5
+        del bk, bv, bslots
+    bulk2_bytes = n_bulk2 * hkv * 128 * 2 * (2 + 2)
 
     # ---- max over ranks
-    t = torch.tensor([total_ms, decode_ms, append_ms, e2e_ms, bulk_ms], device=device, dtype=torch.float64)
+    t = torch.tensor([total_ms, decode_ms, append_ms, e2e_ms, bulk_ms, bulk2_ms], device=device, dtype=torch.float64)
     b = torch.tensor([float(kv_bytes)], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dist.all_reduce(b, op=dist.ReduceOp.SUM)
-    total_ms, decode_ms, append_ms, e2e_ms, bulk_ms = t.tolist()
+    total_ms, decode_ms, append_ms, e2e_ms, bulk_ms, bulk2_ms = t.tolist()
     job_bytes = b.item()
 
     if rank == 0:
@@ -410,14 +436,23 @@ def main():
         step_ms = total_ms / args.steps
         value = job_bytes / (step_ms * 1e-3) / 1e9
         achieved = kv_bytes / (decode_ms * 1e-3) / 1e9
+        n_seq = len(w.context_lens)
+        if args.workload == "long":
+            desc = (f"qwen3-32b long-context decode: batch {n_seq}, ctx lognormal(median 4096, sigma 0.8) capped at 32768, "
+                    f"half the batch sharing the pages of a 2048-token prefix, 64q/8kv heads sharded {world}-way by KV "
+                    "head, page 256, 1 appended token per sequence; KV bytes count a shared page once")
+        else:
+            desc = (f"qwen3-8b decode shape: batch {n_seq}, ctx U[512,8192], 32q/8kv heads "
+                    f"sharded {world}-way by KV head, page 256, 1 appended token per sequence")
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
+            "scaling": "strong" if args.workload == "long" else "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"qwen3-8b decode shape: batch {args.batch * world}, ctx U[512,8192], 32q/8kv heads "
-                                   f"sharded {world}-way by KV head, page 256, 1 appended token per sequence",
-                       "global_batch": args.batch * world, "kv_bytes_per_gpu": kv_bytes,
-                       "l2": "KV per step (1.1 GB per GPU) exceeds L2 (126 MB); no flush needed",
+            "config": {"workload": desc,
+                       "global_batch": n_seq, "kv_bytes_per_gpu": kv_bytes,
+                       "kv_bytes_per_gpu_logical": w.kv_bytes(unique=False),
+                       "l2": f"KV per step ({kv_bytes / 1e9:.1f} GB per GPU) exceeds L2 (126 MB); no flush needed",
                        "parallelism": f"kv-head-shard{world}"},
             "e2e": {"value": job_bytes / (e2e_ms / args.steps * 1e-3) / 1e9, "unit": UNIT,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps,
@@ -429,9 +464,12 @@ def main():
                          "traffic": kv_bytes * DECODE_TRAFFIC_PER_KV_BYTE,
                          "traffic_note": "DRAM bytes per decode launch: ncu capture of a batch-16 case (259.5 MB read + "
                                          "written for 249.9 MB of KV), scaled by KV bytes"},
-            "append": {"decode_shape_us": append_ms * 1e3, "decode_shape_tok_s": args.batch * world / (append_ms * 1e-3),
+            "append": {"decode_shape_us": append_ms * 1e3, "decode_shape_tok_s": n_seq / (append_ms * 1e-3),
                        "bulk_rows": n_bulk, "bulk_tok_s": n_bulk / (bulk_ms * 1e-3),
-                       "bulk_gbs": bulk_bytes / (bulk_ms * 1e-3) / 1e9, "bulk_frac": bulk_bytes / (bulk_ms * 1e-3) / 1e9 / peak},
+                       "bulk_gbs": bulk_bytes / (bulk_ms * 1e-3) / 1e9, "bulk_frac": bulk_bytes / (bulk_ms * 1e-3) / 1e9 / peak,
+                       "bulk2_rows": n_bulk2 if bulk2_ms else 0,
+                       "bulk2_tok_s": n_bulk2 / (bulk2_ms * 1e-3) if bulk2_ms else None,
+                       "bulk2_gbs": bulk2_bytes / (bulk2_ms * 1e-3) / 1e9 if bulk2_ms else None},
             "clocks": clocks.summary(),
         }
         if not args.no_cpu_baseline and not args.profile and world == 1:

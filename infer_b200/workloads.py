@@ -210,9 +210,11 @@ def config3(device="cpu", seed=1003):
     return w
 
 
-def config4(device="cpu", seed=1004, batch=256, cap=32768, with_pool=True):
+def config4(device="cpu", seed=1004, batch=256, cap=32768, with_pool=True, n_kv_heads=8, n_q_heads=64,
+            tensor_seed=None):
     """Qwen3-32B long-context shape: Hq64/Hkv8, ctx lognormal(median 4096, sigma 0.8) capped
-    at 32768; the first half of the batch shares the pages of a 2048-token prefix."""
+    at 32768; the first half of the batch shares the pages of a 2048-token prefix.
+    ``n_kv_heads``/``n_q_heads`` below 8/64 build one KV-head shard directly (see config1)."""
     rng = np.random.default_rng(seed)
     lens = np.minimum(cap, np.floor(rng.lognormal(math.log(4096), 0.8, size=batch))).astype(np.int64)
     n_shared = batch // 2
@@ -220,8 +222,8 @@ def config4(device="cpu", seed=1004, batch=256, cap=32768, with_pool=True):
     lens = np.maximum(lens, 2)
     pages = sum(-(-int(n) // BLOCK_SIZE) for n in lens)
     num_blocks = max(pages, math.ceil(1.1 * int(lens.sum()) / BLOCK_SIZE))
-    return _decode_workload("qwen3-32b-long-decode", seed, 64, 8, lens, num_blocks, device,
-                            shared_prefix=2048, n_shared=n_shared, with_pool=with_pool)
+    return _decode_workload("qwen3-32b-long-decode", seed, n_q_heads, n_kv_heads, lens, num_blocks, device,
+                            shared_prefix=2048, n_shared=n_shared, with_pool=with_pool, tensor_seed=tensor_seed)
 
 
 CONFIGS = [config0, config1, config2, config3, config4]
