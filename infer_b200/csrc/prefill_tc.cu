@@ -288,18 +288,40 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
         // ================================================================= MMA issue
         // Order on the tensor core: S_0(0) S_1(0), then per key tile j: PV_0(j) S_0(j+1) PV_1(j) S_1(j+1).
         // tcgen05 operations of one thread execute in order, which is what lets P reuse columns
-        // of S (S_i(j+1) is behind PV_i(j)) and makes the final commit cover everything.
+        // of S (S_i(j+1) is behind PV_i(j)) and makes the final commit cover everything.  One
+        // issuing thread also keeps the two softmax warpgroups half a period apart.  What this
+        // warp does between two issues costs tensor-core time, so the waits for the next
+        // iteration's K and V tiles are taken while the products of tile 0 execute, and the
+        // descriptors are the stage's base descriptor plus a constant.
         constexpr uint32_t idesc_s = tc_idesc(false), idesc_pv = tc_idesc(true);
-        auto issue_s = [&](int i, int j) {       // S_i = Q_i K_j^T  (K_FULL of tile j already awaited)
+        const int kt0 = tile[0].n_kt, kt1 = tile[1].n_kt;
+        // descriptors differ from operand tile to operand tile only in the 14-bit start address
+        // (16-byte units) at the bottom of the low word
+        const uint64_t q_desc0 = tc_desc(base + TcSmem::q, 16);
+        const uint64_t k_desc0 = tc_desc(base + TcSmem::k, 16), v_desc0 = tc_desc(base + TcSmem::v, kTcHalf);
+        auto issue_s = [&](int i, int stage) {     // S_i = Q_i K^T  (K_FULL of that stage already awaited)
             if (lane == 0) {
-                const uint32_t q_addr = base + TcSmem::q + i * kTcTile;
-                const uint32_t k_addr = base + TcSmem::k + (j % kTcKStages) * kTcTile;
+                const uint64_t qd = q_desc0 + uint64_t(i * (kTcTile >> 4));
+                const uint64_t kd = k_desc0 + uint64_t(stage * (kTcTile >> 4));
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
-                    const uint32_t off = (kk >> 2) * kTcHalf + (kk & 3) * 32;
-                    tc_mma(tmem + i * 128, tc_desc(q_addr + off, 16), tc_desc(k_addr + off, 16), idesc_s, kk > 0);
+                    const uint32_t off = ((kk >> 2) * kTcHalf + (kk & 3) * 32) >> 4;
+                    tc_mma(tmem + i * 128, qd + off, kd + off, idesc_s, kk > 0);
                 }
                 tc_commit(bar(S_FULL, i));
+            }
+            __syncwarp();
+        };
+        auto issue_pv = [&](int i, int stage, bool first) {   // O_i += P_i V  (P_FULL and V_FULL already awaited)
+            tc_fence_after();
+            if (lane == 0) {
+                const uint64_t vd = v_desc0 + uint64_t(stage * (kTcTile >> 4));
+                const uint32_t p_tmem = tmem + i * 128 + kTmemPinS;
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk)     // 16 keys: 8 packed columns of P, 16 rows of V
+                    tc_mma_ts(tmem + kTmemO + i * 128, p_tmem + kk * 8, vd + uint32_t(kk * 16 * 128 >> 4), idesc_pv,
+                              (!first || kk > 0) ? 1u : 0u);
+                tc_commit(bar(PV_DONE, i));
             }
             __syncwarp();
         };
@@ -307,50 +329,54 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
         if (ok && !tc_wait(bar(K_FULL, 0), 0, s_abort)) ok = false;
         if (ok) {
             tc_fence_after();
-            for (int i = 0; i < kTcQTiles; ++i)
-                if (tile[i].n_kt > 0) issue_s(i, 0);
+            issue_s(0, 0);
+            if (kt1 > 0) issue_s(1, 0);
             if (lane == 0) tc_commit(bar(K_EMPTY, 0));
             __syncwarp();
         }
+        int vs = 0, vph = 0;                                           // stage and phase of V_j
+        int ks = 1 % kTcKStages, kph = (1 / kTcKStages) & 1;           // stage and phase of K_{j+1}
+        bool v_here = false, k_here = false;                          // already seen complete by an early test
         for (int j = 0; j < n_max && ok; ++j) {
-            if (!tc_wait(bar(V_FULL, j % kTcVStages), (j / kTcVStages) & 1, s_abort)) { ok = false; break; }
-            if (PAGED && j == n_max - 1) {
+            const bool next = j + 1 < n_max;
+            if (!v_here && !tc_wait(bar(V_FULL, vs), vph, s_abort)) { ok = false; break; }
+            if (next && !k_here && !tc_wait(bar(K_FULL, ks), kph, s_abort)) { ok = false; break; }
+            if (PAGED && !next) {
                 // keys past the end of the context: P is 0 there, but 0 * (stale bytes) must not
                 // produce NaN, so clear those V rows before the tensor core reads them
                 const int valid = lk - j * kTcKeys;
                 if (valid < kTcKeys) {
-                    uint8_t* vt = smem + TcSmem::v + (j % kTcVStages) * kTcTile;
-                    for (int i = valid * 8 + lane; i < kTcKeys * 8; i += 32) {
-                        *reinterpret_cast<uint4*>(vt + i * 16) = make_uint4(0, 0, 0, 0);
-                        *reinterpret_cast<uint4*>(vt + kTcHalf + i * 16) = make_uint4(0, 0, 0, 0);
+                    uint8_t* vt = smem + TcSmem::v + vs * kTcTile;
+                    for (int x = valid * 8 + lane; x < kTcKeys * 8; x += 32) {
+                        *reinterpret_cast<uint4*>(vt + x * 16) = make_uint4(0, 0, 0, 0);
+                        *reinterpret_cast<uint4*>(vt + kTcHalf + x * 16) = make_uint4(0, 0, 0, 0);
                     }
                     fence_proxy_async();
                     __syncwarp();
                 }
             }
-            const bool next = j + 1 < n_max;
-            if (next && !tc_wait(bar(K_FULL, (j + 1) % kTcKStages), ((j + 1) / kTcKStages) & 1, s_abort)) { ok = false; break; }
-            for (int i = 0; i < kTcQTiles && ok; ++i) {
-                if (j >= tile[i].n_kt) continue;
-                if (!tc_wait(bar(P_FULL, i), j & 1, s_abort)) { ok = false; break; }
-                tc_fence_after();
-                if (lane == 0) {
-                    const uint32_t v_addr = base + TcSmem::v + (j % kTcVStages) * kTcTile;
-                    const uint32_t p_tmem = tmem + i * 128 + kTmemPinS;
-#pragma unroll
-                    for (int ks = 0; ks < 8; ++ks)     // 16 keys: 8 packed columns of P, 16 rows of V
-                        tc_mma_ts(tmem + kTmemO + i * 128, p_tmem + ks * 8, tc_desc(v_addr + ks * 16 * 128, kTcHalf), idesc_pv,
-                                  (j > 0 || ks > 0) ? 1u : 0u);
-                    tc_commit(bar(PV_DONE, i));
-                }
-                __syncwarp();
-                if (j + 1 < tile[i].n_kt) issue_s(i, j + 1);
+            if (j < kt0) {
+                if (!tc_wait(bar(P_FULL, 0), j & 1, s_abort)) { ok = false; break; }
+                issue_pv(0, vs, j == 0);
+                if (j + 1 < kt0) issue_s(0, ks);
             }
-            if (ok && lane == 0) {
-                tc_commit(bar(V_EMPTY, j % kTcVStages));
-                if (next) tc_commit(bar(K_EMPTY, (j + 1) % kTcKStages));
+            if (j < kt1) {
+                if (!tc_wait(bar(P_FULL, 1), j & 1, s_abort)) { ok = false; break; }
+                issue_pv(1, vs, j == 0);
             }
+            if (lane == 0) tc_commit(bar(V_EMPTY, vs));                 // both products with V_j are issued
             __syncwarp();
+            if (j + 1 < kt1) issue_s(1, ks);
+            if (next) {
+                if (lane == 0) tc_commit(bar(K_EMPTY, ks));             // both S(j+1) are issued
+                __syncwarp();
+            }
+            if (++vs == kTcVStages) { vs = 0; vph ^= 1; }
+            if (++ks == kTcKStages) { ks = 0; kph ^= 1; }
+            // The tensor core still works on what was just issued: look at the next iteration's
+            // tiles now (V_{j+1}, K_{j+2}), so that the blocking waits above are usually skipped.
+            v_here = next && mbar_test_wait(bar(V_FULL, vs), vph);
+            k_here = j + 2 < n_max && mbar_test_wait(bar(K_FULL, ks), kph);
         }
         // all tensor-core work issued by this warp must have retired before TMEM is freed
         if (lane == 0) tc_commit(bar(DRAIN));
