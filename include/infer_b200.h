@@ -159,6 +159,13 @@ INFER_API int infer_paged_decode_noalloc(const infer_kv_pool_t* pool, void* out,
                                int64_t bt_stride, int batch, int n_q_heads, float softmax_scale,
                                void* stream);
 
+/* Reads (and clears) the status word of the prefill kernels on the current device
+ * (synchronises the stream): INFER_ERR_DEVICE if a bounded wait inside infer_paged_prefill or
+ * infer_flash_attn_prefill ran out since the last call, INFER_OK otherwise.  The word lives in
+ * the library's device image; the first prefill call on a device looks its address up, so make
+ * that call before any stream capture.  A debugging read, like infer_paged_decode_status. */
+INFER_API int infer_prefill_status(void* stream);
+
 /* Reads the device status word the last decode call on this workspace left behind
  * (synchronises the stream).  0 = no bounded wait ran out. */
 INFER_API int infer_paged_decode_status(const void* workspace, void* stream);

@@ -33,6 +33,7 @@ SIGNATURES = {
     "infer_paged_prefill": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _f32, _vp]),
     "infer_flash_attn_prefill": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
     "infer_paged_decode_status": (_i32, [_vp, _vp]),
+    "infer_prefill_status": (_i32, [_vp]),
     "infer_strerror": (C.c_char_p, [_i32]),
     "infer_last_cuda_error": (_i32, []),
     "infer_abi_version": (_i32, []),

@@ -1,5 +1,6 @@
 // Entry points of the prefill attention ops: argument checks, tensor maps, kernel choice.
 #include <cstdlib>
+#include <mutex>
 
 #include "prefill.cuh"
 
@@ -13,9 +14,46 @@ static int prefill_impl() {
     return (v == 1 || v == 2) ? v : 2;
 }
 
+// Status word of the prefill kernels: lives in the library's device image (one per GPU), set to
+// 0x5AFE0000 | code by a kernel whose bounded wait ran out, read and cleared by
+// infer_prefill_status().  In host code the NAME is only a handle for cudaGetSymbolAddress.
+static __device__ int g_prefill_status;
+constexpr int kMaxDevices = 64;
+static int* g_prefill_status_addr[kMaxDevices];
+static std::mutex g_prefill_status_mutex;
+
+// Device address of the status word on the current device; nullptr (the kernels then report
+// nothing) if it cannot be looked up.
+static int* prefill_status_word() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    std::lock_guard<std::mutex> lock(g_prefill_status_mutex);
+    if (!g_prefill_status_addr[dev]) {
+        void* addr = nullptr;
+        if (cudaGetSymbolAddress(&addr, g_prefill_status) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        g_prefill_status_addr[dev] = static_cast<int*>(addr);
+    }
+    return g_prefill_status_addr[dev];
+}
+
 }  // namespace ib
 
 extern "C" {
+
+int infer_prefill_status(void* stream_) {
+    int* word_dev = ib::prefill_status_word();
+    if (!word_dev) return INFER_ERR_CUDA;
+    int word = 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream_);
+    IB_CUDA(cudaMemcpyAsync(&word, word_dev, sizeof(int), cudaMemcpyDeviceToHost, st));
+    IB_CUDA(cudaStreamSynchronize(st));
+    if ((word & 0xFFFF0000) != 0x5AFE0000) return INFER_OK;
+    IB_CUDA(cudaMemsetAsync(word_dev, 0, sizeof(int), st));
+    return INFER_ERR_DEVICE;
+}
 
 int infer_paged_prefill(const infer_kv_pool_t* pool, void* out, const void* q, int64_t total_q,
                         const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, const int32_t* block_tables,
@@ -46,7 +84,7 @@ int infer_paged_prefill(const infer_kv_pool_t* pool, void* out, const void* q, i
     p.block_size = pool->block_size;
     p.seq_len = 0;
     p.scale_log2 = softmax_scale * 1.4426950408889634f;
-    p.status = nullptr;
+    p.status = prefill_status_word();
     cudaStream_t st = static_cast<cudaStream_t>(stream_);
     if (prefill_impl() == 2) {
         CUtensorMap mq;   // q [total_q, Hq, 128]: rows past total_q are filled with zeros
@@ -92,7 +130,7 @@ int infer_flash_attn_prefill(const void* q, const void* k, const void* v, void* 
     p.block_size = 1;
     p.seq_len = seq_len;
     p.scale_log2 = 1.4426950408889634f / sqrtf(float(kHeadDim));
-    p.status = nullptr;
+    p.status = prefill_status_word();
     cudaStream_t st = static_cast<cudaStream_t>(stream_);
     if (tc) return launch_prefill_tc(false, p, mq, mk, mv, seq_len, batch, st);
     return launch_prefill_mma(false, p, mk, mv, seq_len, batch, st);

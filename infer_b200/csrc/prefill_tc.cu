@@ -6,21 +6,26 @@
 //   S = Q K^T        tcgen05.mma, A = Q and B = K from shared memory (K-major, 128-byte
 //                    swizzle, written by TMA), accumulator in tensor memory (128 columns)
 //   softmax          one warpgroup per query tile, one thread per query row = one TMEM lane:
-//                    tcgen05.ld of the row, running max / sum in registers, P written back to
-//                    tensor memory as packed bf16 over columns of S that were already read
+//                    tcgen05.ld of the whole row into registers, running max / sum in
+//                    registers, P written to tensor memory as packed bf16
 //   O += P V         tcgen05.mma, A = P from tensor memory, B = V (MN-major: dims contiguous),
 //                    the accumulator stays in tensor memory for the whole key loop
-// The tensor core alternates between the two query tiles (P V of one, then its next S), so
-// while one warpgroup runs its softmax the other one's matrix products execute; the two
-// warpgroups of an SM sub-partition are independent and fill each other's latencies.
+// Tensor memory (512 columns): ONE S buffer that the two query tiles take turns on (a row of
+// S only lives there from the end of its product until its warpgroup has copied it to
+// registers), P of tile 0, P of tile 1 (64 columns each), O of tile 0, O of tile 1.  Because P
+// has its own columns, S_i(j+1) does not have to wait for P V_i(j): the tensor core computes
+// the next S of a tile while that tile's warpgroup is still in the softmax of the current
+// one, so neither waits for the other in the steady state (issue order per key tile:
+// S_0(j+1), P V_0(j), S_1(j+1), P V_1(j)).
 // The softmax keeps a reference maximum per row and only moves it (rescaling the row of O in
 // tensor memory and the running sum) when the true maximum has grown by more than 2^8; the
 // result is exact because O and the sum always share the same reference.
 // Warp roles: 0-3 softmax of tile 0, 4-7 softmax of tile 1, 8 TMA producer, 9 MMA issue and
 // TMEM allocation, 10-11 idle (they complete the third warpgroup, which hands 64 registers per
 // thread to the softmax warpgroups with setmaxnreg so that a whole 128-column row of S fits in
-// registers).  The softmax arithmetic uses packed f32x2 instructions and 3-input max.  Every barrier wait is bounded; a wait that runs out raises a CTA-wide
-// abort flag, every role drains to the common epilogue, TMEM is freed and a status is set.
+// registers).  The softmax arithmetic uses packed f32x2 instructions and 3-input max.  Every
+// barrier wait is bounded; a wait that runs out raises a CTA-wide abort flag, every role
+// drains to the common epilogue, TMEM is freed and a status is set.
 #include "prefill.cuh"
 
 namespace ib {
@@ -34,9 +39,9 @@ constexpr int kTcSoftmaxWarps = 4 * kTcQTiles;
 constexpr int kTcProducerWarp = kTcSoftmaxWarps, kTcMmaWarp = kTcSoftmaxWarps + 1;
 constexpr int kTcThreads = (kTcSoftmaxWarps + 4) * 32;   // third warpgroup: producer, MMA issue, two idle warps
 constexpr int kTcKStages = 3, kTcVStages = 2;
-// tensor memory columns: S of tile 0 at 0, S of tile 1 at 128, O of tile 0 at 256, O of tile 1 at 384;
-// P (bf16, two keys per column) reuses columns 64-127 of its tile's S
-constexpr uint32_t kTmemO = 256, kTmemPinS = 64;
+// tensor memory columns: S (shared by the two tiles) at 0, P of tile i (bf16, two keys per column) at
+// 128 + 64 i, O of tile i at 256 + 128 i
+constexpr uint32_t kTmemP = 128, kTmemO = 256;
 
 struct TcSmem {
     static constexpr int q = 0;                              // kTcQTiles tiles
@@ -49,7 +54,7 @@ struct TcSmem {
 };
 
 enum TcBar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 4, V_FULL = 7, V_EMPTY = 9, S_FULL = 11, P_FULL = 13, PV_DONE = 15,
-             DRAIN = 17 };
+             DRAIN = 17, S_FREE = 18 };
 constexpr float kLazyLog2 = 8.f;              // the reference maximum may lag the true one by 2^8
 
 // ---- tcgen05 wrappers
@@ -63,6 +68,30 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
         ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc), "r"(0u)
+        : "memory");
+}
+// The three wrappers below take an `issue` flag (true in one lane): the warp stays converged
+// around them, so the descriptor arithmetic in front of them is uniform across the warp.
+__device__ __forceinline__ void tc_commit_if(uint32_t bar, uint32_t issue) {
+    asm volatile(
+        "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %1, 0;\n\t"
+        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+        ::"r"(bar), "r"(issue) : "memory");
+}
+__device__ __forceinline__ void tc_mma_if(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc,
+                                          uint32_t issue) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %6, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc), "r"(0u), "r"(issue)
+        : "memory");
+}
+__device__ __forceinline__ void tc_mma_ts_if(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t acc,
+                                             uint32_t issue) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %6, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc), "r"(0u), "r"(issue)
         : "memory");
 }
 // same, with the A operand in tensor memory (16-bit elements packed two per column)
@@ -140,12 +169,18 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
     asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
     return r;
 }
-// Bounded wait that also gives up as soon as another thread raised the abort flag.
+// Bounded wait that also gives up as soon as another thread raised the abort flag.  One test
+// in front of the polling loop: a wait on a phase that is already complete then costs a test
+// and a branch (about 35 clocks) instead of a trip through the loop (about 210 as measured).
 __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t i = 0; i < (1u << 22); ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    uint32_t i = 0;
+#pragma unroll 1
+    while (true) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 63) == 63) {
+        if ((++i & 63) == 0) {
             if (*abort_flag) return false;
+            if (i >= (1u << 22)) break;
             __nanosleep(i > 4096 ? 256 : 32);
         }
     }
@@ -193,7 +228,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
     if (tile[0].n_kt == 0) return;                           // whole CTA leaves before any barrier or TMEM use
     const int n_max = max(tile[0].n_kt, tile[1].n_kt);
     const int kvh = tile[0].head / p.group;                  // both tiles read the same kv head
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // Roles are numbered as in the header comment, but the third warpgroup's roles (producer, MMA
+    // issue) sit in the FIRST four hardware warps: when several warps of a scheduler are ready the
+    // oldest one goes first, and the MMA issue warp, which has little to do but whose every
+    // instruction is on the tensor core's critical path, must not queue behind the softmax warps.
+    const int warp = (int(threadIdx.x >> 5) + kTcSoftmaxWarps) % (kTcThreads / 32), lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
         mbar_init(bar(Q_FULL), 1);
@@ -211,6 +250,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
             mbar_init(bar(PV_DONE, i), 1);
         }
         mbar_init(bar(DRAIN), 1);
+        mbar_init(bar(S_FREE), 128);             // the warpgroup that copied the S buffer to registers
         *s_abort = 0;
         fence_mbar_init();
         fence_proxy_async();
@@ -286,61 +326,58 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
         }
     } else if (warp == kTcMmaWarp) {
         // ================================================================= MMA issue
-        // Order on the tensor core: S_0(0) S_1(0), then per key tile j: PV_0(j) S_0(j+1) PV_1(j) S_1(j+1).
-        // tcgen05 operations of one thread execute in order, which is what lets P reuse columns
-        // of S (S_i(j+1) is behind PV_i(j)) and makes the final commit cover everything.  One
-        // issuing thread also keeps the two softmax warpgroups half a period apart.  What this
-        // warp does between two issues costs tensor-core time, so the waits for the next
-        // iteration's K and V tiles are taken while the products of tile 0 execute, and the
-        // descriptors are the stage's base descriptor plus a constant.
+        // Order on the tensor core: S_0(0) S_1(0), then per key tile j: S_0(j+1) PV_0(j) S_1(j+1) PV_1(j).
+        // An S product may start once the warpgroup of the previous S product (the other tile's,
+        // as a rule) has copied the S buffer to registers (S_FREE, one phase per S product); a
+        // P V product once its warpgroup has written P.  tcgen05 operations of one thread execute
+        // in order, so the final commit covers everything.  Descriptors are the stage's base
+        // descriptor plus a constant.
         constexpr uint32_t idesc_s = tc_idesc(false), idesc_pv = tc_idesc(true);
         const int kt0 = tile[0].n_kt, kt1 = tile[1].n_kt;
         // descriptors differ from operand tile to operand tile only in the 14-bit start address
         // (16-byte units) at the bottom of the low word
         const uint64_t q_desc0 = tc_desc(base + TcSmem::q, 16);
         const uint64_t k_desc0 = tc_desc(base + TcSmem::k, 16), v_desc0 = tc_desc(base + TcSmem::v, kTcHalf);
-        auto issue_s = [&](int i, int stage) {     // S_i = Q_i K^T  (K_FULL of that stage already awaited)
-            if (lane == 0) {
-                const uint64_t qd = q_desc0 + uint64_t(i * (kTcTile >> 4));
-                const uint64_t kd = k_desc0 + uint64_t(stage * (kTcTile >> 4));
-#pragma unroll
-                for (int kk = 0; kk < 8; ++kk) {
-                    const uint32_t off = ((kk >> 2) * kTcHalf + (kk & 3) * 32) >> 4;
-                    tc_mma(tmem + i * 128, qd + off, kd + off, idesc_s, kk > 0);
-                }
-                tc_commit(bar(S_FULL, i));
-            }
-            __syncwarp();
-        };
-        auto issue_pv = [&](int i, int stage, bool first) {   // O_i += P_i V  (P_FULL and V_FULL already awaited)
+        int n_s = 0;                               // S products issued so far
+        const uint32_t one = lane == 0 ? 1u : 0u;  // the lane that issues
+        auto issue_s = [&](int i, int stage) {     // S = Q_i K^T  (K_FULL of that stage already awaited)
+            if (n_s > 0 && !tc_wait(bar(S_FREE), (n_s - 1) & 1, s_abort)) { ok = false; return; }
+            ++n_s;
             tc_fence_after();
-            if (lane == 0) {
-                const uint64_t vd = v_desc0 + uint64_t(stage * (kTcTile >> 4));
-                const uint32_t p_tmem = tmem + i * 128 + kTmemPinS;
+            const uint64_t qd = q_desc0 + uint64_t(i * (kTcTile >> 4));
+            const uint64_t kd = k_desc0 + uint64_t(stage * (kTcTile >> 4));
 #pragma unroll
-                for (int kk = 0; kk < 8; ++kk)     // 16 keys: 8 packed columns of P, 16 rows of V
-                    tc_mma_ts(tmem + kTmemO + i * 128, p_tmem + kk * 8, vd + uint32_t(kk * 16 * 128 >> 4), idesc_pv,
-                              (!first || kk > 0) ? 1u : 0u);
-                tc_commit(bar(PV_DONE, i));
+            for (int kk = 0; kk < 8; ++kk) {
+                const uint32_t off = ((kk >> 2) * kTcHalf + (kk & 3) * 32) >> 4;
+                tc_mma_if(tmem, qd + off, kd + off, idesc_s, kk > 0, one);
             }
-            __syncwarp();
+            tc_commit_if(bar(S_FULL, i), one);
+        };
+        auto issue_pv = [&](int i, int stage, int j) {   // O_i += P_i V  (V_FULL of that stage already awaited)
+            if (!tc_wait(bar(P_FULL, i), j & 1, s_abort)) { ok = false; return; }
+            tc_fence_after();
+            const uint64_t vd = v_desc0 + uint64_t(stage * (kTcTile >> 4));
+            const uint32_t p_tmem = tmem + kTmemP + i * 64;
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk)     // 16 keys: 8 packed columns of P, 16 rows of V
+                tc_mma_ts_if(tmem + kTmemO + i * 128, p_tmem + kk * 8, vd + uint32_t(kk * 16 * 128 >> 4), idesc_pv,
+                             (j > 0 || kk > 0) ? 1u : 0u, one);
+            tc_commit_if(bar(PV_DONE, i), one);
         };
         if (!tc_wait(bar(Q_FULL), 0, s_abort)) ok = false;
         if (ok && !tc_wait(bar(K_FULL, 0), 0, s_abort)) ok = false;
         if (ok) {
-            tc_fence_after();
             issue_s(0, 0);
-            if (kt1 > 0) issue_s(1, 0);
-            if (lane == 0) tc_commit(bar(K_EMPTY, 0));
-            __syncwarp();
+            if (ok && kt1 > 0) issue_s(1, 0);
+            tc_commit_if(bar(K_EMPTY, 0), one);
         }
         int vs = 0, vph = 0;                                           // stage and phase of V_j
         int ks = 1 % kTcKStages, kph = (1 / kTcKStages) & 1;           // stage and phase of K_{j+1}
-        bool v_here = false, k_here = false;                          // already seen complete by an early test
         for (int j = 0; j < n_max && ok; ++j) {
             const bool next = j + 1 < n_max;
-            if (!v_here && !tc_wait(bar(V_FULL, vs), vph, s_abort)) { ok = false; break; }
-            if (next && !k_here && !tc_wait(bar(K_FULL, ks), kph, s_abort)) { ok = false; break; }
+            if (next && !tc_wait(bar(K_FULL, ks), kph, s_abort)) { ok = false; break; }
+            if (j + 1 < kt0) issue_s(0, ks);
+            if (!ok || !tc_wait(bar(V_FULL, vs), vph, s_abort)) { ok = false; break; }
             if (PAGED && !next) {
                 // keys past the end of the context: P is 0 there, but 0 * (stale bytes) must not
                 // produce NaN, so clear those V rows before the tensor core reads them
@@ -355,32 +392,18 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
                     __syncwarp();
                 }
             }
-            if (j < kt0) {
-                if (!tc_wait(bar(P_FULL, 0), j & 1, s_abort)) { ok = false; break; }
-                issue_pv(0, vs, j == 0);
-                if (j + 1 < kt0) issue_s(0, ks);
-            }
-            if (j < kt1) {
-                if (!tc_wait(bar(P_FULL, 1), j & 1, s_abort)) { ok = false; break; }
-                issue_pv(1, vs, j == 0);
-            }
-            if (lane == 0) tc_commit(bar(V_EMPTY, vs));                 // both products with V_j are issued
-            __syncwarp();
-            if (j + 1 < kt1) issue_s(1, ks);
-            if (next) {
-                if (lane == 0) tc_commit(bar(K_EMPTY, ks));             // both S(j+1) are issued
-                __syncwarp();
-            }
+            if (j < kt0) issue_pv(0, vs, j);
+            if (ok && j + 1 < kt1) issue_s(1, ks);
+            if (!ok) break;
+            if (next) tc_commit_if(bar(K_EMPTY, ks), one);              // both S(j+1) are issued
+            if (j < kt1) issue_pv(1, vs, j);
+            if (!ok) break;
+            tc_commit_if(bar(V_EMPTY, vs), one);                        // both products with V_j are issued
             if (++vs == kTcVStages) { vs = 0; vph ^= 1; }
             if (++ks == kTcKStages) { ks = 0; kph ^= 1; }
-            // The tensor core still works on what was just issued: look at the next iteration's
-            // tiles now (V_{j+1}, K_{j+2}), so that the blocking waits above are usually skipped.
-            v_here = next && mbar_test_wait(bar(V_FULL, vs), vph);
-            k_here = j + 2 < n_max && mbar_test_wait(bar(K_FULL, ks), kph);
         }
         // all tensor-core work issued by this warp must have retired before TMEM is freed
-        if (lane == 0) tc_commit(bar(DRAIN));
-        __syncwarp();
+        tc_commit_if(bar(DRAIN), one);
         mbar_wait(bar(DRAIN), 0);
     }
     } else {
@@ -393,7 +416,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
         const int row = tile[g].row0 + r;
         const int pos = shift + row;
         const int tile_first_pos = shift + tile[g].row0;
-        const uint32_t s_addr = tmem + lane_sel + g * 128;
+        const uint32_t s_addr = tmem + lane_sel;                   // the S buffer is shared by the two tiles
+        const uint32_t p_addr = tmem + lane_sel + kTmemP + g * 64;
         const uint32_t o_addr = tmem + lane_sel + kTmemO + g * 128;
         float m_ref = -INFINITY, l_run = 0.f;                      // reference maximum (log2 domain), row sum
 
@@ -411,6 +435,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
             tc_ld32(s_addr + 64, *reinterpret_cast<uint32_t(*)[32]>(&sv[64]));
             tc_ld32(s_addr + 96, *reinterpret_cast<uint32_t(*)[32]>(&sv[96]));
             tc_wait_ld();
+            // the row is in registers: the tensor core may overwrite the S buffer
+            tc_fence_before();
+            mbar_arrive(bar(S_FREE));
             if (masked) {
 #pragma unroll
                 for (int i = 0; i < 128; ++i)
@@ -448,7 +475,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
                 m_ref = m_new;
             }
             const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-            // P = exp2(S * c - m) as packed bf16 over columns 64-127 of S (all of S is in registers)
+            // the tensor core must be done reading P of the previous key tile (long since, as a rule)
+            if (j > 0 && !tc_wait(bar(PV_DONE, g), (j - 1) & 1, s_abort)) { ok = false; continue; }
+            // P = exp2(S * c - m) as packed bf16
             uint64_t rsa = pk2(0.f, 0.f), rsb = pk2(0.f, 0.f);
             const uint64_t c2 = pk2(p.scale_log2, p.scale_log2), nm2 = pk2(-m_use, -m_use);
 #pragma unroll
@@ -465,7 +494,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
                     if (i & 1) rsb = fadd2(rsb, pk2(e0, e1)); else rsa = fadd2(rsa, pk2(e0, e1));
                     pk[i] = pack_bf16(e0, e1);
                 }
-                tc_st32(s_addr + kTmemPinS + h * 32, pk);
+                tc_st32(p_addr + h * 32, pk);
             }
             float rs0, rs1, rs2, rs3;
             upk2(rsa, rs0, rs1);

@@ -207,8 +207,16 @@ def paged_attn_prefill(q, k_cache, v_cache, cu_seqlens_q, cu_seqlens_k, max_seql
                                      _ptr(block_table), block_table.stride(0), cu_seqlens_q.numel() - 1,
                                      int(max_seqlen_q), int(max_seqlen_k), q.shape[1], float(softmax_scale),
                                      _stream())
-    _lib.check(rc, "paged_attn_prefill")
+        _lib.check(rc, "paged_attn_prefill")
+        _check_prefill_status(lib, "paged_attn_prefill")
     return o
+
+
+def _check_prefill_status(lib, what):
+    """With INFER_B200_CHECK=1 (and outside stream capture): synchronise and raise if a bounded
+    wait inside the prefill kernel ran out."""
+    if os.environ.get("INFER_B200_CHECK") == "1" and not torch.cuda.is_current_stream_capturing():
+        _lib.check(lib.infer_prefill_status(_stream()), f"{what} (device status)")
 
 
 def flash_attn_prefill(Q, K, V, O):
@@ -222,7 +230,8 @@ def flash_attn_prefill(Q, K, V, O):
     with torch.cuda.device(Q.device):
         rc = lib.infer_flash_attn_prefill(_ptr(Q), _ptr(K), _ptr(V), _ptr(O), Q.shape[0], Q.shape[1], K.shape[1],
                                           Q.shape[2], _stream())
-    _lib.check(rc, "flash_attn_prefill")
+        _lib.check(rc, "flash_attn_prefill")
+        _check_prefill_status(lib, "flash_attn_prefill")
 
 
 # --------------------------------------------------------------------------- torch.ops._C
