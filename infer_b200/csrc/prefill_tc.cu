@@ -15,13 +15,13 @@
 // registers), P of tile 0, P of tile 1 (64 columns each), O of tile 0, O of tile 1.  Because P
 // has its own columns, S_i(j+1) does not have to wait for P V_i(j): the tensor core computes
 // the next S of a tile while that tile's warpgroup is still in the softmax of the current
-// one, so neither waits for the other in the steady state (issue order per key tile:
-// S_0(j+1), P V_0(j), S_1(j+1), P V_1(j)).
+// one, so neither waits for the other in the steady state.
 // The softmax keeps a reference maximum per row and only moves it (rescaling the row of O in
 // tensor memory and the running sum) when the true maximum has grown by more than 2^8; the
 // result is exact because O and the sum always share the same reference.
-// Warp roles: 0-3 softmax of tile 0, 4-7 softmax of tile 1, 8 TMA producer, 9 MMA issue and
-// TMEM allocation, 10-11 idle (they complete the third warpgroup, which hands 64 registers per
+// Warp roles: 0-3 softmax of tile 0, 4-7 softmax of tile 1, 8 TMA producer, 9 issue of the S
+// products and TMEM allocation, 10 issue of the P V products, 11 idle (8-11 make up the third
+// warpgroup, which hands 64 registers per
 // thread to the softmax warpgroups with setmaxnreg so that a whole 128-column row of S fits in
 // registers).  The softmax arithmetic uses packed f32x2 instructions and 3-input max.  Every
 // barrier wait is bounded; a wait that runs out raises a CTA-wide abort flag, every role
@@ -54,7 +54,7 @@ struct TcSmem {
 };
 
 enum TcBar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 4, V_FULL = 7, V_EMPTY = 9, S_FULL = 11, P_FULL = 13, PV_DONE = 15,
-             DRAIN = 17, S_FREE = 18 };
+             DRAIN = 17 /* two */, S_FREE = 19 };
 constexpr float kLazyLog2 = 8.f;              // the reference maximum may lag the true one by 2^8
 
 // ---- tcgen05 wrappers
@@ -68,30 +68,6 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
         ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc), "r"(0u)
-        : "memory");
-}
-// The three wrappers below take an `issue` flag (true in one lane): the warp stays converged
-// around them, so the descriptor arithmetic in front of them is uniform across the warp.
-__device__ __forceinline__ void tc_commit_if(uint32_t bar, uint32_t issue) {
-    asm volatile(
-        "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %1, 0;\n\t"
-        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
-        ::"r"(bar), "r"(issue) : "memory");
-}
-__device__ __forceinline__ void tc_mma_if(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc,
-                                          uint32_t issue) {
-    asm volatile(
-        "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %6, 0;\n\t"
-        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc), "r"(0u), "r"(issue)
-        : "memory");
-}
-__device__ __forceinline__ void tc_mma_ts_if(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t acc,
-                                             uint32_t issue) {
-    asm volatile(
-        "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %6, 0;\n\t"
-        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc), "r"(0u), "r"(issue)
         : "memory");
 }
 // same, with the A operand in tensor memory (16-bit elements packed two per column)
@@ -249,7 +225,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
             mbar_init(bar(P_FULL, i), 128);
             mbar_init(bar(PV_DONE, i), 1);
         }
-        mbar_init(bar(DRAIN), 1);
+        mbar_init(bar(DRAIN, 0), 1);
+        mbar_init(bar(DRAIN, 1), 1);
         mbar_init(bar(S_FREE), 128);             // the warpgroup that copied the S buffer to registers
         *s_abort = 0;
         fence_mbar_init();
@@ -325,60 +302,73 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
             for (int j = max(0, v_issued - kTcVStages); j < v_issued; ++j) mbar_wait(bar(V_FULL, j % kTcVStages), (j / kTcVStages) & 1);
         }
     } else if (warp == kTcMmaWarp) {
-        // ================================================================= MMA issue
-        // Order on the tensor core: S_0(0) S_1(0), then per key tile j: S_0(j+1) PV_0(j) S_1(j+1) PV_1(j).
-        // An S product may start once the warpgroup of the previous S product (the other tile's,
-        // as a rule) has copied the S buffer to registers (S_FREE, one phase per S product); a
-        // P V product once its warpgroup has written P.  tcgen05 operations of one thread execute
-        // in order, so the final commit covers everything.  Descriptors are the stage's base
-        // descriptor plus a constant.
-        constexpr uint32_t idesc_s = tc_idesc(false), idesc_pv = tc_idesc(true);
+        // ================================================================= MMA issue: the S products
+        // S_0(0) S_1(0) S_0(1) S_1(1) ...: an S product may start once the warpgroup of the previous
+        // one has copied the S buffer to registers (S_FREE, one phase per S product).  The P V
+        // products are issued by the next warp: under the softmax warps' instruction stream the
+        // descriptor arithmetic and barrier tests of one issuing thread take longer than the
+        // products they lead to, two threads keep the tensor core fed.
+        constexpr uint32_t idesc_s = tc_idesc(false);
         const int kt0 = tile[0].n_kt, kt1 = tile[1].n_kt;
         // descriptors differ from operand tile to operand tile only in the 14-bit start address
         // (16-byte units) at the bottom of the low word
-        const uint64_t q_desc0 = tc_desc(base + TcSmem::q, 16);
-        const uint64_t k_desc0 = tc_desc(base + TcSmem::k, 16), v_desc0 = tc_desc(base + TcSmem::v, kTcHalf);
+        const uint64_t q_desc0 = tc_desc(base + TcSmem::q, 16), k_desc0 = tc_desc(base + TcSmem::k, 16);
         int n_s = 0;                               // S products issued so far
-        const uint32_t one = lane == 0 ? 1u : 0u;  // the lane that issues
         auto issue_s = [&](int i, int stage) {     // S = Q_i K^T  (K_FULL of that stage already awaited)
             if (n_s > 0 && !tc_wait(bar(S_FREE), (n_s - 1) & 1, s_abort)) { ok = false; return; }
             ++n_s;
             tc_fence_after();
-            const uint64_t qd = q_desc0 + uint64_t(i * (kTcTile >> 4));
-            const uint64_t kd = k_desc0 + uint64_t(stage * (kTcTile >> 4));
+            if (lane == 0) {
+                const uint64_t qd = q_desc0 + uint64_t(i * (kTcTile >> 4));
+                const uint64_t kd = k_desc0 + uint64_t(stage * (kTcTile >> 4));
 #pragma unroll
-            for (int kk = 0; kk < 8; ++kk) {
-                const uint32_t off = ((kk >> 2) * kTcHalf + (kk & 3) * 32) >> 4;
-                tc_mma_if(tmem, qd + off, kd + off, idesc_s, kk > 0, one);
+                for (int kk = 0; kk < 8; ++kk) {
+                    const uint32_t off = ((kk >> 2) * kTcHalf + (kk & 3) * 32) >> 4;
+                    tc_mma(tmem, qd + off, kd + off, idesc_s, kk > 0);
+                }
+                tc_commit(bar(S_FULL, i));
             }
-            tc_commit_if(bar(S_FULL, i), one);
+            __syncwarp();
         };
+        if (!tc_wait(bar(Q_FULL), 0, s_abort)) ok = false;
+        int ks = 0, kph = 0;                                           // stage and phase of K_j
+        for (int j = 0; j < n_max && ok; ++j) {
+            if (!tc_wait(bar(K_FULL, ks), kph, s_abort)) { ok = false; break; }
+            if (j < kt0) issue_s(0, ks);
+            if (ok && j < kt1) issue_s(1, ks);
+            if (!ok) break;
+            if (lane == 0) tc_commit(bar(K_EMPTY, ks));                 // both S(j) are issued
+            __syncwarp();
+            if (++ks == kTcKStages) { ks = 0; kph ^= 1; }
+        }
+        // all tensor-core work issued by this warp must have retired before TMEM is freed
+        if (lane == 0) tc_commit(bar(DRAIN, 0));
+        __syncwarp();
+        mbar_wait(bar(DRAIN, 0), 0);
+    } else if (warp == kTcMmaWarp + 1) {
+        // ================================================================= MMA issue: the P V products
+        // P V_0(0) P V_1(0) P V_0(1) ...: each once its warpgroup has written P.
+        constexpr uint32_t idesc_pv = tc_idesc(true);
+        const int kt0 = tile[0].n_kt, kt1 = tile[1].n_kt;
+        const uint64_t v_desc0 = tc_desc(base + TcSmem::v, kTcHalf);
         auto issue_pv = [&](int i, int stage, int j) {   // O_i += P_i V  (V_FULL of that stage already awaited)
             if (!tc_wait(bar(P_FULL, i), j & 1, s_abort)) { ok = false; return; }
             tc_fence_after();
-            const uint64_t vd = v_desc0 + uint64_t(stage * (kTcTile >> 4));
-            const uint32_t p_tmem = tmem + kTmemP + i * 64;
+            if (lane == 0) {
+                const uint64_t vd = v_desc0 + uint64_t(stage * (kTcTile >> 4));
+                const uint32_t p_tmem = tmem + kTmemP + i * 64;
 #pragma unroll
-            for (int kk = 0; kk < 8; ++kk)     // 16 keys: 8 packed columns of P, 16 rows of V
-                tc_mma_ts_if(tmem + kTmemO + i * 128, p_tmem + kk * 8, vd + uint32_t(kk * 16 * 128 >> 4), idesc_pv,
-                             (j > 0 || kk > 0) ? 1u : 0u, one);
-            tc_commit_if(bar(PV_DONE, i), one);
+                for (int kk = 0; kk < 8; ++kk)     // 16 keys: 8 packed columns of P, 16 rows of V
+                    tc_mma_ts(tmem + kTmemO + i * 128, p_tmem + kk * 8, vd + uint32_t(kk * 16 * 128 >> 4), idesc_pv,
+                              (j > 0 || kk > 0) ? 1u : 0u);
+                tc_commit(bar(PV_DONE, i));
+            }
+            __syncwarp();
         };
-        if (!tc_wait(bar(Q_FULL), 0, s_abort)) ok = false;
-        if (ok && !tc_wait(bar(K_FULL, 0), 0, s_abort)) ok = false;
-        if (ok) {
-            issue_s(0, 0);
-            if (ok && kt1 > 0) issue_s(1, 0);
-            tc_commit_if(bar(K_EMPTY, 0), one);
-        }
         int vs = 0, vph = 0;                                           // stage and phase of V_j
-        int ks = 1 % kTcKStages, kph = (1 / kTcKStages) & 1;           // stage and phase of K_{j+1}
         for (int j = 0; j < n_max && ok; ++j) {
-            const bool next = j + 1 < n_max;
-            if (next && !tc_wait(bar(K_FULL, ks), kph, s_abort)) { ok = false; break; }
-            if (j + 1 < kt0) issue_s(0, ks);
-            if (!ok || !tc_wait(bar(V_FULL, vs), vph, s_abort)) { ok = false; break; }
-            if (PAGED && !next) {
+            if (!tc_wait(bar(V_FULL, vs), vph, s_abort)) { ok = false; break; }
+            if (PAGED && j == n_max - 1) {
                 // keys past the end of the context: P is 0 there, but 0 * (stale bytes) must not
                 // produce NaN, so clear those V rows before the tensor core reads them
                 const int valid = lk - j * kTcKeys;
@@ -393,18 +383,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
                 }
             }
             if (j < kt0) issue_pv(0, vs, j);
-            if (ok && j + 1 < kt1) issue_s(1, ks);
+            if (ok && j < kt1) issue_pv(1, vs, j);
             if (!ok) break;
-            if (next) tc_commit_if(bar(K_EMPTY, ks), one);              // both S(j+1) are issued
-            if (j < kt1) issue_pv(1, vs, j);
-            if (!ok) break;
-            tc_commit_if(bar(V_EMPTY, vs), one);                        // both products with V_j are issued
+            if (lane == 0) tc_commit(bar(V_EMPTY, vs));                 // both products with V_j are issued
+            __syncwarp();
             if (++vs == kTcVStages) { vs = 0; vph ^= 1; }
-            if (++ks == kTcKStages) { ks = 0; kph ^= 1; }
         }
-        // all tensor-core work issued by this warp must have retired before TMEM is freed
-        tc_commit_if(bar(DRAIN), one);
-        mbar_wait(bar(DRAIN), 0);
+        if (lane == 0) tc_commit(bar(DRAIN, 1));
+        __syncwarp();
+        mbar_wait(bar(DRAIN, 1), 0);
     }
     } else {
         // ================================================================= softmax, one row per thread
