@@ -221,6 +221,26 @@ def run_prefill(args):
         peak, kind = 1400.0, "of fallback"
     achieved = flops / (attn_ms * 1e-3) / 1e12
     n_tok = sum(w.new_lens)
+    dense = None
+    if args.dense:
+        gen = torch.Generator(device=device).manual_seed(7)
+        B, H, Hkv, S = 4, 16, 8, 4096
+        dq = torch.randn(B, H, S, 128, generator=gen, device=device).bfloat16()
+        dk = torch.randn(B, Hkv, S, 128, generator=gen, device=device).bfloat16()
+        dv = torch.randn(B, Hkv, S, 128, generator=gen, device=device).bfloat16()
+        do = torch.empty_like(dq)
+        for _ in range(3):
+            ops.flash_attn_prefill(dq, dk, dv, do)
+        torch.cuda.synchronize()
+        d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        d0.record(stream)
+        for _ in range(10):
+            ops.flash_attn_prefill(dq, dk, dv, do)
+        d1.record(stream)
+        torch.cuda.synchronize()
+        dms = d0.elapsed_time(d1) / 10
+        dflops = 4 * 128 * B * H * S * (S + 1) // 2
+        dense = {"shape": [B, H, S, 128], "kv_heads": Hkv, "ms": dms, "tflops": dflops / (dms * 1e-3) / 1e12}
     print(json.dumps({
         "metric": "paged chunked-prefill attention TFLOP/s", "value": flops / (step_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
         "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
@@ -237,6 +257,7 @@ def run_prefill(args):
         "append": {"rows": n_tok, "ms": append_ms, "tok_s": n_tok / (append_ms * 1e-3),
                    "gbs": n_tok * w.n_kv_heads * 128 * 2 * 4 / (append_ms * 1e-3) / 1e9},
         "clocks": clocks.summary(),
+        **({"dense_op": dense} if dense else {}),
     }))
 
 
@@ -256,6 +277,11 @@ def main():
                          "configuration (16 sequences, prefix U[0,4096], chunk 2048), single GPU; long = the "
                          "long-context scale-out configuration (batch 256, 64q/8kv heads, ctx lognormal capped at "
                          "32768, half the batch sharing a 2048-token prefix), strong scaling over KV heads")
+    ap.add_argument("--fp8", action="store_true",
+                    help="decode workloads: also time the e4m3 pool (decode, decode-shape append, 32768-row append) "
+                         "and add an fp8_kv object to the line (rank 0's figures)")
+    ap.add_argument("--dense", action="store_true",
+                    help="prefill workload: also time the dense op flash_attn_prefill on [4, 16, 4096, 128]")
     ap.add_argument("--batch", type=int, default=BASE_BATCH,
                     help="sequences per GPU share (default 64 = the benchmark configuration; smaller values "
                          "give the small case used for profiler captures)")
@@ -422,6 +448,46 @@ def main():
         del bk, bv, bslots
     bulk2_bytes = n_bulk2 * hkv * 128 * 2 * (2 + 2)
 
+    # ---- optional: the same pool as e4m3 bytes with one fp32 scale per (page, kv head)
+    fp8 = None
+    if args.fp8:
+        nb = w.num_blocks
+        k8 = torch.zeros(nb, 256, hkv, 128, dtype=torch.uint8, device=device)
+        v8 = torch.zeros_like(k8)
+        ks8 = torch.zeros(nb, hkv, device=device)
+        vs8 = torch.zeros(nb, hkv, device=device)
+        for lo in range(0, nb, 64):                           # quantise the bf16 pool page group by page group
+            hi = min(nb, lo + 64)
+            sl = torch.arange(lo * 256, hi * 256, dtype=torch.int32, device=device)
+            ops.store_kvcache(w.k_cache[lo:hi].reshape(-1, hkv, 128), w.v_cache[lo:hi].reshape(-1, hkv, 128), k8, v8, sl, ks8, vs8)
+        torch.cuda.synchronize()
+
+        def timed(fn, reps):
+            for _ in range(0 if args.profile else 3):
+                fn()
+            torch.cuda.synchronize()
+            a0.record(stream)
+            for _ in range(reps):
+                fn()
+            a1.record(stream)
+            torch.cuda.synchronize()
+            return a0.elapsed_time(a1) / reps
+
+        reps8 = 3 if args.profile else 20
+        dec8_ms = timed(lambda: ops.paged_attn_decode(w.q, k8, v8, cl, bt, w.scale, out=out, k_scale=ks8, v_scale=vs8), reps8)
+        app8_ms = timed(lambda: ops.store_kvcache(w.k, w.v, k8, v8, slots, ks8, vs8), reps8)
+        n_rows = min(32768, nb * 256)
+        sl = torch.arange(0, n_rows, dtype=torch.int32, device=device)
+        rk = w.k_cache.view(-1, hkv, 128)[:n_rows]
+        rv = w.v_cache.view(-1, hkv, 128)[:n_rows]
+        bulk8_ms = timed(lambda: ops.store_kvcache(rk, rv, k8, v8, sl, ks8, vs8), reps8)
+        kv8 = w.kv_bytes(elem_bytes=1)
+        fp8 = {"decode_us": dec8_ms * 1e3, "kv_bytes_e4m3": kv8, "decode_gbs": kv8 / (dec8_ms * 1e-3) / 1e9,
+               "tokens_per_us_vs_bf16": decode_ms / dec8_ms, "append_decode_shape_us": app8_ms * 1e3,
+               "bulk_rows": n_rows, "bulk_us": bulk8_ms * 1e3, "bulk_tok_s": n_rows / (bulk8_ms * 1e-3),
+               "bulk_gbs": n_rows * hkv * 128 * 2 * (2 + 1) / (bulk8_ms * 1e-3) / 1e9}
+        del k8, v8
+
     # ---- max over ranks
     t = torch.tensor([total_ms, decode_ms, append_ms, e2e_ms, bulk_ms, bulk2_ms], device=device, dtype=torch.float64)
     b = torch.tensor([float(kv_bytes)], device=device, dtype=torch.float64)
@@ -472,6 +538,8 @@ def main():
                        "bulk2_gbs": bulk2_bytes / (bulk2_ms * 1e-3) / 1e9 if bulk2_ms else None},
             "clocks": clocks.summary(),
         }
+        if fp8 is not None:
+            line["fp8_kv"] = fp8
         if not args.no_cpu_baseline and not args.profile and world == 1:
             secs, cpu_bytes, threads = cpu_sample(w, 8, 2)
             line["cpu_baseline"] = {
