@@ -64,6 +64,17 @@ def test_prefill_ragged_chunks_and_no_prefix():
     assert_close(got, want, ATOL_BF16, RTOL_BF16, "ragged prefill")
 
 
+def test_prefill_odd_group_size():
+    """Three query heads per KV head: the two query tiles of a thread block are then two row
+    blocks of one head with different numbers of key tiles (the other tests pair two heads)."""
+    w = workloads.config2(n_seqs=3, max_prefix=900, chunk=420, seed=35)
+    gen = torch.Generator().manual_seed(35)
+    w.q = torch.randn(w.q.shape[0], 24, 128, generator=gen).bfloat16()
+    w.n_q_heads = 24
+    got, want, _ = _run(w)
+    assert_close(got, want, ATOL_BF16, RTOL_BF16, "prefill, group 3")
+
+
 def test_prefill_last_row_equals_decode():
     w = workloads.config2(n_seqs=3, max_prefix=900, chunk=200, seed=33)
     got, _, d = _run(w)
