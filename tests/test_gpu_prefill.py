@@ -75,6 +75,30 @@ def test_prefill_odd_group_size():
     assert_close(got, want, ATOL_BF16, RTOL_BF16, "prefill, group 3")
 
 
+def test_prefill_full_size_two_kernels_and_decode_agree(prefill_impl, monkeypatch):
+    """The benchmark configuration itself (16 sequences, prefix up to 4096, chunk 2048), too large
+    for the CPU oracle: the tcgen05 kernel and the mma.sync kernel, two independent programs, must
+    agree within the bf16 tolerance on every row, and the last row of every chunk must equal the
+    decode kernel's answer for that position."""
+    if prefill_impl != "2":
+        pytest.skip("one run covers both kernels")
+    w = workloads.config2(device="cuda")
+    cu_q, cu_k = (t.cuda() for t in w.cu_seqlens())
+    bt = w.block_tables_tensor().cuda()
+    ops.store_kvcache(w.k, w.v, w.k_cache, w.v_cache, w.slot_mapping.cuda())
+    outs = {}
+    for impl in ("2", "1"):
+        monkeypatch.setenv("INFER_B200_PREFILL_IMPL", impl)
+        outs[impl] = ops.paged_attn_prefill(w.q, w.k_cache, w.v_cache, cu_q, cu_k, max(w.new_lens), max(w.context_lens),
+                                            w.scale, bt)
+    torch.cuda.synchronize()
+    assert_close(outs["2"], outs["1"], ATOL_BF16, RTOL_BF16, "tcgen05 vs mma.sync, full size")
+    last = (cu_q[1:] - 1).long()
+    dec = ops.paged_attn_decode(w.q[last].contiguous(), w.k_cache, w.v_cache,
+                                torch.tensor(w.context_lens, dtype=torch.int32, device="cuda"), bt, w.scale)
+    assert_close(outs["2"][last], dec, ATOL_BF16, RTOL_BF16, "last chunk rows vs decode, full size")
+
+
 def test_prefill_last_row_equals_decode():
     w = workloads.config2(n_seqs=3, max_prefix=900, chunk=200, seed=33)
     got, _, d = _run(w)
