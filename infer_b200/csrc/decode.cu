@@ -188,7 +188,7 @@ constexpr int kStages = 3;
 constexpr int kTileBytes = 32768;                 // K (or V) bytes per stage: 128 rows x 256 B
 constexpr int kConsumerWarps = 8;
 constexpr int kTmaThreads = (kConsumerWarps + 1) * 32;
-constexpr int kMergeSlotFloats = 34 * 32;         // 32 accumulators + max + sum per lane
+constexpr int kMergeSlotFloats = 36 * 32;         // 32 accumulators + up to two maxima and two sums per lane
 
 struct TmaSmem {
     // dynamic shared memory, 1024-byte aligned base:
@@ -441,30 +441,46 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_kernel(DecodeParams
 }
 
 // =========================================================================== TMA kernel, e4m3 pools
-// Same work split, ring and merge as decode_tma_kernel<1>, with a tile of one whole 256-token
-// page of one kv head (32 KiB of K + 32 KiB of V).  K and V bytes go from shared memory to
-// the tensor cores as f16 (e4m3 -> f16 is exact), q is converted to f16 once per segment.
+// Same work split and ring as decode_tma_kernel<1>, with a tile of one whole 256-token page of
+// one kv head (32 KiB of K + 32 KiB of V).  K and V bytes go from shared memory to the tensor
+// cores as f16 (e4m3 -> f16 is exact), q is converted to f16 once per segment.  The products
+// are token-major (the 16 MMA rows are tokens, the 8 columns the group's query heads), which
+// halves the number of products and accumulator registers against head-major ones (131 against
+// 138 us on the benchmark's lengths).
 // The page's K scale is folded into the softmax exponent; the V scale is handled by keeping
 // the accumulator in units of the current page's V scale and folding scale changes into the
 // online-softmax correction, so no per-element dequantisation multiply is needed.
 constexpr int kFp8TileTokens = 256;
 
+// W consumer warps (8 or 16; 16 was measured 5 % slower): 256 / W tokens per warp and tile.
+template <int W>
 struct Fp8Smem {
-    static constexpr int meta = TmaSmem::total;                 // [kStages][2] floats: k scale, v scale
+    static constexpr int threads = (W + 1) * 32;
+    static constexpr int merge = TmaSmem::tiles;
+    static constexpr int prefix = merge + 4 * kMergeSlotFloats * 4;
+    static constexpr int scan = prefix + (kMaxBatch + 1) * 4 + 12;
+    static constexpr int bars = scan + threads * 4;
+    static constexpr int meta = bars + 2 * kStages * 8 + 16;      // [kStages][2] floats: k scale, v scale
     static constexpr int total = meta + kStages * 8;
 };
 
-__global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_fp8_kernel(DecodeParams p,
-                                                                        const __grid_constant__ CUtensorMap map_k,
-                                                                        const __grid_constant__ CUtensorMap map_v) {
+template <int W>
+__global__ void __launch_bounds__((W + 1) * 32, 1) decode_tma_fp8_kernel(DecodeParams p,
+                                                                          const __grid_constant__ CUtensorMap map_k,
+                                                                          const __grid_constant__ CUtensorMap map_v) {
     constexpr int TT = kFp8TileTokens;
+    constexpr int TPW = TT / W;                  // tokens per warp and tile
+    constexpr int NH = TPW / 16;                 // 16-token MMA tiles per warp and tile
+    static_assert(W == 8 || W == 16, "8 or 16 consumer warps");
+    using L = Fp8Smem<W>;
+    auto consumer_bar = [] { asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory"); };
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    float* s_merge = reinterpret_cast<float*>(smem + TmaSmem::merge);
-    int* s_tp = reinterpret_cast<int*>(smem + TmaSmem::prefix);
-    int* s_scan = reinterpret_cast<int*>(smem + TmaSmem::scan);
-    uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + TmaSmem::bars);
-    volatile float* s_meta = reinterpret_cast<volatile float*>(smem + Fp8Smem::meta);
+    float* s_merge = reinterpret_cast<float*>(smem + L::merge);
+    int* s_tp = reinterpret_cast<int*>(smem + L::prefix);
+    int* s_scan = reinterpret_cast<int*>(smem + L::scan);
+    uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + L::bars);
+    volatile float* s_meta = reinterpret_cast<volatile float*>(smem + L::meta);
     const uint32_t tiles_u32 = smem_u32(smem);
     const uint32_t full0 = smem_u32(s_bar), empty0 = full0 + kStages * 8;
 
@@ -472,7 +488,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_fp8_kernel(DecodePa
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(full0 + s * 8, 1);
-            mbar_init(empty0 + s * 8, kConsumerWarps);
+            mbar_init(empty0 + s * 8, W);
         }
         fence_mbar_init();
         fence_proxy_async();
@@ -494,7 +510,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_fp8_kernel(DecodePa
     }
     const int lo = min(total, int(blockIdx.x) * chunk), hi = min(total, lo + chunk);
 
-    if (warp == kConsumerWarps) {
+    if (warp == W) {
         // ------------------------------------------------------------ producer
         if (lane != 0) return;
         tma_prefetch_desc(&map_k);
@@ -533,6 +549,11 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_fp8_kernel(DecodePa
     }
 
     // ---------------------------------------------------------------- consumers: 32 tokens per warp and tile
+    // Token-major products: the 16 rows of an MMA are TOKENS (all used), the 8 columns the query
+    // heads of the group.  S^T[token][head] = K Q^T takes 16 products per 32 tokens, and
+    // O^T[dim][head] += V^T P^T another 16, half of what head-major products need, with 32
+    // accumulator registers instead of 64.  A lane holds, for the heads (2t, 2t+1) of its quad
+    // position t, the scores of four tokens and the output dims (16c + 2g, 16c + 2g + 1), c = 0..7.
     const int tw = warp;
     const int gid = lane >> 2, tig = lane & 3;
     const int mi = lane >> 3, mr = lane & 7;
@@ -543,27 +564,28 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_fp8_kernel(DecodePa
         const Segment sg = locate_segment(s_tp, p.batch, ng, g, hi);
         const int ctx = p.context_lens[sg.b];
         const int head = sg.hg;
-        // Query fragments in f16.  MMA k-slots (2t, 2t+1, 2t+8, 2t+9) of a 16-dim chunk carry
-        // dims (4t, 4t+1, 4t+2, 4t+3): the order in which ldmatrix hands out e4m3 bytes.
-        uint32_t qa[8][2];
+        // B fragments of Q^T in f16: column gid is query head gid of the group.  MMA k-slots
+        // (2t, 2t+1, 2t+8, 2t+9) of a 16-dim chunk carry dims (4t, 4t+1, 4t+2, 4t+3): the order in
+        // which ldmatrix hands out e4m3 bytes.
+        uint32_t qb[8][2];
         {
             const __nv_bfloat16* qrow = p.q + (int64_t(sg.b) * p.n_q_heads + head * p.group + gid) * kHeadDim;
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
-                qa[c][0] = qa[c][1] = 0u;
+                qb[c][0] = qb[c][1] = 0u;
                 if (gid < p.group) {
                     const uint2 raw = *reinterpret_cast<const uint2*>(qrow + c * 16 + tig * 4);
                     const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
                     const __nv_bfloat162 y = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-                    qa[c][0] = pack_f16(__low2float(x), __high2float(x));
-                    qa[c][1] = pack_f16(__low2float(y), __high2float(y));
+                    qb[c][0] = pack_f16(__low2float(x), __high2float(x));
+                    qb[c][1] = pack_f16(__low2float(y), __high2float(y));
                 }
             }
         }
-        float o[16][4];
+        float o[8][4];                           // O^T: tile c, rows (dims 16c + 2g, 16c + 2g + 1), columns (heads 2t, 2t+1)
 #pragma unroll
-        for (int j = 0; j < 16; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
-        float m_run = -INFINITY, l_run = 0.f;
+        for (int j = 0; j < 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+        float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};   // per head (2t, 2t+1)
         float s_cur = 0.f;                       // V scale the accumulator is currently expressed in
 
         for (int t = sg.t0; t < sg.t1; ++t, ++it) {
@@ -571,60 +593,85 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_fp8_kernel(DecodePa
             if (ok && !mbar_wait(full0 + s * 8, ph)) ok = false;
             const float c_k = s_meta[s * 2 + 0] * p.scale_log2;
             const float vs = s_meta[s * 2 + 1];
-            const int row0 = tw * 32;                       // this warp's 32 tokens of the tile
+            const int row0 = tw * TPW;                      // this warp's tokens of the tile
             const int valid = ctx - (t * TT + row0);
             if (ok && valid > 0) {
                 const uint32_t kbase = tiles_u32 + s * (2 * kTileBytes);
                 const uint32_t vbase = kbase + kTileBytes;
-                // S for 32 tokens: four independent accumulator tiles of 8 tokens each
-                float sc[4][4];
+                // S^T: NH 16-token tiles, each with an even-chunk and an odd-chunk accumulator
+                float sc[NH][2][4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+                for (int h = 0; h < NH; ++h)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) sc[h][e][0] = sc[h][e][1] = sc[h][e][2] = sc[h][e][3] = 0.f;
 #pragma unroll
                 for (int c2 = 0; c2 < 4; ++c2) {
 #pragma unroll
-                    for (int h = 0; h < 2; ++h) {
+                    for (int h = 0; h < NH; ++h) {
                         uint32_t r0, r1, r2, r3;   // (tokens 0-7, chunk 2c2), (0-7, 2c2+1), (8-15, 2c2), (8-15, 2c2+1) of half h
                         ldsm_x4(kbase + swz128(row0 + h * 16 + (mi >> 1) * 8 + mr, c2 * 2 + (mi & 1)), r0, r1, r2, r3);
-                        mma_f16(sc[2 * h], qa[2 * c2][0], 0u, qa[2 * c2][1], 0u, e4m3x2_to_f16x2(r0), e4m3x2_to_f16x2(r0 >> 16));
-                        mma_f16(sc[2 * h + 1], qa[2 * c2][0], 0u, qa[2 * c2][1], 0u, e4m3x2_to_f16x2(r2), e4m3x2_to_f16x2(r2 >> 16));
-                        mma_f16(sc[2 * h], qa[2 * c2 + 1][0], 0u, qa[2 * c2 + 1][1], 0u, e4m3x2_to_f16x2(r1), e4m3x2_to_f16x2(r1 >> 16));
-                        mma_f16(sc[2 * h + 1], qa[2 * c2 + 1][0], 0u, qa[2 * c2 + 1][1], 0u, e4m3x2_to_f16x2(r3), e4m3x2_to_f16x2(r3 >> 16));
+                        mma_f16(sc[h][0], e4m3x2_to_f16x2(r0), e4m3x2_to_f16x2(r2), e4m3x2_to_f16x2(r0 >> 16), e4m3x2_to_f16x2(r2 >> 16),
+                                qb[2 * c2][0], qb[2 * c2][1]);
+                        mma_f16(sc[h][1], e4m3x2_to_f16x2(r1), e4m3x2_to_f16x2(r3), e4m3x2_to_f16x2(r1 >> 16), e4m3x2_to_f16x2(r3 >> 16),
+                                qb[2 * c2 + 1][0], qb[2 * c2 + 1][1]);
                     }
                 }
-                if (valid < 32) {
+                // sv[h][x][y]: token 16h + 8x + gid, head 2 tig + y
+                float sv[NH][2][2];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        if (j * 8 + 2 * tig >= valid) sc[j][0] = -INFINITY;
-                        if (j * 8 + 2 * tig + 1 >= valid) sc[j][1] = -INFINITY;
+                for (int h = 0; h < NH; ++h)
+#pragma unroll
+                    for (int x = 0; x < 2; ++x) {
+                        const bool dead = h * 16 + x * 8 + gid >= valid;
+                        sv[h][x][0] = dead ? -INFINITY : sc[h][0][2 * x] + sc[h][1][2 * x];
+                        sv[h][x][1] = dead ? -INFINITY : sc[h][0][2 * x + 1] + sc[h][1][2 * x + 1];
                     }
-                }
-                float mx = fmaxf(fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1])),
-                                 fmaxf(fmaxf(sc[2][0], sc[2][1]), fmaxf(sc[3][0], sc[3][1])));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-                // with c_k == 0 (all-zero page) every visible logit is 0; masked ones stay -inf
-                const float m_new = fmaxf(m_run, c_k > 0.f ? mx * c_k : 0.f);
-                float alpha = fast_exp2(m_run - m_new);
-                float pr[4][2];
-                float rs = 0.f;
+                float alpha[2];
+                uint32_t pp[NH][2];                         // P as f16 pairs (head 2t, head 2t+1): [h][x] = token 16h + 8x + gid
+                float pr[NH][2][2];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    pr[j][0] = sc[j][0] == -INFINITY ? 0.f : fast_exp2(fmaf(sc[j][0], c_k, -m_new));
-                    pr[j][1] = sc[j][1] == -INFINITY ? 0.f : fast_exp2(fmaf(sc[j][1], c_k, -m_new));
-                    rs += pr[j][0] + pr[j][1];
+                for (int y = 0; y < 2; ++y) {
+                    float mx = fmaxf(sv[0][0][y], sv[0][1][y]);
+                    if (NH == 2) mx = fmaxf(mx, fmaxf(sv[NH - 1][0][y], sv[NH - 1][1][y]));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                    // with c_k == 0 (all-zero page) every visible logit is 0; masked ones stay -inf
+                    const float m_new = fmaxf(m_run[y], c_k > 0.f ? mx * c_k : 0.f);
+                    alpha[y] = fast_exp2(m_run[y] - m_new);
+                    float rs = 0.f;
+#pragma unroll
+                    for (int h = 0; h < NH; ++h)
+#pragma unroll
+                        for (int x = 0; x < 2; ++x) {
+                            pr[h][x][y] = sv[h][x][y] == -INFINITY ? 0.f : fast_exp2(fmaf(sv[h][x][y], c_k, -m_new));
+                            rs += pr[h][x][y];
+                        }
+                    l_run[y] = l_run[y] * alpha[y] + rs;
+                    m_run[y] = m_new;
                 }
-                l_run = l_run * alpha + rs;
-                m_run = m_new;
+#pragma unroll
+                for (int h = 0; h < NH; ++h)
+#pragma unroll
+                    for (int x = 0; x < 2; ++x) pp[h][x] = pack_f16(pr[h][x][0], pr[h][x][1]);
                 if (vs > 0.f && vs != s_cur) {       // re-express the accumulator in this page's V scale
-                    if (s_cur > 0.f) alpha *= __fdividef(s_cur, vs);
+                    if (s_cur > 0.f) {
+                        const float f = __fdividef(s_cur, vs);
+                        alpha[0] *= f;
+                        alpha[1] *= f;
+                    }
                     s_cur = vs;
                 }
 #pragma unroll
-                for (int j = 0; j < 16; ++j) { o[j][0] *= alpha; o[j][1] *= alpha; }
+                for (int j = 0; j < 8; ++j) {
+                    o[j][0] *= alpha[0]; o[j][2] *= alpha[0];
+                    o[j][1] *= alpha[1]; o[j][3] *= alpha[1];
+                }
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const uint32_t pa0 = pack_f16(pr[2 * h][0], pr[2 * h][1]), pa2 = pack_f16(pr[2 * h + 1][0], pr[2 * h + 1][1]);
+                for (int h = 0; h < NH; ++h) {
+                    // B fragments of P^T: transposing the two 8x8 blocks (tokens x heads) turns "token gid, heads
+                    // 2t 2t+1" into "head gid, tokens 2t 2t+1"
+                    const uint32_t pb0 = movmatrix_trans(pp[h][0]), pb1 = movmatrix_trans(pp[h][1]);
                     const int vh = valid - h * 16;          // tokens of this half that exist
 #pragma unroll
                     for (int c2 = 0; c2 < 4; ++c2) {
@@ -636,73 +683,93 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_fp8_kernel(DecodePa
                             r0 &= keep_lo; r2 &= keep_lo;
                             r1 &= keep_hi; r3 &= keep_hi;
                         }
-                        // a transposed register holds (tok 2t, dims 2g 2g+1 | tok 2t+1, dims 2g 2g+1):
-                        // bytes (0,2) feed the even-dim tile, bytes (1,3) the odd-dim tile
-                        mma_f16(o[4 * c2 + 0], pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(__byte_perm(r0, 0, 0x0020)), e4m3x2_to_f16x2(__byte_perm(r1, 0, 0x0020)));
-                        mma_f16(o[4 * c2 + 1], pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(__byte_perm(r0, 0, 0x0031)), e4m3x2_to_f16x2(__byte_perm(r1, 0, 0x0031)));
-                        mma_f16(o[4 * c2 + 2], pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(__byte_perm(r2, 0, 0x0020)), e4m3x2_to_f16x2(__byte_perm(r3, 0, 0x0020)));
-                        mma_f16(o[4 * c2 + 3], pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(__byte_perm(r2, 0, 0x0031)), e4m3x2_to_f16x2(__byte_perm(r3, 0, 0x0031)));
+                        // a transposed register holds (tok 2t, dims 2g 2g+1 | tok 2t+1, dims 2g 2g+1): bytes (0,2) are the
+                        // even dim's two tokens (A rows 0-7 of the tile), bytes (1,3) the odd dim's (A rows 8-15)
+                        mma_f16(o[2 * c2], e4m3x2_to_f16x2(__byte_perm(r0, 0, 0x0020)), e4m3x2_to_f16x2(__byte_perm(r0, 0, 0x0031)),
+                                e4m3x2_to_f16x2(__byte_perm(r1, 0, 0x0020)), e4m3x2_to_f16x2(__byte_perm(r1, 0, 0x0031)), pb0, pb1);
+                        mma_f16(o[2 * c2 + 1], e4m3x2_to_f16x2(__byte_perm(r2, 0, 0x0020)), e4m3x2_to_f16x2(__byte_perm(r2, 0, 0x0031)),
+                                e4m3x2_to_f16x2(__byte_perm(r3, 0, 0x0020)), e4m3x2_to_f16x2(__byte_perm(r3, 0, 0x0031)), pb0, pb1);
                     }
                 }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(empty0 + s * 8);
         }
-        l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
-        l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+        // row sums over the warp's tokens (lanes of equal t); m_run is already equal in those lanes
+#pragma unroll
+        for (int y = 0; y < 2; ++y) {
+            l_run[y] += __shfl_xor_sync(0xffffffffu, l_run[y], 4);
+            l_run[y] += __shfl_xor_sync(0xffffffffu, l_run[y], 8);
+            l_run[y] += __shfl_xor_sync(0xffffffffu, l_run[y], 16);
+        }
         // back to true units before warps (which may sit on different pages) are merged
 #pragma unroll
-        for (int j = 0; j < 16; ++j) { o[j][0] *= s_cur; o[j][1] *= s_cur; }
+        for (int j = 0; j < 8; ++j) { o[j][0] *= s_cur; o[j][1] *= s_cur; o[j][2] *= s_cur; o[j][3] *= s_cur; }
 
+        // merge the warps' partial results through four shared slots: warps [src, src + n) hand theirs to warps [dst, dst + n)
+        auto merge_round = [&](int src, int dst, int n) {
+            if (tw >= src && tw < src + n) {
+                float* slot = s_merge + (tw - src) * kMergeSlotFloats;
 #pragma unroll
-        for (int stride = kConsumerWarps / 2; stride >= 1; stride >>= 1) {
-            float* slot = s_merge + (tw % stride) * kMergeSlotFloats;
-            if (tw >= stride && tw < 2 * stride) {
+                for (int j = 0; j < 8; ++j)
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    slot[(2 * j) * 32 + lane] = o[j][0];
-                    slot[(2 * j + 1) * 32 + lane] = o[j][1];
-                }
-                slot[32 * 32 + lane] = m_run;
-                slot[33 * 32 + lane] = l_run;
+                    for (int k = 0; k < 4; ++k) slot[(4 * j + k) * 32 + lane] = o[j][k];
+                slot[32 * 32 + lane] = m_run[0];
+                slot[33 * 32 + lane] = m_run[1];
+                slot[34 * 32 + lane] = l_run[0];
+                slot[35 * 32 + lane] = l_run[1];
             }
             consumer_bar();
-            if (tw < stride) {
-                const float m2 = slot[32 * 32 + lane], l2 = slot[33 * 32 + lane];
-                const float mm = fmaxf(m_run, m2);
-                const float a1 = m_run == -INFINITY ? 0.f : fast_exp2(m_run - mm);
-                const float a2 = m2 == -INFINITY ? 0.f : fast_exp2(m2 - mm);
+            if (tw >= dst && tw < dst + n) {
+                const float* slot = s_merge + (tw - dst) * kMergeSlotFloats;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    o[j][0] = o[j][0] * a1 + slot[(2 * j) * 32 + lane] * a2;
-                    o[j][1] = o[j][1] * a1 + slot[(2 * j + 1) * 32 + lane] * a2;
+                for (int y = 0; y < 2; ++y) {
+                    const float m2 = slot[(32 + y) * 32 + lane], l2 = slot[(34 + y) * 32 + lane];
+                    const float mm = fmaxf(m_run[y], m2);
+                    const float a1 = m_run[y] == -INFINITY ? 0.f : fast_exp2(m_run[y] - mm);
+                    const float a2 = m2 == -INFINITY ? 0.f : fast_exp2(m2 - mm);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        o[j][y] = o[j][y] * a1 + slot[(4 * j + y) * 32 + lane] * a2;
+                        o[j][y + 2] = o[j][y + 2] * a1 + slot[(4 * j + y + 2) * 32 + lane] * a2;
+                    }
+                    l_run[y] = l_run[y] * a1 + l2 * a2;
+                    m_run[y] = mm;
                 }
-                l_run = l_run * a1 + l2 * a2;
-                m_run = mm;
             }
             consumer_bar();
+        };
+        if (W == 16) {
+            merge_round(12, 8, 4);
+            merge_round(8, 0, 4);       // warps 8-11 now carry 8-15
         }
+        merge_round(4, 0, 4);
+        merge_round(2, 0, 2);
+        merge_round(1, 0, 1);
 
-        if (ok && tw == 0 && gid < p.group) {
-            // accumulator tile 2c + e, column pair (2t, 2t+1) holds dims 16c + 4t + e and 16c + 4t + 2 + e
+        if (ok && tw == 0) {
+            // tile c holds dims (16c + 2g, 16c + 2g + 1) in (o[c][y], o[c][y + 2]) for head 2t + y
             const bool complete = sg.t0 == 0 && sg.t1 == sg.ntiles;
-            const int qh = head * p.group + gid;
-            if (complete) {
-                const float inv = 1.f / l_run;
-                uint2* dst = reinterpret_cast<uint2*>(p.out + (int64_t(sg.b) * p.n_q_heads + qh) * kHeadDim);
 #pragma unroll
-                for (int c = 0; c < 8; ++c)
-                    dst[c * 4 + tig] = make_uint2(pack_bf16(o[2 * c][0] * inv, o[2 * c + 1][0] * inv),
-                                                  pack_bf16(o[2 * c][1] * inv, o[2 * c + 1][1] * inv));
-            } else {
-                const int rows = p.group;
-                const int64_t slot = int64_t(blockIdx.x) * 2 + (sg.t0 > 0 ? 0 : 1);
-                float4* dst = reinterpret_cast<float4*>(p.ws_o + (slot * rows + gid) * kHeadDim);
+            for (int y = 0; y < 2; ++y) {
+                const int hq = 2 * tig + y;
+                if (hq >= p.group) continue;
+                const int qh = head * p.group + hq;
+                if (complete) {
+                    const float inv = 1.f / l_run[y];
+                    uint32_t* dst = reinterpret_cast<uint32_t*>(p.out + (int64_t(sg.b) * p.n_q_heads + qh) * kHeadDim);
 #pragma unroll
-                for (int c = 0; c < 8; ++c) dst[c * 4 + tig] = make_float4(o[2 * c][0], o[2 * c + 1][0], o[2 * c][1], o[2 * c + 1][1]);
-                if (tig == 0) {
-                    p.ws_ml[(slot * rows + gid) * 2 + 0] = m_run;
-                    p.ws_ml[(slot * rows + gid) * 2 + 1] = l_run;
+                    for (int c = 0; c < 8; ++c) dst[c * 8 + gid] = pack_bf16(o[c][y] * inv, o[c][y + 2] * inv);
+                } else {
+                    const int rows = p.group;
+                    const int64_t slot = int64_t(blockIdx.x) * 2 + (sg.t0 > 0 ? 0 : 1);
+                    float2* dst = reinterpret_cast<float2*>(p.ws_o + (slot * rows + hq) * kHeadDim);
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) dst[c * 8 + gid] = make_float2(o[c][y], o[c][y + 2]);
+                    if (gid == 0) {
+                        p.ws_ml[(slot * rows + hq) * 2 + 0] = m_run[y];
+                        p.ws_ml[(slot * rows + hq) * 2 + 1] = l_run[y];
+                    }
                 }
             }
         }
@@ -829,9 +896,10 @@ int infer_paged_decode(const infer_kv_pool_t* pool, void* out, const void* q, co
     p.ws_o = reinterpret_cast<float*>(ws + lay.o_off);
 
     if (cfg.impl == 2 && pool->dtype == INFER_KV_E4M3) {
-        const int smem = Fp8Smem::total + 1024;
-        IB_CUDA(cudaFuncSetAttribute(decode_tma_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        IB_CUDA(launch_pdl(decode_tma_fp8_kernel, dim3(cfg.grid), dim3(kTmaThreads), smem, st, p, pool->maps[4].k, pool->maps[4].v));
+        const int smem_t = Fp8Smem<8>::total + 1024;
+        IB_CUDA(cudaFuncSetAttribute(decode_tma_fp8_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_t));
+        IB_CUDA(launch_pdl(decode_tma_fp8_kernel<8>, dim3(cfg.grid), dim3(Fp8Smem<8>::threads), smem_t, st, p,
+                           pool->maps[4].k, pool->maps[4].v));
     } else if (cfg.impl == 2) {
         int rc = INFER_OK;
         switch (cfg.hpc) {
