@@ -172,6 +172,13 @@ __device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t x) {
     __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(x & 0xffffu), __NV_E4M3);
     return uint32_t(h.x) | (uint32_t(h.y) << 16);
 }
+// four e4m3 bytes -> two f16x2 (bytes 0,1 and bytes 2,3), exact: two conversions and nothing else
+__device__ __forceinline__ void e4m3x4_to_f16x2x2(uint32_t x, uint32_t& lo, uint32_t& hi) {
+    asm("{\n\t.reg .b16 a, b;\n\tmov.b32 {a, b}, %2;\n\t"
+        "cvt.rn.f16x2.e4m3x2 %0, a;\n\tcvt.rn.f16x2.e4m3x2 %1, b;\n\t}"
+        : "=r"(lo), "=r"(hi)
+        : "r"(x));
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&t);

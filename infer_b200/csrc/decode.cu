@@ -610,10 +610,13 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) decode_tma_fp8_kernel(DecodeP
                     for (int h = 0; h < NH; ++h) {
                         uint32_t r0, r1, r2, r3;   // (tokens 0-7, chunk 2c2), (0-7, 2c2+1), (8-15, 2c2), (8-15, 2c2+1) of half h
                         ldsm_x4(kbase + swz128(row0 + h * 16 + (mi >> 1) * 8 + mr, c2 * 2 + (mi & 1)), r0, r1, r2, r3);
-                        mma_f16(sc[h][0], e4m3x2_to_f16x2(r0), e4m3x2_to_f16x2(r2), e4m3x2_to_f16x2(r0 >> 16), e4m3x2_to_f16x2(r2 >> 16),
-                                qb[2 * c2][0], qb[2 * c2][1]);
-                        mma_f16(sc[h][1], e4m3x2_to_f16x2(r1), e4m3x2_to_f16x2(r3), e4m3x2_to_f16x2(r1 >> 16), e4m3x2_to_f16x2(r3 >> 16),
-                                qb[2 * c2 + 1][0], qb[2 * c2 + 1][1]);
+                        uint32_t a0, a1, a2, a3;
+                        e4m3x4_to_f16x2x2(r0, a0, a2);      // token gid: dims (4t, 4t+1) and (4t+2, 4t+3) of chunk 2c2
+                        e4m3x4_to_f16x2x2(r2, a1, a3);      // token gid + 8
+                        mma_f16(sc[h][0], a0, a1, a2, a3, qb[2 * c2][0], qb[2 * c2][1]);
+                        e4m3x4_to_f16x2x2(r1, a0, a2);      // chunk 2c2 + 1
+                        e4m3x4_to_f16x2x2(r3, a1, a3);
+                        mma_f16(sc[h][1], a0, a1, a2, a3, qb[2 * c2 + 1][0], qb[2 * c2 + 1][1]);
                     }
                 }
                 // sv[h][x][y]: token 16h + 8x + gid, head 2 tig + y
@@ -685,10 +688,14 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) decode_tma_fp8_kernel(DecodeP
                         }
                         // a transposed register holds (tok 2t, dims 2g 2g+1 | tok 2t+1, dims 2g 2g+1): bytes (0,2) are the
                         // even dim's two tokens (A rows 0-7 of the tile), bytes (1,3) the odd dim's (A rows 8-15)
-                        mma_f16(o[2 * c2], e4m3x2_to_f16x2(__byte_perm(r0, 0, 0x0020)), e4m3x2_to_f16x2(__byte_perm(r0, 0, 0x0031)),
-                                e4m3x2_to_f16x2(__byte_perm(r1, 0, 0x0020)), e4m3x2_to_f16x2(__byte_perm(r1, 0, 0x0031)), pb0, pb1);
-                        mma_f16(o[2 * c2 + 1], e4m3x2_to_f16x2(__byte_perm(r2, 0, 0x0020)), e4m3x2_to_f16x2(__byte_perm(r2, 0, 0x0031)),
-                                e4m3x2_to_f16x2(__byte_perm(r3, 0, 0x0020)), e4m3x2_to_f16x2(__byte_perm(r3, 0, 0x0031)), pb0, pb1);
+                        // one byte permute (0,2,1,3) per register, then the low half converts to A rows 0-7, the high half to 8-15
+                        uint32_t a0, a1, a2, a3;
+                        e4m3x4_to_f16x2x2(__byte_perm(r0, 0, 0x3120), a0, a1);
+                        e4m3x4_to_f16x2x2(__byte_perm(r1, 0, 0x3120), a2, a3);
+                        mma_f16(o[2 * c2], a0, a1, a2, a3, pb0, pb1);
+                        e4m3x4_to_f16x2x2(__byte_perm(r2, 0, 0x3120), a0, a1);
+                        e4m3x4_to_f16x2x2(__byte_perm(r3, 0, 0x3120), a2, a3);
+                        mma_f16(o[2 * c2 + 1], a0, a1, a2, a3, pb0, pb1);
                     }
                 }
             }
