@@ -311,8 +311,8 @@ struct Divisor {
             neg_s2 = pk2(-s_, -s_);
         }
     }
-    // a 32-bit word holding two bf16 values -> the two e4m3 bytes of their quotients
-    __device__ __forceinline__ uint32_t quantise2(uint32_t w) const {
+    // a 32-bit word holding two bf16 values -> their two quotients
+    __device__ __forceinline__ float2 divide2(uint32_t w) const {
         const float lo = __uint_as_float(w << 16), hi = __uint_as_float(w & 0xffff0000u);
         float2 q;
         if (fast) {
@@ -323,11 +323,24 @@ struct Divisor {
         } else {
             q = make_float2(__fdiv_rn(lo, s), __fdiv_rn(hi, s));
         }
-        return uint32_t(__nv_cvt_float2_to_fp8x2(q, __NV_SATFINITE, __NV_E4M3));
+        return q;
+    }
+    // two 32-bit words (four bf16 values) -> the four e4m3 bytes of their quotients: one conversion
+    // instruction per pair (round to nearest even, saturating), the halves joined by register naming
+    __device__ __forceinline__ uint32_t quantise4(uint32_t w0, uint32_t w1) const {
+        const float2 a = divide2(w0), b = divide2(w1);
+        uint32_t out;
+        asm("{\n\t.reg .b16 lo, hi;\n\t"
+            "cvt.rn.satfinite.e4m3x2.f32 lo, %2, %1;\n\t"
+            "cvt.rn.satfinite.e4m3x2.f32 hi, %4, %3;\n\t"
+            "mov.b32 %0, {lo, hi};\n\t}"
+            : "=r"(out)
+            : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+        return out;
     }
     __device__ __forceinline__ uint2 quantise8(const uint4& raw) const {
         if (!(s > 0.0f)) return make_uint2(0, 0);
-        return make_uint2(quantise2(raw.x) | (quantise2(raw.y) << 16), quantise2(raw.z) | (quantise2(raw.w) << 16));
+        return make_uint2(quantise4(raw.x, raw.y), quantise4(raw.z, raw.w));
     }
 };
 
