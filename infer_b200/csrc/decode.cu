@@ -452,28 +452,36 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_kernel(DecodeParams
 // online-softmax correction, so no per-element dequantisation multiply is needed.
 constexpr int kFp8TileTokens = 256;
 
-// W consumer warps (8 or 16; 16 was measured 5 % slower): 256 / W tokens per warp and tile.
-template <int W>
+// HPC kv heads per tile (1 or 2): a tile is 256 / HPC tokens of HPC adjacent heads, loaded head by head
+// (one TMA box of 128-byte rows each) into [head][token][128 B].  With two heads the two boxes fetch the
+// adjacent 128-byte halves of the same 256 bytes of every token row back to back, which is what the bf16
+// kernel's two column halves do; with one head every row is a lone 128-byte line at a pitch of Hkv * 128 B
+// (measured: 8 heads per token 112 us, the same bytes as a single-head pool 98 us).  Eight consumer warps,
+// 32 tokens per warp and tile; sixteen warps of 16 tokens were measured slower.
+template <int HPC>
 struct Fp8Smem {
-    static constexpr int threads = (W + 1) * 32;
+    static constexpr int threads = kTmaThreads;
     static constexpr int merge = TmaSmem::tiles;
     static constexpr int prefix = merge + 4 * kMergeSlotFloats * 4;
     static constexpr int scan = prefix + (kMaxBatch + 1) * 4 + 12;
     static constexpr int bars = scan + threads * 4;
-    static constexpr int meta = bars + 2 * kStages * 8 + 16;      // [kStages][2] floats: k scale, v scale
-    static constexpr int total = meta + kStages * 8;
+    static constexpr int meta = bars + 2 * kStages * 8 + 16;      // [kStages][HPC][2] floats: k scale, v scale
+    static constexpr int total = meta + kStages * HPC * 8;
 };
 
-template <int W>
-__global__ void __launch_bounds__((W + 1) * 32, 1) decode_tma_fp8_kernel(DecodeParams p,
+template <int HPC>
+__global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_fp8_kernel(DecodeParams p,
                                                                           const __grid_constant__ CUtensorMap map_k,
                                                                           const __grid_constant__ CUtensorMap map_v) {
-    constexpr int TT = kFp8TileTokens;
-    constexpr int TPW = TT / W;                  // tokens per warp and tile
+    static_assert(HPC == 1 || HPC == 2, "one or two kv heads per tile");
+    constexpr int W = kConsumerWarps;
+    constexpr int TT = kFp8TileTokens / HPC;     // tokens per tile
+    constexpr int WPH = W / HPC;                 // consumer warps per head
+    constexpr int TPW = TT / WPH;                // tokens per warp and tile
     constexpr int NH = TPW / 16;                 // 16-token MMA tiles per warp and tile
-    static_assert(W == 8 || W == 16, "8 or 16 consumer warps");
-    using L = Fp8Smem<W>;
-    auto consumer_bar = [] { asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory"); };
+    constexpr int kHeadBytes = TT * 128;         // one head's K (or V) rows of a tile
+    static_assert(TPW == 32, "32 tokens per warp and tile");
+    using L = Fp8Smem<HPC>;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     float* s_merge = reinterpret_cast<float*>(smem + L::merge);
@@ -497,7 +505,7 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) decode_tma_fp8_kernel(DecodeP
     pdl_launch_dependents();
     pdl_wait();
 
-    const int ng = p.n_kv_heads;
+    const int ng = p.n_kv_heads / HPC;
     const int total = ng * s_tp[p.batch];
     const int chunk = max(1, (total + int(gridDim.x) - 1) / int(gridDim.x));
     if (blockIdx.x == 0) {
@@ -526,16 +534,26 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) decode_tma_fp8_kernel(DecodeP
                 const int page = table[tok0 / p.block_size];
                 const int slot0 = page * p.block_size + tok0 % p.block_size;
                 const bool page_ok = page >= 0 && page < p.num_blocks;
-                const float ks = page_ok ? p.k_scale[int64_t(page) * p.n_kv_heads + sg.hg] : 0.f;
-                const float vs = page_ok ? p.v_scale[int64_t(page) * p.n_kv_heads + sg.hg] : 0.f;
+                float ks[HPC], vs[HPC];
+#pragma unroll
+                for (int hl = 0; hl < HPC; ++hl) {
+                    ks[hl] = page_ok ? p.k_scale[int64_t(page) * p.n_kv_heads + sg.hg * HPC + hl] : 0.f;
+                    vs[hl] = page_ok ? p.v_scale[int64_t(page) * p.n_kv_heads + sg.hg * HPC + hl] : 0.f;
+                }
                 if (!mbar_wait(empty0 + s * 8, ph ^ 1)) { ok = false; break; }
-                s_meta[s * 2 + 0] = ks;
-                s_meta[s * 2 + 1] = vs;
+#pragma unroll
+                for (int hl = 0; hl < HPC; ++hl) {
+                    s_meta[(s * HPC + hl) * 2 + 0] = ks[hl];
+                    s_meta[(s * HPC + hl) * 2 + 1] = vs[hl];
+                }
                 const uint32_t bar = full0 + s * 8;
                 const uint32_t kdst = tiles_u32 + s * (2 * kTileBytes), vdst = kdst + kTileBytes;
                 mbar_expect_tx(bar, 2 * kTileBytes);      // release: the scales above are visible to the waiters
-                tma_load_3d(kdst, &map_k, bar, 0, sg.hg, slot0);
-                tma_load_3d(vdst, &map_v, bar, 0, sg.hg, slot0);
+#pragma unroll
+                for (int hl = 0; hl < HPC; ++hl) {        // the heads' boxes back to back: adjacent lines of every token row
+                    tma_load_3d(kdst + hl * kHeadBytes, &map_k, bar, 0, sg.hg * HPC + hl, slot0);
+                    tma_load_3d(vdst + hl * kHeadBytes, &map_v, bar, 0, sg.hg * HPC + hl, slot0);
+                }
             }
             g += sg.t1 - sg.t0;
         }
@@ -554,7 +572,7 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) decode_tma_fp8_kernel(DecodeP
     // O^T[dim][head] += V^T P^T another 16, half of what head-major products need, with 32
     // accumulator registers instead of 64.  A lane holds, for the heads (2t, 2t+1) of its quad
     // position t, the scores of four tokens and the output dims (16c + 2g, 16c + 2g + 1), c = 0..7.
-    const int tw = warp;
+    const int hl = warp / WPH, tw = warp % WPH;      // head of the tile, warp within that head
     const int gid = lane >> 2, tig = lane & 3;
     const int mi = lane >> 3, mr = lane & 7;
     uint32_t it = 0;
@@ -563,7 +581,7 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) decode_tma_fp8_kernel(DecodeP
     for (int g = lo; g < hi;) {
         const Segment sg = locate_segment(s_tp, p.batch, ng, g, hi);
         const int ctx = p.context_lens[sg.b];
-        const int head = sg.hg;
+        const int head = sg.hg * HPC + hl;
         // B fragments of Q^T in f16: column gid is query head gid of the group.  MMA k-slots
         // (2t, 2t+1, 2t+8, 2t+9) of a 16-dim chunk carry dims (4t, 4t+1, 4t+2, 4t+3): the order in
         // which ldmatrix hands out e4m3 bytes.
@@ -591,12 +609,12 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) decode_tma_fp8_kernel(DecodeP
         for (int t = sg.t0; t < sg.t1; ++t, ++it) {
             const uint32_t s = it % kStages, ph = (it / kStages) & 1;
             if (ok && !mbar_wait(full0 + s * 8, ph)) ok = false;
-            const float c_k = s_meta[s * 2 + 0] * p.scale_log2;
-            const float vs = s_meta[s * 2 + 1];
+            const float c_k = s_meta[(s * HPC + hl) * 2 + 0] * p.scale_log2;
+            const float vs = s_meta[(s * HPC + hl) * 2 + 1];
             const int row0 = tw * TPW;                      // this warp's tokens of the tile
             const int valid = ctx - (t * TT + row0);
             if (ok && valid > 0) {
-                const uint32_t kbase = tiles_u32 + s * (2 * kTileBytes);
+                const uint32_t kbase = tiles_u32 + s * (2 * kTileBytes) + hl * kHeadBytes;
                 const uint32_t vbase = kbase + kTileBytes;
                 // S^T: NH 16-token tiles, each with an even-chunk and an odd-chunk accumulator
                 float sc[NH][2][4];
@@ -713,10 +731,12 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) decode_tma_fp8_kernel(DecodeP
 #pragma unroll
         for (int j = 0; j < 8; ++j) { o[j][0] *= s_cur; o[j][1] *= s_cur; o[j][2] *= s_cur; o[j][3] *= s_cur; }
 
-        // merge the warps' partial results through four shared slots: warps [src, src + n) hand theirs to warps [dst, dst + n)
-        auto merge_round = [&](int src, int dst, int n) {
-            if (tw >= src && tw < src + n) {
-                float* slot = s_merge + (tw - src) * kMergeSlotFloats;
+        // merge the partial results of a head's warps through shared slots (four in all): warps [n, 2n) of
+        // every head hand theirs to warps [0, n)
+#pragma unroll
+        for (int n = WPH / 2; n >= 1; n >>= 1) {
+            float* slot = s_merge + (hl * (WPH / 2) + (tw % n)) * kMergeSlotFloats;
+            if (tw >= n && tw < 2 * n) {
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
 #pragma unroll
@@ -727,8 +747,7 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) decode_tma_fp8_kernel(DecodeP
                 slot[35 * 32 + lane] = l_run[1];
             }
             consumer_bar();
-            if (tw >= dst && tw < dst + n) {
-                const float* slot = s_merge + (tw - dst) * kMergeSlotFloats;
+            if (tw < n) {
 #pragma unroll
                 for (int y = 0; y < 2; ++y) {
                     const float m2 = slot[(32 + y) * 32 + lane], l2 = slot[(34 + y) * 32 + lane];
@@ -745,14 +764,7 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) decode_tma_fp8_kernel(DecodeP
                 }
             }
             consumer_bar();
-        };
-        if (W == 16) {
-            merge_round(12, 8, 4);
-            merge_round(8, 0, 4);       // warps 8-11 now carry 8-15
         }
-        merge_round(4, 0, 4);
-        merge_round(2, 0, 2);
-        merge_round(1, 0, 1);
 
         if (ok && tw == 0) {
             // tile c holds dims (16c + 2g, 16c + 2g + 1) in (o[c][y], o[c][y + 2]) for head 2t + y
@@ -768,14 +780,14 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) decode_tma_fp8_kernel(DecodeP
 #pragma unroll
                     for (int c = 0; c < 8; ++c) dst[c * 8 + gid] = pack_bf16(o[c][y] * inv, o[c][y + 2] * inv);
                 } else {
-                    const int rows = p.group;
+                    const int rows = HPC * p.group, r = hl * p.group + hq;
                     const int64_t slot = int64_t(blockIdx.x) * 2 + (sg.t0 > 0 ? 0 : 1);
-                    float2* dst = reinterpret_cast<float2*>(p.ws_o + (slot * rows + hq) * kHeadDim);
+                    float2* dst = reinterpret_cast<float2*>(p.ws_o + (slot * rows + r) * kHeadDim);
 #pragma unroll
                     for (int c = 0; c < 8; ++c) dst[c * 8 + gid] = make_float2(o[c][y], o[c][y + 2]);
                     if (gid == 0) {
-                        p.ws_ml[(slot * rows + hq) * 2 + 0] = m_run[y];
-                        p.ws_ml[(slot * rows + hq) * 2 + 1] = l_run[y];
+                        p.ws_ml[(slot * rows + r) * 2 + 0] = m_run[y];
+                        p.ws_ml[(slot * rows + r) * 2 + 1] = l_run[y];
                     }
                 }
             }
@@ -810,8 +822,10 @@ static DecodeConfig decode_config(const infer_kv_pool* pool, int n_q_heads) {
     const int forced = env_int("INFER_B200_DECODE_IMPL", 0);   // development switch: 1 = plain-load kernel
     if (forced == 1 || forced == 2) c.impl = forced;
     if (c.impl == 2 && pool->dtype == INFER_KV_E4M3) {
-        c.hpc = 1;
-        c.tile_tokens = kFp8TileTokens;
+        // two adjacent heads per tile when the head count allows: their boxes fetch neighbouring lines
+        c.hpc = pool->n_kv_heads % 2 == 0 ? 2 : 1;
+        if (env_int("INFER_B200_FP8_HPC", 0) == 1) c.hpc = 1;       // development switch
+        c.tile_tokens = kFp8TileTokens / c.hpc;
         c.grid = pool->sm_count;
     } else if (c.impl == 2) {
         // One kv head per tile (128 tokens x 256 B rows) measured fastest at every head count:
@@ -903,10 +917,17 @@ int infer_paged_decode(const infer_kv_pool_t* pool, void* out, const void* q, co
     p.ws_o = reinterpret_cast<float*>(ws + lay.o_off);
 
     if (cfg.impl == 2 && pool->dtype == INFER_KV_E4M3) {
-        const int smem_t = Fp8Smem<8>::total + 1024;
-        IB_CUDA(cudaFuncSetAttribute(decode_tma_fp8_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_t));
-        IB_CUDA(launch_pdl(decode_tma_fp8_kernel<8>, dim3(cfg.grid), dim3(Fp8Smem<8>::threads), smem_t, st, p,
-                           pool->maps[4].k, pool->maps[4].v));
+        if (cfg.hpc == 2) {
+            const int smem_t = Fp8Smem<2>::total + 1024;
+            IB_CUDA(cudaFuncSetAttribute(decode_tma_fp8_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_t));
+            IB_CUDA(launch_pdl(decode_tma_fp8_kernel<2>, dim3(cfg.grid), dim3(kTmaThreads), smem_t, st, p, pool->maps[3].k,
+                               pool->maps[3].v));
+        } else {
+            const int smem_t = Fp8Smem<1>::total + 1024;
+            IB_CUDA(cudaFuncSetAttribute(decode_tma_fp8_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_t));
+            IB_CUDA(launch_pdl(decode_tma_fp8_kernel<1>, dim3(cfg.grid), dim3(kTmaThreads), smem_t, st, p, pool->maps[4].k,
+                               pool->maps[4].v));
+        }
     } else if (cfg.impl == 2) {
         int rc = INFER_OK;
         switch (cfg.hpc) {
