@@ -452,11 +452,11 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_kernel(DecodeParams
 // online-softmax correction, so no per-element dequantisation multiply is needed.
 constexpr int kFp8TileTokens = 256;
 
-// HPC kv heads per tile (1 or 2): a tile is 256 / HPC tokens of HPC adjacent heads, loaded head by head
-// (one TMA box of 128-byte rows each) into [head][token][128 B].  With two heads the two boxes fetch the
-// adjacent 128-byte halves of the same 256 bytes of every token row back to back, which is what the bf16
-// kernel's two column halves do; with one head every row is a lone 128-byte line at a pitch of Hkv * 128 B
-// (measured: 8 heads per token 112 us, the same bytes as a single-head pool 98 us).  Eight consumer warps,
+// HPC kv heads per tile (1, 2, 4 or 8): a tile is 256 / HPC tokens of HPC adjacent heads, loaded head by
+// head (one TMA box of 128-byte rows each) into [head][token][128 B].  With several heads the boxes fetch
+// adjacent 128-byte pieces of every token row back to back, which is what the bf16 kernel's two column
+// halves do; with one head every row is a lone 128-byte line at a pitch of Hkv * 128 B (measured: 8
+// heads per token 112 us, the same bytes as a single-head pool 98 us).  Eight consumer warps,
 // 32 tokens per warp and tile; sixteen warps of 16 tokens were measured slower.
 template <int HPC>
 struct Fp8Smem {
@@ -473,7 +473,7 @@ template <int HPC>
 __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_fp8_kernel(DecodeParams p,
                                                                           const __grid_constant__ CUtensorMap map_k,
                                                                           const __grid_constant__ CUtensorMap map_v) {
-    static_assert(HPC == 1 || HPC == 2, "one or two kv heads per tile");
+    static_assert(HPC == 1 || HPC == 2 || HPC == 4 || HPC == 8, "1, 2, 4 or 8 kv heads per tile");
     constexpr int W = kConsumerWarps;
     constexpr int TT = kFp8TileTokens / HPC;     // tokens per tile
     constexpr int WPH = W / HPC;                 // consumer warps per head
@@ -822,9 +822,11 @@ static DecodeConfig decode_config(const infer_kv_pool* pool, int n_q_heads) {
     const int forced = env_int("INFER_B200_DECODE_IMPL", 0);   // development switch: 1 = plain-load kernel
     if (forced == 1 || forced == 2) c.impl = forced;
     if (c.impl == 2 && pool->dtype == INFER_KV_E4M3) {
-        // two adjacent heads per tile when the head count allows: their boxes fetch neighbouring lines
-        c.hpc = pool->n_kv_heads % 2 == 0 ? 2 : 1;
-        if (env_int("INFER_B200_FP8_HPC", 0) == 1) c.hpc = 1;       // development switch
+        // several adjacent heads per tile when the head count allows: their boxes fetch neighbouring lines
+        // (measured on 8 heads: 1 head 111 us, 2 heads 98.7, 4 heads 96.5, 8 heads 105)
+        c.hpc = pool->n_kv_heads % 4 == 0 ? 4 : (pool->n_kv_heads % 2 == 0 ? 2 : 1);
+        const int want8 = env_int("INFER_B200_FP8_HPC", 0);         // development switch
+        if ((want8 == 1 || want8 == 2 || want8 == 4 || want8 == 8) && pool->n_kv_heads % want8 == 0) c.hpc = want8;
         c.tile_tokens = kFp8TileTokens / c.hpc;
         c.grid = pool->sm_count;
     } else if (c.impl == 2) {
@@ -917,7 +919,20 @@ int infer_paged_decode(const infer_kv_pool_t* pool, void* out, const void* q, co
     p.ws_o = reinterpret_cast<float*>(ws + lay.o_off);
 
     if (cfg.impl == 2 && pool->dtype == INFER_KV_E4M3) {
-        if (cfg.hpc == 2) {
+        if (cfg.hpc == 8 || cfg.hpc == 4) {
+            const int mi = cfg.hpc == 8 ? 1 : 2;
+            if (cfg.hpc == 8) {
+                const int smem_t = Fp8Smem<8>::total + 1024;
+                IB_CUDA(cudaFuncSetAttribute(decode_tma_fp8_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_t));
+                IB_CUDA(launch_pdl(decode_tma_fp8_kernel<8>, dim3(cfg.grid), dim3(kTmaThreads), smem_t, st, p, pool->maps[mi].k,
+                                   pool->maps[mi].v));
+            } else {
+                const int smem_t = Fp8Smem<4>::total + 1024;
+                IB_CUDA(cudaFuncSetAttribute(decode_tma_fp8_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_t));
+                IB_CUDA(launch_pdl(decode_tma_fp8_kernel<4>, dim3(cfg.grid), dim3(kTmaThreads), smem_t, st, p, pool->maps[mi].k,
+                                   pool->maps[mi].v));
+            }
+        } else if (cfg.hpc == 2) {
             const int smem_t = Fp8Smem<2>::total + 1024;
             IB_CUDA(cudaFuncSetAttribute(decode_tma_fp8_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_t));
             IB_CUDA(launch_pdl(decode_tma_fp8_kernel<2>, dim3(cfg.grid), dim3(kTmaThreads), smem_t, st, p, pool->maps[3].k,
