@@ -38,71 +38,61 @@ struct FusedArgs {
     float eps;
 };
 
-__device__ __forceinline__ float bf(__nv_bfloat16 x) { return __bfloat162float(x); }
-__device__ __forceinline__ __nv_bfloat16 rb(float x) { return __float2bfloat16_rn(x); }
-
-__device__ __forceinline__ void unpack8(const uint4& r, float (&x)[8]) {
-    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&r);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        x[2 * i] = __low2float(p[i]);
-        x[2 * i + 1] = __high2float(p[i]);
-    }
-}
-__device__ __forceinline__ uint4 pack8(const __nv_bfloat16 (&x)[8]) {
-    uint4 r;
-    __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&r);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        p[i].x = x[2 * i];
-        p[i].y = x[2 * i + 1];
-    }
-    return r;
-}
-
-// normalise + rotate the sixteen values of this lane (sub = lane within the head's group of 8)
+// normalise + rotate the sixteen values of this lane (sub = lane within the head's group of 8).
+// Packed bf16 arithmetic: a bf16 product or sum is the fp32 result rounded once, which is exactly
+// the reference's "compute in the tensor's dtype" step.
 __device__ __forceinline__ void norm_rope(const __nv_bfloat16* row, const __nv_bfloat16* weight, const __nv_bfloat16* cs,
                                           float eps, int sub, uint4& lo_out, uint4& hi_out) {
-    float x[8], y[8], wl[8], wh[8], c[8], sn[8];
-    unpack8(*reinterpret_cast<const uint4*>(row + 8 * sub), x);
-    unpack8(*reinterpret_cast<const uint4*>(row + 64 + 8 * sub), y);
+    const uint4 xr = *reinterpret_cast<const uint4*>(row + 8 * sub);
+    const uint4 yr = *reinterpret_cast<const uint4*>(row + 64 + 8 * sub);
+    const uint4 wlr = *reinterpret_cast<const uint4*>(weight + 8 * sub);
+    const uint4 whr = *reinterpret_cast<const uint4*>(weight + 64 + 8 * sub);
+    const uint4 cr = *reinterpret_cast<const uint4*>(cs + 8 * sub);
+    const uint4 sr = *reinterpret_cast<const uint4*>(cs + 64 + 8 * sub);
+    const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&xr);
+    const __nv_bfloat162* y2 = reinterpret_cast<const __nv_bfloat162*>(&yr);
+    const __nv_bfloat162* wl2 = reinterpret_cast<const __nv_bfloat162*>(&wlr);
+    const __nv_bfloat162* wh2 = reinterpret_cast<const __nv_bfloat162*>(&whr);
+    const __nv_bfloat162* c2 = reinterpret_cast<const __nv_bfloat162*>(&cr);
+    const __nv_bfloat162* s2 = reinterpret_cast<const __nv_bfloat162*>(&sr);
+    float2 xf[4], yf[4];
     float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) ss += x[i] * x[i] + y[i] * y[i];
+    for (int i = 0; i < 4; ++i) {
+        xf[i] = __bfloat1622float2(x2[i]);
+        yf[i] = __bfloat1622float2(y2[i]);
+        ss += xf[i].x * xf[i].x + xf[i].y * xf[i].y + yf[i].x * yf[i].x + yf[i].y * yf[i].y;
+    }
     // only the eight lanes of this head's group take part: other groups of the warp may be V heads
     const uint32_t group_mask = 0xffu << ((threadIdx.x & 31) & ~7);
 #pragma unroll
     for (int o = 4; o > 0; o >>= 1) ss += __shfl_xor_sync(group_mask, ss, o);
     const float inv = rsqrtf(ss * (1.0f / kHeadDim) + eps);
-    unpack8(*reinterpret_cast<const uint4*>(weight + 8 * sub), wl);
-    unpack8(*reinterpret_cast<const uint4*>(weight + 64 + 8 * sub), wh);
-    unpack8(*reinterpret_cast<const uint4*>(cs + 8 * sub), c);
-    unpack8(*reinterpret_cast<const uint4*>(cs + 64 + 8 * sub), sn);
-    __nv_bfloat16 ox[8], oy[8];
+    __nv_bfloat162* ox = reinterpret_cast<__nv_bfloat162*>(&lo_out);
+    __nv_bfloat162* oy = reinterpret_cast<__nv_bfloat162*>(&hi_out);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < 4; ++i) {
         // bf16(bf16(x * inv) * w)
-        const float a = bf(rb(bf(rb(x[i] * inv)) * wl[i]));
-        const float b = bf(rb(bf(rb(y[i] * inv)) * wh[i]));
+        const __nv_bfloat162 a = __hmul2_rn(__floats2bfloat162_rn(xf[i].x * inv, xf[i].y * inv), wl2[i]);
+        const __nv_bfloat162 b = __hmul2_rn(__floats2bfloat162_rn(yf[i].x * inv, yf[i].y * inv), wh2[i]);
         // out_x = bf16(bf16(x c) - bf16(y s)),  out_y = bf16(bf16(y c) + bf16(x s))
-        ox[i] = rb(bf(rb(a * c[i])) - bf(rb(b * sn[i])));
-        oy[i] = rb(bf(rb(b * c[i])) + bf(rb(a * sn[i])));
+        // (the _rn forms are never contracted into a fused multiply-add, which would skip a rounding)
+        ox[i] = __hsub2_rn(__hmul2_rn(a, c2[i]), __hmul2_rn(b, s2[i]));
+        oy[i] = __hadd2_rn(__hmul2_rn(b, c2[i]), __hmul2_rn(a, s2[i]));
     }
-    lo_out = pack8(ox);
-    hi_out = pack8(oy);
 }
 
 __global__ void __launch_bounds__(256) fused_norm_rope_append_kernel(FusedArgs a) {
     pdl_launch_dependents();
     const int heads = a.n_q_heads + 2 * a.n_kv_heads;
-    const int64_t total = a.n_tokens * heads;
-    const int64_t item = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 3;
+    const uint32_t total = uint32_t(a.n_tokens) * uint32_t(heads);       // the host keeps this below 2^31
+    const uint32_t item = (blockIdx.x * blockDim.x + threadIdx.x) >> 3;
     const int sub = threadIdx.x & 7;
     // a group past the end still takes part in the shuffles of its warp
     const bool live = item < total;
-    const int64_t it = live ? item : total - 1;
-    const int64_t tok = it / heads;
-    const int h = int(it - tok * heads);
+    const uint32_t it = live ? item : total - 1;
+    const int64_t tok = it / uint32_t(heads);
+    const int h = int(it - uint32_t(tok) * uint32_t(heads));
     const int64_t slot = a.slot_mapping[tok];
     const bool slot_ok = slot >= 0 && slot < a.num_slots;      // false: padding row of a captured batch
     if (h < a.n_q_heads + a.n_kv_heads) {
@@ -172,7 +162,7 @@ extern "C" int infer_qk_norm_rope_append(const infer_kv_pool_t* pool, void* q_ou
     a.eps = eps;
     const int64_t groups = n_tokens * (n_q_heads + 2 * pool->n_kv_heads);   // eight lanes each
     const int64_t blocks = (groups + 31) / 32;
-    if (blocks >= (int64_t(1) << 31)) return INFER_ERR_GEOMETRY;
+    if (groups >= (int64_t(1) << 28)) return INFER_ERR_GEOMETRY;          // 32-bit item arithmetic in the kernel
     fused_norm_rope_append_kernel<<<unsigned(blocks), 256, 0, static_cast<cudaStream_t>(stream_)>>>(a);
     return check_launch();
 }
