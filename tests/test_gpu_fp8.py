@@ -118,14 +118,16 @@ def test_fp8_decode_step(impl, monkeypatch):
     assert_close(got, want, ATOL_FP8, RTOL_FP8, "fp8 decode vs fp8 oracle")
 
 
+@pytest.mark.parametrize("hkv", [2, 1, 3, 4], ids=["2-heads-per-tile", "1-head", "3-heads-odd", "4-heads-per-tile"])
 @pytest.mark.parametrize("impl", ["0", "1"], ids=["tma", "plain-loads"])
-def test_fp8_decode_group8_long_contexts(impl, monkeypatch):
+def test_fp8_decode_group8_long_contexts(impl, hkv, monkeypatch):
     """8 query heads per KV head, contexts over several pages with different scales per page,
-    lengths around the 16/32/256-token boundaries of the FP8 tile."""
+    lengths around the 16/32/64/128/256-token boundaries of the FP8 tiles; the KV head count
+    decides how many heads share a tile (4, 2, or 1 when it is odd)."""
     monkeypatch.setenv("INFER_B200_DECODE_IMPL", impl)
     gen = torch.Generator().manual_seed(91)
-    hq, hkv, nb = 16, 2, 40
-    lens = [1, 17, 255, 256, 257, 600, 1300, 33]
+    hq, nb = 8 * hkv, 40
+    lens = [1, 17, 255, 256, 257, 600, 1300, 33, 64, 65, 129]
     cpu = _empty_pools(nb, hkv, "cpu")
     gpu = _empty_pools(nb, hkv, "cuda")
     perm = torch.randperm(nb, generator=gen).tolist()
