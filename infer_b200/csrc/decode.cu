@@ -815,7 +815,9 @@ static int env_int(const char* name, int dflt) {
     return s && *s ? std::atoi(s) : dflt;
 }
 
-static DecodeConfig decode_config(const infer_kv_pool* pool, int n_q_heads) {
+// ws_limit: bytes of scratch the caller has (0 = no limit); the e4m3 kernel takes fewer heads per tile
+// when the partial-result slots of more would not fit.
+static DecodeConfig decode_config(const infer_kv_pool* pool, int n_q_heads, size_t ws_limit = 0) {
     DecodeConfig c;
     const int group = n_q_heads / pool->n_kv_heads;
     c.impl = 2;
@@ -827,6 +829,7 @@ static DecodeConfig decode_config(const infer_kv_pool* pool, int n_q_heads) {
         c.hpc = pool->n_kv_heads % 4 == 0 ? 4 : (pool->n_kv_heads % 2 == 0 ? 2 : 1);
         const int want8 = env_int("INFER_B200_FP8_HPC", 0);         // development switch
         if ((want8 == 1 || want8 == 2 || want8 == 4 || want8 == 8) && pool->n_kv_heads % want8 == 0) c.hpc = want8;
+        while (ws_limit && c.hpc > 1 && decode_layout(pool->sm_count, c.hpc * group).total > ws_limit) c.hpc /= 2;
         c.tile_tokens = kFp8TileTokens / c.hpc;
         c.grid = pool->sm_count;
     } else if (c.impl == 2) {
@@ -888,7 +891,7 @@ int infer_paged_decode(const infer_kv_pool_t* pool, void* out, const void* q, co
     if (group > kMaxGroup || (group & (group - 1)) != 0) return INFER_ERR_GEOMETRY;
     if (!aligned16(out) || !aligned16(q)) return INFER_ERR_ALIGN;
     if (batch == 0) return INFER_OK;
-    const DecodeConfig cfg = decode_config(pool, n_q_heads);
+    const DecodeConfig cfg = decode_config(pool, n_q_heads, workspace_bytes);
     const DecodeLayout lay = decode_layout(cfg.grid, cfg.rows);
     if (!workspace || !aligned16(workspace) || workspace_bytes < lay.total) return INFER_ERR_WORKSPACE;
     cudaStream_t st = static_cast<cudaStream_t>(stream_);
@@ -1000,7 +1003,7 @@ int infer_paged_decode_noalloc(const infer_kv_pool_t* pool, void* out, const voi
     if (!pool || !out || !q || !context_lens || !block_tables) return INFER_ERR_NULL;
     if (n_q_heads <= 0 || n_q_heads % pool->n_kv_heads != 0 || batch < 0) return INFER_ERR_GEOMETRY;
     if (batch > kMaxBatch) return INFER_ERR_TOO_LARGE;
-    const DecodeConfig cfg = decode_config(pool, n_q_heads);
+    const DecodeConfig cfg = decode_config(pool, n_q_heads, kBuiltinScratchBytes);
     if (decode_layout(cfg.grid, cfg.rows).total > kBuiltinScratchBytes) return INFER_ERR_TOO_LARGE;
 
     int dev = -1;

@@ -48,6 +48,32 @@ def test_noalloc_matches_regular_entry_point_twice_in_a_row():
     assert_close(got, want, ATOL_BF16, RTOL_BF16, "no-alloc decode, second call on the used scratch")
 
 
+def test_noalloc_e4m3_pool_fits_by_taking_fewer_heads_per_tile():
+    """An e4m3 pool with 8 KV heads and 4 query heads each: the partial-result slots of four heads
+    per tile (the default) need more than the built-in 2 MiB, so the entry point has to fall back
+    to fewer heads per tile instead of refusing the call."""
+    dev = torch.device("cuda", 0)
+    lib = _lib.load()
+    w = workloads.config1(batch=12, lo=200, hi=3000, device=dev)
+    nb, hkv = w.num_blocks, w.n_kv_heads
+    k8 = torch.zeros(nb, 256, hkv, 128, dtype=torch.uint8, device=dev)
+    v8 = torch.zeros_like(k8)
+    ks, vs = torch.zeros(nb, hkv, device=dev), torch.zeros(nb, hkv, device=dev)
+    slots = torch.arange(nb * 256, dtype=torch.int32, device=dev)
+    ops.store_kvcache(w.k_cache.view(-1, hkv, 128), w.v_cache.view(-1, hkv, 128), k8, v8, slots, ks, vs)
+    cl, bt = w.context_lens_tensor().to(dev), w.block_tables_tensor().to(dev)
+    want = ops.paged_attn_decode(w.q, k8, v8, cl, bt, w.scale, k_scale=ks, v_scale=vs)
+    pool = ops.pool_of(k8, v8, ks, vs)
+    out = torch.zeros_like(w.q)
+    rc = lib.infer_paged_decode_noalloc(pool.handle, C.c_void_p(out.data_ptr()), C.c_void_p(w.q.data_ptr()),
+                                        C.c_void_p(cl.data_ptr()), C.c_void_p(bt.data_ptr()), bt.stride(0),
+                                        w.batch, w.n_q_heads, w.scale, C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0, lib.infer_strerror(rc).decode()
+    torch.cuda.synchronize()
+    # same kernel with a different tile width: the same bytes in a different summation order
+    assert_close(out, want, 2e-2, 1e-2, "no-alloc e4m3 decode vs regular entry point")
+
+
 def test_noalloc_rejects_what_does_not_fit():
     dev = torch.device("cuda", 0)
     lib = _lib.load()
