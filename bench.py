@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-Workload at N GPUs: the Qwen3-8B decode shape (32 query / 8 KV heads, head_dim 128,
+Headline workload at N GPUs: the Qwen3-8B decode shape (32 query / 8 KV heads, head_dim 128,
 page 256 tokens, context lengths uniform in [512, 8192], one appended token per sequence),
 batch 64*N, KV heads sharded N ways (rank r owns 8/N KV heads and their query heads of
 every sequence; page ids, slots and lengths are replicated).  Per-GPU KV bytes are the same
@@ -10,13 +10,24 @@ at every N (weak scaling); at N=1 it is exactly the 64-sequence configuration.  
 one append (one new row per sequence) followed by one paged decode attention pass.
 
 One JSON line is printed by rank 0:
-  value      whole-job KV GB/s: algorithmic KV bytes of all ranks / step time (max over ranks),
-             inputs resident in HBM, timed with CUDA events; the K steps replayed as one CUDA graph
-             (value_launched_one_by_one is the same K steps launched kernel by kernel);
+  value      whole-job KV GB/s: algorithmic KV bytes of all ranks / step time.  The K steps are
+             captured as ONE CUDA graph, which is replayed R >= 50 times inside the clock-sampling
+             window with an event pair around every replay; the step time is the median over
+             replays (max over ranks), minimum and maximum are reported next to it.
+             value_launched_one_by_one is the same K steps launched kernel by kernel;
   e2e        same metric with the step's host inputs copied from pinned memory and the
              attention output copied back inside the timed region;
-  roofline   the decode kernels (partition + reduce) against the measured HBM copy peak;
+  roofline   the decode kernel against the measured HBM copy peak (per-step CUDA events);
   append     bulk-append throughput (32768 rows, the chunked-prefill append) in tok/s;
+  prefill    (N = 1) the paged chunked-prefill configuration: TFLOP/s against the measured bf16 peak;
+  fp8_kv     the same pool as e4m3 bytes: decode GB/s on e4m3 bytes, decode-shape and bulk append;
+  fused_append   q/k RMSNorm + rotary embedding + append in one pass, 32768 tokens;
+  strong     strong scaling: the long-context configuration (batch 256, 64q/8kv heads) and the
+             Qwen3-8B decode shape at batch 64, the 8 KV heads sharded N ways, with the single-GPU
+             step they scale from measured in the same process;
+  validated  (N > 1) attention outputs all-gathered over NCCL and checked against the CPU oracle;
+  reference_gpu  (N = 1) the library call the reference makes for decode (flash_attn's
+             flash_attn_with_kvcache), timed on the same tensors;
   cpu_baseline  the torch-CPU restatement of the reference path, timed on a sample.
 
 ``--impl reference`` times that CPU restatement alone (the reference has no CPU or
@@ -26,6 +37,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -48,6 +60,7 @@ BASE_BATCH = 64
 DECODE_TRAFFIC_PER_KV_BYTE = 259.5 / 249.9
 PREFILL_TRAFFIC_PER_SEQUENCE = 119.0e6 / 4
 FALLBACK_HBM_GBS = 6650.0
+FALLBACK_TFLOPS = 1400.0
 
 
 def measured_peak():
@@ -56,6 +69,14 @@ def measured_peak():
             return float(json.load(f)["hbm_gbs"]), "measured"
     except Exception:
         return FALLBACK_HBM_GBS, "fallback"
+
+
+def measured_tflops():
+    try:
+        with open(ROOT / "MEASURED_PEAKS.json") as f:
+            return float(json.load(f)["bf16_tflops_sustained"]), "of measured (sustained)"
+    except Exception:
+        return FALLBACK_TFLOPS, "of fallback"
 
 
 class ClockSampler:
@@ -70,7 +91,7 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
@@ -111,13 +132,14 @@ class ClockSampler:
 
 
 def build_workload(world: int, rank: int, device, base_batch: int = BASE_BATCH, kind: str = "decode"):
+    """decode: the headline weak-scaling workload (batch 64 * world); long / decode64: the two
+    strong-scaling workloads (fixed batch, the 8 KV heads sharded world ways, page ids replicated)."""
     from infer_b200 import workloads
     if kind == "long":
-        # the long-context scale-out configuration: batch 256 on every GPU count, the 8 KV heads
-        # (and their 8 query heads each) sharded world ways, page ids replicated
         return workloads.config4(device=device, seed=1004, n_kv_heads=8 // world, n_q_heads=64 // world,
                                  tensor_seed=1004 + rank)
-    return workloads.config1(device=device, seed=1001, batch=base_batch * world, n_kv_heads=8 // world,
+    batch = base_batch if kind == "decode64" else base_batch * world
+    return workloads.config1(device=device, seed=1001, batch=batch, n_kv_heads=8 // world,
                              n_q_heads=32 // world, tensor_seed=1001 + rank)
 
 
@@ -175,14 +197,147 @@ def run_reference(args, rank, world):
     }))
 
 
-# ------------------------------------------------------------------------------- prefill leg
-def run_prefill(args):
+# ------------------------------------------------------------------------------- timing helpers
+def _timed(fn, reps, warm, stream):
+    """Mean milliseconds of ``fn`` over ``reps`` back-to-back calls (CUDA events on the launching stream)."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a0.record(stream)
+    for _ in range(reps):
+        fn()
+    a1.record(stream)
+    torch.cuda.synchronize()
+    return a0.elapsed_time(a1) / reps
+
+
+def time_decode_steps(ops, w, cl, bt, slots, out, steps, warmup, barrier, window_s=0.5, min_replays=50, graph=True):
+    """Times ``steps`` steps (append + decode) of one workload three ways:
+      * captured once as ONE CUDA graph of ``steps`` steps and replayed R >= min_replays times (at least
+        ``window_s`` seconds), an event pair around every replay: median / min / max ms per step;
+      * launched kernel by kernel, one event pair around the whole run: ms per step;
+      * launched kernel by kernel with events around every decode call: the decode kernel's own time."""
+    stream = torch.cuda.current_stream()
+
+    def step():
+        ops.store_kvcache(w.k, w.v, w.k_cache, w.v_cache, slots)
+        ops.paged_attn_decode(w.q, w.k_cache, w.v_cache, cl, bt, w.scale, out=out)
+
+    for _ in range(warmup):
+        step()
+    barrier()
+    res = {"graph": None}
+    g = None
+    if graph:
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for _ in range(steps):
+                    step()
+            g.replay()                                        # untimed: the first replay uploads the graph
+            torch.cuda.synchronize()
+        except Exception as exc:                              # pragma: no cover - reported as absent
+            print(f"[bench] CUDA-graph capture of the device-resident steps failed ({exc})", file=sys.stderr)
+            g = None
+    t_begin = time.time()
+    if g is not None:
+        # how many replays fill the window: one timed probe
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        p0.record(stream)
+        g.replay()
+        p1.record(stream)
+        torch.cuda.synchronize()
+        replays = max(min_replays, int(math.ceil(window_s * 1e3 / max(p0.elapsed_time(p1), 1e-3))))
+        replays = min(replays, 2000)
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(replays)]
+        barrier()
+        for e0, e1 in evs:
+            e0.record(stream)
+            g.replay()
+            e1.record(stream)
+        barrier()
+        per_step = sorted(e0.elapsed_time(e1) / steps for e0, e1 in evs)
+        res["graph"] = {"median": statistics.median(per_step), "min": per_step[0], "max": per_step[-1],
+                        "replays": replays, "timed_s": sum(per_step) * steps / 1e3}
+    # launched one by one, no events in between (events between kernels would break their overlap)
+    reps = max(1, int(math.ceil(0.1 / max(1e-6, steps * 2e-4)))) if window_s > 0 else 1      # about 0.1 s of steps
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    s0.record(stream)
+    for _ in range(reps * steps):
+        step()
+    s1.record(stream)
+    barrier()
+    res["eager_ms"] = s0.elapsed_time(s1) / (reps * steps)
+    # per-call events: the decode kernel and the decode-shape append on their own
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
+    for i in range(steps):
+        ev[i][0].record(stream)
+        ops.store_kvcache(w.k, w.v, w.k_cache, w.v_cache, slots)
+        ev[i][1].record(stream)
+        ops.paged_attn_decode(w.q, w.k_cache, w.v_cache, cl, bt, w.scale, out=out)
+        ev[i][2].record(stream)
+    barrier()
+    decode_all = [e[1].elapsed_time(e[2]) for e in ev]
+    res["decode_ms"] = statistics.mean(decode_all)
+    res["decode_ms_median"] = statistics.median(decode_all)
+    res["decode_ms_min"] = min(decode_all)
+    res["append_ms"] = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+    res["region_s"] = time.time() - t_begin
+    return res
+
+
+def reduce_max(values, device, world):
+    import torch.distributed as dist
+    t = torch.tensor(values, device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.tolist()
+
+
+def reduce_sum(value, device, world):
+    import torch.distributed as dist
+    t = torch.tensor([float(value)], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return t.item()
+
+
+# ------------------------------------------------------------------------------- validation over NCCL
+def validate_gathered(w, out, world, rank, n_check=3):
+    """north-star use of NCCL: all-gather the attention outputs (and, for the checked sequences, the
+    pages and queries of every shard) and compare with the CPU oracle of the unsharded problem on rank 0."""
+    import numpy as np
+    import torch.distributed as dist
+    from infer_b200.sharding import gather_heads
+    from oracle import paged_kv_oracle as oracle
+    full_out = gather_heads(out)
+    full_q = gather_heads(w.q)
+    order = np.argsort(w.context_lens)
+    picks = sorted({int(order[0]), int(order[len(order) // 2]), int(order[-1])})[:n_check]
+    max_err, ok = 0.0, True
+    for b in picks:
+        pages = torch.tensor(w.block_tables[b], device=out.device)
+        kc = gather_heads(w.k_cache[pages].reshape(-1, w.n_kv_heads, 128)).reshape(len(pages), 256, -1, 128)
+        vc = gather_heads(w.v_cache[pages].reshape(-1, w.n_kv_heads, 128)).reshape(len(pages), 256, -1, 128)
+        if rank == 0:
+            local = torch.arange(len(pages), dtype=torch.int32)[None]
+            want = oracle.paged_decode(full_q[b:b + 1].cpu(), kc.cpu(), vc.cpu(),
+                                       torch.tensor([w.context_lens[b]], dtype=torch.int32), local, w.scale).float()
+            err = (full_out[b:b + 1].float().cpu() - want).abs()
+            max_err = max(max_err, float(err.max()))
+            ok = ok and bool((err <= 2e-2 + 1e-2 * want.abs()).all())
+    dist.barrier()
+    return {"nranks": world, "sequences": len(picks), "max_err": max_err, "ok": ok,
+            "tolerance": "2e-2 abs + 1e-2 rel against the CPU oracle", "gather": "nccl all_gather"}
+
+
+# ------------------------------------------------------------------------------- sub-benchmarks
+def bench_prefill(ops, device, n_seqs, steps, warmup, dense=True, sample_clocks=True):
     """Chunked prefill over cached prefixes: append the chunk, then causal attention over
     prefix + chunk.  FLOPs = 4 * 128 * Hq * sum(chunk * prefix + chunk * (chunk + 1) / 2)."""
-    from infer_b200 import ops, workloads
-    device = torch.device("cuda", 0)
-    torch.cuda.set_device(device)
-    n_seqs = 16 if args.batch == BASE_BATCH else args.batch
+    from infer_b200 import workloads
     w = workloads.config2(device=device, n_seqs=n_seqs)
     cu_q, cu_k = (t.to(device) for t in w.cu_seqlens())
     bt = w.block_tables_tensor().to(device)
@@ -196,70 +351,184 @@ def run_prefill(args):
         ops.store_kvcache(w.k, w.v, w.k_cache, w.v_cache, slots)
         ops.paged_attn_prefill(w.q, w.k_cache, w.v_cache, cu_q, cu_k, mq, mk, w.scale, bt, out=out)
 
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         step()
     torch.cuda.synchronize()
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
-    with ClockSampler(0) as clocks:
-        for i in range(args.steps):
-            ev[i][0].record(stream)
-            ops.store_kvcache(w.k, w.v, w.k_cache, w.v_cache, slots)
-            ev[i][1].record(stream)
-            ops.paged_attn_prefill(w.q, w.k_cache, w.v_cache, cu_q, cu_k, mq, mk, w.scale, bt, out=out)
-            ev[i][2].record(stream)
-        torch.cuda.synchronize()
-        t_end = time.time() + (0.0 if args.profile else 0.5)
-        while time.time() < t_end:
-            step()
-        torch.cuda.synchronize()
-    attn_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
-    append_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
-    step_ms = statistics.mean(e[0].elapsed_time(e[2]) for e in ev)
-    try:
-        with open(ROOT / "MEASURED_PEAKS.json") as f:
-            peak, kind = float(json.load(f)["bf16_tflops_sustained"]), "of measured (sustained)"
-    except Exception:
-        peak, kind = 1400.0, "of fallback"
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
+    with ClockSampler(device.index) as clocks:
+        t_end = time.time() + (0.5 if sample_clocks else 0.0)
+        rounds = 0
+        while True:
+            for i in range(steps):
+                ev[i][0].record(stream)
+                ops.store_kvcache(w.k, w.v, w.k_cache, w.v_cache, slots)
+                ev[i][1].record(stream)
+                ops.paged_attn_prefill(w.q, w.k_cache, w.v_cache, cu_q, cu_k, mq, mk, w.scale, bt, out=out)
+                ev[i][2].record(stream)
+            torch.cuda.synchronize()
+            rounds += 1
+            if time.time() >= t_end:
+                break
+    attn_all = [e[1].elapsed_time(e[2]) for e in ev]           # the last round's steps
+    attn_ms = statistics.median(attn_all)
+    append_ms = statistics.median(e[0].elapsed_time(e[1]) for e in ev)
+    step_ms = statistics.median(e[0].elapsed_time(e[2]) for e in ev)
+    peak, kind = measured_tflops()
     achieved = flops / (attn_ms * 1e-3) / 1e12
     n_tok = sum(w.new_lens)
-    dense = None
-    if args.dense:
+    res = {
+        "workload": f"paged chunked prefill: {n_seqs} sequences, prefix U[0,4096], chunk 2048, 16q/8kv heads, page 256; "
+                    "append of the chunk + causal attention over prefix + chunk",
+        "flops_per_step": flops, "tflops_step": flops / (step_ms * 1e-3) / 1e12, "ms_per_step": step_ms,
+        "attn_ms": attn_ms, "attn_ms_min": min(attn_all), "attn_ms_max": max(attn_all),
+        "tflops": achieved, "peak": peak, "frac": achieved / peak, "peak_kind": kind, "bound": "tensor",
+        "timed_steps": steps * rounds,
+        "traffic": PREFILL_TRAFFIC_PER_SEQUENCE * n_seqs,
+        "append": {"rows": n_tok, "ms": append_ms, "tok_s": n_tok / (append_ms * 1e-3),
+                   "gbs": n_tok * w.n_kv_heads * 128 * 2 * 4 / (append_ms * 1e-3) / 1e9},
+        "clocks": clocks.summary(),
+    }
+    del w
+    if dense:
         gen = torch.Generator(device=device).manual_seed(7)
         B, H, Hkv, S = 4, 16, 8, 4096
         dq = torch.randn(B, H, S, 128, generator=gen, device=device).bfloat16()
         dk = torch.randn(B, Hkv, S, 128, generator=gen, device=device).bfloat16()
         dv = torch.randn(B, Hkv, S, 128, generator=gen, device=device).bfloat16()
         do = torch.empty_like(dq)
-        for _ in range(3):
-            ops.flash_attn_prefill(dq, dk, dv, do)
-        torch.cuda.synchronize()
-        d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        d0.record(stream)
-        for _ in range(10):
-            ops.flash_attn_prefill(dq, dk, dv, do)
-        d1.record(stream)
-        torch.cuda.synchronize()
-        dms = d0.elapsed_time(d1) / 10
+        dms = _timed(lambda: ops.flash_attn_prefill(dq, dk, dv, do), 10, 3, stream)
         dflops = 4 * 128 * B * H * S * (S + 1) // 2
-        dense = {"shape": [B, H, S, 128], "kv_heads": Hkv, "ms": dms, "tflops": dflops / (dms * 1e-3) / 1e12}
-    print(json.dumps({
-        "metric": "paged chunked-prefill attention TFLOP/s", "value": flops / (step_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"paged chunked prefill: {n_seqs} sequences, prefix U[0,4096], chunk 2048, 16q/8kv heads, "
-                               "page 256; append of the chunk + causal attention over prefix + chunk",
-                   "flops_per_step": flops, "l2": "q + KV read per step exceed L2"},
-        "gpu_launches": 2 * args.steps,
-        "roofline": {"bound": "tensor", "kernel": "prefill attention kernel", "achieved": achieved, "peak": peak,
-                     "unit": "TFLOP/s", "frac": achieved / peak, "peak_kind": kind, "attn_ms": attn_ms,
-                     "traffic": PREFILL_TRAFFIC_PER_SEQUENCE * n_seqs,
-                     "traffic_note": "DRAM bytes per launch: ncu capture of a 4-sequence case (103.9 MB read + 15.1 MB "
-                                     "written), scaled by the number of sequences"},
-        "append": {"rows": n_tok, "ms": append_ms, "tok_s": n_tok / (append_ms * 1e-3),
-                   "gbs": n_tok * w.n_kv_heads * 128 * 2 * 4 / (append_ms * 1e-3) / 1e9},
-        "clocks": clocks.summary(),
-        **({"dense_op": dense} if dense else {}),
-    }))
+        res["dense_op"] = {"shape": [B, H, S, 128], "kv_heads": Hkv, "ms": dms, "tflops": dflops / (dms * 1e-3) / 1e12,
+                           "frac": dflops / (dms * 1e-3) / 1e12 / peak}
+    return res
+
+
+def bench_fp8(ops, w, cl, bt, slots, out, decode_ms_bf16, peak, profile):
+    """The same pool as e4m3 bytes with one fp32 scale per (page, kv head)."""
+    device, hkv, nb = w.q.device, w.n_kv_heads, w.num_blocks
+    stream = torch.cuda.current_stream()
+    k8 = torch.zeros(nb, 256, hkv, 128, dtype=torch.uint8, device=device)
+    v8 = torch.zeros_like(k8)
+    ks8 = torch.zeros(nb, hkv, device=device)
+    vs8 = torch.zeros(nb, hkv, device=device)
+    for lo in range(0, nb, 64):                           # quantise the bf16 pool page group by page group
+        hi = min(nb, lo + 64)
+        sl = torch.arange(lo * 256, hi * 256, dtype=torch.int32, device=device)
+        ops.store_kvcache(w.k_cache[lo:hi].reshape(-1, hkv, 128), w.v_cache[lo:hi].reshape(-1, hkv, 128), k8, v8, sl, ks8, vs8)
+    torch.cuda.synchronize()
+    reps, warm = (3, 0) if profile else (20, 3)
+    dec8_ms = _timed(lambda: ops.paged_attn_decode(w.q, k8, v8, cl, bt, w.scale, out=out, k_scale=ks8, v_scale=vs8),
+                     reps, warm, stream)
+    app8_ms = _timed(lambda: ops.store_kvcache(w.k, w.v, k8, v8, slots, ks8, vs8), reps, warm, stream)
+    n_rows = min(32768, nb * 256)
+    sl = torch.arange(0, n_rows, dtype=torch.int32, device=device)
+    rk = w.k_cache.view(-1, hkv, 128)[:n_rows]
+    rv = w.v_cache.view(-1, hkv, 128)[:n_rows]
+    bulk8_ms = _timed(lambda: ops.store_kvcache(rk, rv, k8, v8, sl, ks8, vs8), reps, warm, stream)
+    kv8 = w.kv_bytes(elem_bytes=1) + 2 * 4 * hkv * sum(-(-n // 256) for n in w.context_lens)
+    dec_gbs = kv8 / (dec8_ms * 1e-3) / 1e9
+    bulk_gbs = n_rows * hkv * 128 * 2 * (2 + 1) / (bulk8_ms * 1e-3) / 1e9
+    return {"decode_us": dec8_ms * 1e3, "kv_bytes_e4m3": kv8, "decode_gbs": dec_gbs, "decode_frac": dec_gbs / peak,
+            "tokens_per_us_vs_bf16": decode_ms_bf16 / dec8_ms, "append_decode_shape_us": app8_ms * 1e3,
+            "bulk_rows": n_rows, "bulk_us": bulk8_ms * 1e3, "bulk_tok_s": n_rows / (bulk8_ms * 1e-3),
+            "bulk_gbs": bulk_gbs, "bulk_frac": bulk_gbs / peak,
+            "bulk_bytes_note": "per row and head: 256 B of bf16 read for K and V each, 128 B of e4m3 written each"}
+
+
+def bench_fused_append(ops, w, peak, profile):
+    """q/k RMSNorm + rotary embedding + KV append in one pass over the fused qkv rows (32768 tokens)."""
+    device, hq, hkv, t = w.q.device, w.n_q_heads, w.n_kv_heads, 32768
+    stream = torch.cuda.current_stream()
+    gen = torch.Generator(device=device).manual_seed(9)
+    qkv = torch.randn(t, (hq + 2 * hkv) * 128, generator=gen, device=device).bfloat16()
+    q = qkv[:, :hq * 128].view(t, hq, 128)
+    k = qkv[:, hq * 128:(hq + hkv) * 128].view(t, hkv, 128)
+    v = qkv[:, (hq + hkv) * 128:].view(t, hkv, 128)
+    qw = torch.randn(128, generator=gen, device=device).bfloat16()
+    kw = torch.randn(128, generator=gen, device=device).bfloat16()
+    cache = torch.randn(8192, 128, generator=gen, device=device).bfloat16()
+    pos = torch.randint(0, 8192, (t,), generator=gen, device=device)
+    slots = torch.randperm(w.num_blocks * 256, generator=gen, device=device)[:t].to(torch.int32)
+    qo = torch.empty(t, hq, 128, device=device, dtype=torch.bfloat16)
+    reps, warm = (3, 0) if profile else (20, 3)
+    ms = _timed(lambda: ops.qk_norm_rope_append(q, k, v, qw, kw, 1e-6, pos, cache, w.k_cache, w.v_cache, slots, q_out=qo),
+                reps, warm, stream)
+    nbytes = t * (hq + 2 * hkv) * 256 + t * hq * 256 + t * 2 * hkv * 256
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    return {"tokens": t, "heads": f"{hq}q/{hkv}kv", "us": ms * 1e3, "min_traffic_bytes": nbytes, "gbs": gbs,
+            "frac": gbs / peak, "tok_s": t / (ms * 1e-3)}
+
+
+def bench_flash_attn(w, cl, bt, slots, out, steps):
+    """The library call the reference makes for decode (infer/ops/attention.py:117-121), on the same
+    tensors.  The append stands in for the reference's Triton store kernel (whose source is not
+    shipped with this repository) as torch's index_copy_."""
+    try:
+        import flash_attn
+        from flash_attn import flash_attn_with_kvcache
+    except Exception as exc:
+        return {"unavailable": f"flash_attn does not import ({type(exc).__name__})"}
+    stream = torch.cuda.current_stream()
+    kflat = w.k_cache.view(-1, w.n_kv_heads, 128)
+    vflat = w.v_cache.view(-1, w.n_kv_heads, 128)
+    idx = slots.long()
+    q4 = w.q.unsqueeze(1)
+
+    def step():
+        kflat.index_copy_(0, idx, w.k)
+        vflat.index_copy_(0, idx, w.v)
+        return flash_attn_with_kvcache(q4, w.k_cache, w.v_cache, cache_seqlens=cl, block_table=bt,
+                                       softmax_scale=w.scale, causal=True)
+    try:
+        o = step()
+        torch.cuda.synchronize()
+        err = float((o.squeeze(1).float() - out.float()).abs().max())
+        ms = _timed(step, steps, 3, stream)
+    except Exception as exc:
+        return {"unavailable": f"flash_attn_with_kvcache failed here ({type(exc).__name__}: {str(exc)[:120]})"}
+    kv = w.kv_bytes()
+    return {"kind": f"flash_attn {getattr(flash_attn, '__version__', '?')} flash_attn_with_kvcache + torch index_copy_ append, "
+                    "launched one by one", "ms_per_step": ms, "value": kv / (ms * 1e-3) / 1e9, "unit": UNIT,
+            "max_abs_diff_vs_this_library": err}
+
+
+def bench_strong(ops, kind, world, rank, device, steps, warmup, barrier, peak):
+    """One strong-scaling workload at ``world`` GPUs and, in the same process, the single-GPU problem it
+    scales from (all 8 KV heads on this GPU)."""
+    res = {}
+    for label, wd, rk in (("sharded", world, rank), ("single_gpu", 1, 0)):
+        if label == "single_gpu" and world == 1:
+            res[label] = res["sharded"]
+            break
+        w = build_workload(wd, rk, device, BASE_BATCH, kind)
+        cl, bt, slots = w.context_lens_tensor().to(device), w.block_tables_tensor().to(device), w.slot_mapping.to(device)
+        out = torch.empty_like(w.q)
+        r = time_decode_steps(ops, w, cl, bt, slots, out, steps, warmup, barrier if label == "sharded" else torch.cuda.synchronize,
+                              window_s=0.2, min_replays=20)
+        kv = w.kv_bytes()
+        g = r["graph"]
+        step_ms = g["median"] if g else r["eager_ms"]
+        vals = [step_ms, r["eager_ms"], r["decode_ms"]]
+        if label == "sharded":
+            vals = reduce_max(vals, device, world)
+            job = reduce_sum(kv, device, world)
+        else:
+            job = kv
+        res[label] = {"n_gpus": wd, "batch": len(w.context_lens), "kv_bytes_per_gpu": kv, "job_kv_bytes": job,
+                      "step_us": vals[0] * 1e3, "step_us_launched_one_by_one": vals[1] * 1e3,
+                      "decode_us": vals[2] * 1e3, "aggregate_gbs": job / (vals[0] * 1e-3) / 1e9,
+                      "per_gpu_decode_gbs": kv / (vals[2] * 1e-3) / 1e9, "per_gpu_decode_frac": kv / (vals[2] * 1e-3) / 1e9 / peak}
+        if label == "sharded" and world > 1 and kind == "long":
+            ops.store_kvcache(w.k, w.v, w.k_cache, w.v_cache, slots)
+            ops.paged_attn_decode(w.q, w.k_cache, w.v_cache, cl, bt, w.scale, out=out)
+            res["validated"] = validate_gathered(w, out, world, rank)
+        del w, out
+        torch.cuda.empty_cache()
+    s, one = res["sharded"], res["single_gpu"]
+    res["speedup_vs_single_gpu"] = one["step_us"] / s["step_us"]
+    res["step_efficiency"] = one["step_us"] / (world * s["step_us"])
+    res["step_efficiency_launched_one_by_one"] = one["step_us_launched_one_by_one"] / (world * s["step_us_launched_one_by_one"])
+    return res
 
 
 # ------------------------------------------------------------------------------- GPU leg
@@ -271,18 +540,14 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile", action="store_true",
-                    help="short run for profiler captures: no end-to-end leg, no CPU baseline, no padding of the "
-                         "clock-sampling window, 3 bulk appends")
+                    help="short run for profiler captures: the headline steps launched one by one and 3 bulk appends, "
+                         "no graph, no end-to-end leg, no sub-benchmarks, no CPU baseline")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "long"],
-                    help="decode = the headline append + paged decode step; prefill = the paged chunked-prefill "
-                         "configuration (16 sequences, prefix U[0,4096], chunk 2048), single GPU; long = the "
-                         "long-context scale-out configuration (batch 256, 64q/8kv heads, ctx lognormal capped at "
-                         "32768, half the batch sharing a 2048-token prefix), strong scaling over KV heads")
-    ap.add_argument("--fp8", action="store_true",
-                    help="decode workloads: also time the e4m3 pool (decode, decode-shape append, 32768-row append) "
-                         "and add an fp8_kv object to the line (rank 0's figures)")
-    ap.add_argument("--dense", action="store_true",
-                    help="prefill workload: also time the dense op flash_attn_prefill on [4, 16, 4096, 128]")
+                    help="decode = the full line; prefill = only the paged chunked-prefill configuration (single GPU, "
+                         "used for profiler captures); long = only the long-context configuration as the headline")
+    ap.add_argument("--only", default="", help="comma-separated sub-benchmarks to keep (prefill,fp8,fused,strong,flash); "
+                                               "default: all")
+    ap.add_argument("--fp8", action="store_true", help="with --profile: also run the e4m3 legs")
     ap.add_argument("--batch", type=int, default=BASE_BATCH,
                     help="sequences per GPU share (default 64 = the benchmark configuration; smaller values "
                          "give the small case used for profiler captures)")
@@ -297,11 +562,6 @@ def main():
         return
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
-    if args.workload == "prefill":
-        if world != 1:
-            raise SystemExit("--workload prefill runs on one GPU")
-        run_prefill(args)
-        return
     if 8 % world:
         raise SystemExit("KV-head sharding needs a GPU count that divides 8")
 
@@ -310,10 +570,34 @@ def main():
 
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    if args.workload == "prefill":
+        if world != 1:
+            raise SystemExit("--workload prefill runs on one GPU")
+        n_seqs = 16 if args.batch == BASE_BATCH else args.batch
+        res = bench_prefill(ops, device, n_seqs, args.steps, args.warmup, dense=not args.profile,
+                            sample_clocks=not args.profile)
+        print(json.dumps({"metric": "paged chunked-prefill attention TFLOP/s", "value": res["tflops_step"], "unit": "TFLOP/s",
+                          "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_step"],
+                          "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+                          "data": "synthetic", "config": {"workload": res["workload"]}, "gpu_launches": 2 * res["timed_steps"],
+                          "roofline": {"bound": "tensor", "kernel": "prefill_tc_kernel", "achieved": res["tflops"],
+                                       "peak": res["peak"], "unit": "TFLOP/s", "frac": res["frac"],
+                                       "peak_kind": res["peak_kind"], "traffic": res["traffic"]},
+                          "prefill": res, "clocks": res["clocks"]}))
+        return
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
+    want = set(filter(None, args.only.split(","))) or {"prefill", "fp8", "fused", "strong", "flash"}
+    if args.profile:
+        want = {"fp8"} if args.fp8 else set()
 
-    w = build_workload(world, rank, device, args.batch, args.workload)
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    peak, peak_kind = measured_peak()
+    w = build_workload(world, rank, device, args.batch, "long" if args.workload == "long" else "decode")
     cl = w.context_lens_tensor().to(device)
     bt = w.block_tables_tensor().to(device)
     slots = w.slot_mapping.to(device)
@@ -321,68 +605,11 @@ def main():
     kv_bytes = w.kv_bytes()                      # this rank's algorithmic KV bytes per step
     stream = torch.cuda.current_stream()
 
-    def step():
-        ops.store_kvcache(w.k, w.v, w.k_cache, w.v_cache, slots)
-        ops.paged_attn_decode(w.q, w.k_cache, w.v_cache, cl, bt, w.scale, out=out)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(args.warmup):
-        step()
-    barrier()
-
-    # ---- device-resident timing.  The K steps are timed twice inside the clock-sampling window, each time
-    # bracketed by barrier + synchronize: launched one by one with per-step events around the decode, and
-    # captured once and replayed as ONE CUDA graph of K steps (no launch gaps between kernels).
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    g_start, g_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    g_dev = None
-    if not args.profile and os.environ.get("INFER_B200_BENCH_EAGER") != "1":
-        try:
-            g_dev = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g_dev):
-                for _ in range(args.steps):
-                    step()
-            g_dev.replay()                                    # untimed: first replay uploads the graph
-        except Exception as exc:                              # pragma: no cover - reported as absent
-            print(f"[bench] CUDA-graph capture of the device-resident steps failed ({exc})", file=sys.stderr)
-            g_dev = None
-        torch.cuda.synchronize()
+    # ---- device-resident timing, inside the clock-sampling window
     with ClockSampler(local_rank) as clocks:
-        barrier()
-        start.record(stream)
-        for i in range(args.steps):
-            ev[i][0].record(stream)
-            ops.store_kvcache(w.k, w.v, w.k_cache, w.v_cache, slots)
-            ev[i][1].record(stream)
-            ops.paged_attn_decode(w.q, w.k_cache, w.v_cache, cl, bt, w.scale, out=out)
-            ev[i][2].record(stream)
-        stop.record(stream)
-        barrier()
-        if g_dev is not None:
-            g_start.record(stream)
-            g_dev.replay()
-            g_stop.record(stream)
-            barrier()
-        # keep the sampler alive for at least a few samples on very short runs
-        if start.elapsed_time(stop) < 500 and not args.profile:
-            t_end = time.time() + 0.6
-            while time.time() < t_end:
-                if g_dev is not None:
-                    g_dev.replay()
-                else:
-                    step()
-            torch.cuda.synchronize()
-    total_ms = start.elapsed_time(stop)
-    graph_ms = g_start.elapsed_time(g_stop) if g_dev is not None else 0.0
-    g_dev = None
-    decode_all = [e[1].elapsed_time(e[2]) for e in ev]
-    decode_ms = statistics.mean(decode_all)
-    append_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+        r = time_decode_steps(ops, w, cl, bt, slots, out, args.steps, args.warmup, barrier,
+                              window_s=0.0 if args.profile else 0.5, min_replays=50, graph=not args.profile)
+    g = r["graph"]
 
     # ---- end to end: host inputs in pinned memory, output read back, every step
     from infer_b200.staging import StepStaging
@@ -401,17 +628,17 @@ def main():
         ops.paged_attn_decode(dev["q"], w.k_cache, w.v_cache, dev["cl"], dev["bt"], w.scale, out=out)
         out_host.copy_(out, non_blocking=True)
 
-    # The step is captured once in a CUDA graph (upload, append, decode, reduce, read-back) and
+    # The step is captured once in a CUDA graph (upload, append, decode, read-back) and
     # replayed, the way the reference replays its decode graphs (infer/engine/model_runner.py:135-152).
     e2e_graph = None
-    if not args.profile and os.environ.get("INFER_B200_BENCH_EAGER") != "1":
+    if not args.profile:
         try:
             e2e_body()
             torch.cuda.synchronize()
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            eg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(eg):
                 e2e_body()
-            e2e_graph = g
+            e2e_graph = eg
         except Exception as exc:                              # pragma: no cover - falls back to eager launches
             print(f"[bench] CUDA-graph capture of the end-to-end step failed ({exc}); timing eager launches", file=sys.stderr)
             torch.cuda.synchronize()
@@ -423,18 +650,19 @@ def main():
             e2e_body()
         torch.cuda.current_stream().synchronize()       # the caller reads the result every step
 
-    e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_ms, e2e_steps = 1e-6, 0
     if not args.profile:
         for _ in range(args.warmup):
             e2e_step()
-    barrier()
-    e_start.record(stream)
-    if not args.profile:
-        for _ in range(args.steps):
+        e2e_steps = max(args.steps, 1000)                # about a quarter of a second
+        e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e_start.record(stream)
+        for _ in range(e2e_steps):
             e2e_step()
-    e_stop.record(stream)
-    barrier()
-    e2e_ms = max(e_start.elapsed_time(e_stop), 1e-6)
+        e_stop.record(stream)
+        barrier()
+        e2e_ms = max(e_start.elapsed_time(e_stop), 1e-6) / e2e_steps
 
     # ---- bulk append (the chunked-prefill append: 32768 rows)
     n_bulk = 32768
@@ -443,17 +671,8 @@ def main():
     bk = torch.randn(n_bulk, hkv, 128, generator=gen, device=device).bfloat16()
     bv = torch.randn(n_bulk, hkv, 128, generator=gen, device=device).bfloat16()
     bslots = torch.randperm(w.num_blocks * 256, generator=gen, device=device)[:n_bulk].to(torch.int32)
-    reps = 3 if args.profile else 20
-    for _ in range(0 if args.profile else 3):
-        ops.store_kvcache(bk, bv, w.k_cache, w.v_cache, bslots)
-    torch.cuda.synchronize()
-    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a0.record(stream)
-    for _ in range(reps):
-        ops.store_kvcache(bk, bv, w.k_cache, w.v_cache, bslots)
-    a1.record(stream)
-    torch.cuda.synchronize()
-    bulk_ms = a0.elapsed_time(a1) / reps
+    bulk_ms = _timed(lambda: ops.store_kvcache(bk, bv, w.k_cache, w.v_cache, bslots), 3 if args.profile else 20,
+                     0 if args.profile else 3, stream)
     bulk_bytes = n_bulk * hkv * 128 * 2 * (2 + 2)
     del bk, bv, bslots
 
@@ -463,77 +682,51 @@ def main():
         bk = torch.randn(n_bulk2, hkv, 128, generator=gen, device=device).bfloat16()
         bv = torch.randn(n_bulk2, hkv, 128, generator=gen, device=device).bfloat16()
         bslots = torch.randperm(w.num_blocks * 256, generator=gen, device=device)[:n_bulk2].to(torch.int32)
-        for _ in range(2):
-            ops.store_kvcache(bk, bv, w.k_cache, w.v_cache, bslots)
-        torch.cuda.synchronize()
-        a0.record(stream)
-        for _ in range(5):
-            ops.store_kvcache(bk, bv, w.k_cache, w.v_cache, bslots)
-        a1.record(stream)
-        torch.cuda.synchronize()
-        bulk2_ms = a0.elapsed_time(a1) / 5
+        bulk2_ms = _timed(lambda: ops.store_kvcache(bk, bv, w.k_cache, w.v_cache, bslots), 5, 2, stream)
         del bk, bv, bslots
     bulk2_bytes = n_bulk2 * hkv * 128 * 2 * (2 + 2)
 
-    # ---- optional: the same pool as e4m3 bytes with one fp32 scale per (page, kv head)
-    fp8 = None
-    if args.fp8:
-        nb = w.num_blocks
-        k8 = torch.zeros(nb, 256, hkv, 128, dtype=torch.uint8, device=device)
-        v8 = torch.zeros_like(k8)
-        ks8 = torch.zeros(nb, hkv, device=device)
-        vs8 = torch.zeros(nb, hkv, device=device)
-        for lo in range(0, nb, 64):                           # quantise the bf16 pool page group by page group
-            hi = min(nb, lo + 64)
-            sl = torch.arange(lo * 256, hi * 256, dtype=torch.int32, device=device)
-            ops.store_kvcache(w.k_cache[lo:hi].reshape(-1, hkv, 128), w.v_cache[lo:hi].reshape(-1, hkv, 128), k8, v8, sl, ks8, vs8)
-        torch.cuda.synchronize()
-
-        def timed(fn, reps):
-            for _ in range(0 if args.profile else 3):
-                fn()
-            torch.cuda.synchronize()
-            a0.record(stream)
-            for _ in range(reps):
-                fn()
-            a1.record(stream)
-            torch.cuda.synchronize()
-            return a0.elapsed_time(a1) / reps
-
-        reps8 = 3 if args.profile else 20
-        dec8_ms = timed(lambda: ops.paged_attn_decode(w.q, k8, v8, cl, bt, w.scale, out=out, k_scale=ks8, v_scale=vs8), reps8)
-        app8_ms = timed(lambda: ops.store_kvcache(w.k, w.v, k8, v8, slots, ks8, vs8), reps8)
-        n_rows = min(32768, nb * 256)
-        sl = torch.arange(0, n_rows, dtype=torch.int32, device=device)
-        rk = w.k_cache.view(-1, hkv, 128)[:n_rows]
-        rv = w.v_cache.view(-1, hkv, 128)[:n_rows]
-        bulk8_ms = timed(lambda: ops.store_kvcache(rk, rv, k8, v8, sl, ks8, vs8), reps8)
-        kv8 = w.kv_bytes(elem_bytes=1)
-        fp8 = {"decode_us": dec8_ms * 1e3, "kv_bytes_e4m3": kv8, "decode_gbs": kv8 / (dec8_ms * 1e-3) / 1e9,
-               "tokens_per_us_vs_bf16": decode_ms / dec8_ms, "append_decode_shape_us": app8_ms * 1e3,
-               "bulk_rows": n_rows, "bulk_us": bulk8_ms * 1e3, "bulk_tok_s": n_rows / (bulk8_ms * 1e-3),
-               "bulk_gbs": n_rows * hkv * 128 * 2 * (2 + 1) / (bulk8_ms * 1e-3) / 1e9}
-        del k8, v8
+    # ---- sub-benchmarks on the same pool (rank 0's figures are reported)
+    fp8 = bench_fp8(ops, w, cl, bt, slots, out, r["decode_ms"], peak, args.profile) if "fp8" in want else None
+    fused = bench_fused_append(ops, w, peak, args.profile) if "fused" in want else None
+    flash = None
+    if "flash" in want and world == 1:
+        ops.store_kvcache(w.k, w.v, w.k_cache, w.v_cache, slots)
+        ops.paged_attn_decode(w.q, w.k_cache, w.v_cache, cl, bt, w.scale, out=out)
+        flash = bench_flash_attn(w, cl, bt, slots, out, args.steps)
+    validated = None
+    if world > 1:
+        ops.store_kvcache(w.k, w.v, w.k_cache, w.v_cache, slots)
+        ops.paged_attn_decode(w.q, w.k_cache, w.v_cache, cl, bt, w.scale, out=out)
+        validated = validate_gathered(w, out, world, rank)
 
     # ---- max over ranks
-    t = torch.tensor([total_ms, decode_ms, append_ms, e2e_ms, bulk_ms, bulk2_ms, graph_ms], device=device, dtype=torch.float64)
-    b = torch.tensor([float(kv_bytes)], device=device, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dist.all_reduce(b, op=dist.ReduceOp.SUM)
-    total_ms, decode_ms, append_ms, e2e_ms, bulk_ms, bulk2_ms, graph_ms = t.tolist()
-    job_bytes = b.item()
+    step_ms_rank = g["median"] if g else r["eager_ms"]
+    vals = reduce_max([step_ms_rank, g["min"] if g else 0.0, g["max"] if g else 0.0, r["eager_ms"], r["decode_ms"],
+                       r["append_ms"], e2e_ms, bulk_ms, bulk2_ms], device, world)
+    step_ms, step_min, step_max, eager_ms, decode_ms, append_ms, e2e_ms, bulk_ms, bulk2_ms = vals
+    job_bytes = reduce_sum(kv_bytes, device, world)
+    cpu = None
+    if rank == 0 and not args.no_cpu_baseline and not args.profile and world == 1:
+        secs, cpu_bytes, threads = cpu_sample(w, 8, 2)
+        cpu = {"value": cpu_bytes / secs / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
+               "sample": f"append + decode of the first 8 sequences ({cpu_bytes / 1e6:.0f} MB of KV), best of 2"}
+    n_seq = len(w.context_lens)
+    kv_logical = w.kv_bytes(unique=False)
+    del w, out, stage
+    torch.cuda.empty_cache()
+
+    strong = None
+    if "strong" in want and args.workload == "decode":
+        strong = {"long": bench_strong(ops, "long", world, rank, device, 20, 3, barrier, peak),
+                  "decode64": bench_strong(ops, "decode64", world, rank, device, 20, 3, barrier, peak)}
+    prefill = None
+    if "prefill" in want and world == 1:
+        prefill = bench_prefill(ops, device, 16, 10, 3)
 
     if rank == 0:
-        peak, peak_kind = measured_peak()
-        # The K timed steps run twice, each bracketed the same way: launched one by one, and captured
-        # once and replayed as ONE CUDA graph (the reference's own way of running decode,
-        # infer/engine/model_runner.py:135-198).  The graph figure is the headline; the other is kept.
-        eager_ms = total_ms / args.steps
-        step_ms = graph_ms / args.steps if graph_ms else eager_ms
         value = job_bytes / (step_ms * 1e-3) / 1e9
         achieved = kv_bytes / (decode_ms * 1e-3) / 1e9
-        n_seq = len(w.context_lens)
         if args.workload == "long":
             desc = (f"qwen3-32b long-context decode: batch {n_seq}, ctx lognormal(median 4096, sigma 0.8) capped at 32768, "
                     f"half the batch sharing the pages of a 2048-token prefix, 64q/8kv heads sharded {world}-way by KV "
@@ -541,6 +734,7 @@ def main():
         else:
             desc = (f"qwen3-8b decode shape: batch {n_seq}, ctx U[512,8192], 32q/8kv heads "
                     f"sharded {world}-way by KV head, page 256, 1 appended token per sequence")
+        n_replays = g["replays"] if g else 0
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
@@ -548,19 +742,23 @@ def main():
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": desc,
                        "global_batch": n_seq, "kv_bytes_per_gpu": kv_bytes,
-                       "kv_bytes_per_gpu_logical": w.kv_bytes(unique=False),
+                       "kv_bytes_per_gpu_logical": kv_logical,
                        "l2": f"KV per step ({kv_bytes / 1e9:.1f} GB per GPU) exceeds L2 (126 MB); no flush needed",
                        "parallelism": f"kv-head-shard{world}"},
-            "e2e": {"value": job_bytes / (e2e_ms / args.steps * 1e-3) / 1e9, "unit": UNIT,
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps,
+            "timing": {"method": f"one CUDA graph of {args.steps} steps replayed {n_replays} times, an event pair per replay; "
+                                 "value from the median replay (max over ranks)" if g else "kernels launched one by one",
+                       "replays": n_replays, "ms_per_step_min": step_min, "ms_per_step_max": step_max,
+                       "timed_region_s": g["timed_s"] if g else eager_ms * args.steps / 1e3},
+            "e2e": {"value": job_bytes / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps,
                     "launch": "cuda graph replay" if e2e_graph is not None else "eager"},
-            "gpu_launches": 3 * args.steps,
-            "launch": "cuda graph replay of the K steps" if graph_ms else "one launch per kernel",
+            "gpu_launches": 2 * args.steps * max(n_replays, 1),
+            "launch": "cuda graph replay of the K steps" if g else "one launch per kernel",
             "value_launched_one_by_one": job_bytes / (eager_ms * 1e-3) / 1e9, "ms_per_step_launched_one_by_one": eager_ms,
-            "roofline": {"bound": "hbm", "kernel": "decode_tma_kernel + decode_reduce_kernel", "achieved": achieved,
+            "roofline": {"bound": "hbm", "kernel": "decode_tma_kernel", "achieved": achieved,
                          "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
                          "frac_of_8000": achieved / 8000.0, "decode_ms": decode_ms,
-                         "decode_ms_median": statistics.median(decode_all), "decode_ms_min": min(decode_all),
+                         "decode_ms_median": r["decode_ms_median"], "decode_ms_min": r["decode_ms_min"],
                          "traffic": kv_bytes * DECODE_TRAFFIC_PER_KV_BYTE,
                          "traffic_note": "DRAM bytes per decode launch: ncu capture of a batch-16 case (259.5 MB read + "
                                          "written for 249.9 MB of KV), scaled by KV bytes"},
@@ -572,13 +770,10 @@ def main():
                        "bulk2_gbs": bulk2_bytes / (bulk2_ms * 1e-3) / 1e9 if bulk2_ms else None},
             "clocks": clocks.summary(),
         }
-        if fp8 is not None:
-            line["fp8_kv"] = fp8
-        if not args.no_cpu_baseline and not args.profile and world == 1:
-            secs, cpu_bytes, threads = cpu_sample(w, 8, 2)
-            line["cpu_baseline"] = {
-                "value": cpu_bytes / secs / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
-                "sample": f"append + decode of the first 8 sequences ({cpu_bytes / 1e6:.0f} MB of KV), best of 2"}
+        for key, obj in (("fp8_kv", fp8), ("fused_append", fused), ("prefill", prefill), ("strong", strong),
+                         ("validated", validated), ("reference_gpu", flash), ("cpu_baseline", cpu)):
+            if obj is not None:
+                line[key] = obj
         print(json.dumps(line))
     if world > 1:
         dist.barrier()

@@ -199,6 +199,20 @@ public:
         if (--page.ref_count == 0) where_[block_id] = free_.insert(free_.end(), block_id);
     }
 
+    // Replaces the order of the free list (every page must be free and appear once): lets a
+    // workload generator scatter the pages of its sequences over the pool.
+    void set_free_order(const int32_t* ids, size_t n) {
+        if (n != blocks_.size() || free_.size() != blocks_.size())
+            throw std::runtime_error("BlockManager::set_free_order: needs every page, all of them free");
+        std::vector<char> seen(n, 0);
+        for (size_t i = 0; i < n; ++i) {
+            if (ids[i] < 0 || size_t(ids[i]) >= n || seen[ids[i]]) throw std::runtime_error("BlockManager::set_free_order: not a permutation");
+            seen[ids[i]] = 1;
+        }
+        free_.clear();
+        for (size_t i = 0; i < n; ++i) where_[ids[i]] = free_.insert(free_.end(), ids[i]);
+    }
+
     size_t block_size() const { return block_size_; }
     size_t num_free() const { return free_.size(); }
     const std::list<int32_t>& free_block_ids() const { return free_; }

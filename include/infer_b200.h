@@ -3,9 +3,17 @@
  *
  * Every entry point takes plain device pointers, sizes and a CUDA stream handle
  * (cudaStream_t passed as void*; NULL = the legacy default stream).  No entry point
- * allocates, frees or synchronises: outputs, pools and scratch memory belong to the
- * caller, which makes each call capturable in a CUDA graph with static buffers, the
- * scheme the reference engine uses for decode (infer/engine/model_runner.py:135-198).
+ * allocates or frees device memory: outputs, pools and scratch memory belong to the
+ * caller.  The per-step entry points of decode - infer_kv_append,
+ * infer_qk_norm_rope_append, infer_decode_step_advance, infer_paged_decode - make no
+ * CUDA call but kernel launches on the given stream (plus one memset node in
+ * infer_paged_decode_noalloc) and read no device data on the host, so they
+ * can be captured in a CUDA graph with static buffers, the scheme the reference engine
+ * uses for decode (infer/engine/model_runner.py:135-198).  The prefill entry points
+ * encode a tensor map for q on the host in every call (the address of q is baked into the
+ * launch) and are meant for eager launches, which is how the reference runs prefill
+ * (infer/engine/model_runner.py:128-134); a captured prefill is only valid for the q
+ * address it was captured with.  The two *_status functions synchronise the stream.
  * All functions return 0 on success and a negative INFER_ERR_* code otherwise;
  * no C++ exception crosses this boundary.
  *
@@ -46,8 +54,10 @@ enum {
     INFER_ERR_CUDA = -6,       /* a CUDA call failed; see infer_last_cuda_error() */
     INFER_ERR_DTYPE = -7,      /* pool dtype not valid for this entry point */
     INFER_ERR_DEVICE = -8,     /* the kernel reported a bounded wait that ran out */
-    INFER_ERR_TOO_LARGE = -9   /* the problem needs more than the built-in scratch of
+    INFER_ERR_TOO_LARGE = -9,  /* the problem needs more than the built-in scratch of
                                   infer_paged_decode_noalloc */
+    INFER_ERR_STATE = -10      /* page allocator: out of pages, unknown or duplicate sequence id,
+                                  or a call out of order; see infer_block_manager_last_error() */
 };
 
 enum { INFER_KV_BF16 = 0, INFER_KV_E4M3 = 1 };
@@ -105,7 +115,13 @@ INFER_API int infer_decode_step_advance(int32_t* context_lens, int32_t* slot_map
  * (flash_attn_with_kvcache(q[:,None], k_cache, v_cache, cache_seqlens, block_table,
  * softmax_scale, causal=True), infer/ops/attention.py:117-121) and fills the empty
  * flash_attn_decode stub (src/operators/flashattn/flashattn_decode.cu:1-13).
- * q, out: bf16 [batch, n_q_heads, 128] contiguous. */
+ * q, out: bf16 [batch, n_q_heads, 128] contiguous.  Any n_q_heads that is a multiple of the
+ * pool's kv heads with at most 8 query heads per kv head (group sizes 1..8, e.g. 40 over 8).
+ * workspace: infer_paged_decode_workspace_bytes() of 16-byte aligned device memory that the
+ * caller zero-fills ONCE before its first use; a call leaves the part that has to be zero
+ * (a status word and the ticket counters of contexts split over thread blocks) at zero
+ * again.  Calls that share a workspace must not overlap on the GPU (one stream, or one
+ * graph): give every stream that runs decode its own. */
 INFER_API int infer_paged_decode(const infer_kv_pool_t* pool, void* out, const void* q,
                        const int32_t* context_lens, const int32_t* block_tables,
                        int64_t bt_stride, int batch, int n_q_heads, float softmax_scale,
@@ -147,13 +163,17 @@ INFER_API int infer_flash_attn_prefill(const void* q, const void* k, const void*
  * call on a device looks up the device address of the built-in array (the device must be
  * current, and must be the one the pool was created on); make that first call before any
  * stream capture.  Every call on a device shares the one array, which keeps the previous
- * call's contents; the function clears the status word that must start at zero, everything
- * else is rewritten before it is read.  Two calls that overlap on the GPU (different
+ * call's contents; the function clears what must start at zero (the status word and the
+ * ticket counters, one memset), everything else is rewritten before it is read.  A bounded
+ * wait that ran out is reported by infer_paged_decode_status(NULL, stream).  Two calls that overlap on the GPU (different
  * streams, or concurrent graphs) race on the array: serialise them.
  *
- * Limits: the scratch layout for the pool's geometry and this GPU must fit 2 MiB (up to 8 query
- * heads per KV head, GPUs of up to about 240 SMs) and batch <= 2048; anything
- * larger returns INFER_ERR_TOO_LARGE without launching. */
+ * Limits: the scratch layout for the pool's geometry and this GPU must fit 2 MiB - a 4352-byte
+ * header plus 2080 bytes per (thread block = SM, partial row), where a tile carries
+ * (kv heads per tile) x (query heads per kv head) partial rows.  On 148 SMs that is up to 13
+ * rows: every bf16 pool fits (one kv head per tile, at most 8 rows; GPUs of up to 250 SMs),
+ * and an e4m3 pool fits by taking fewer kv heads per tile than its default.  batch <= 2048.
+ * Anything larger returns INFER_ERR_TOO_LARGE without launching. */
 INFER_API int infer_paged_decode_noalloc(const infer_kv_pool_t* pool, void* out, const void* q,
                                const int32_t* context_lens, const int32_t* block_tables,
                                int64_t bt_stride, int batch, int n_q_heads, float softmax_scale,
@@ -166,9 +186,49 @@ INFER_API int infer_paged_decode_noalloc(const infer_kv_pool_t* pool, void* out,
  * that call before any stream capture.  A debugging read, like infer_paged_decode_status. */
 INFER_API int infer_prefill_status(void* stream);
 
-/* Reads the device status word the last decode call on this workspace left behind
- * (synchronises the stream).  0 = no bounded wait ran out. */
+/* Reads the device status word the decode calls on this workspace left behind (synchronises
+ * the stream): INFER_OK = no bounded wait ran out; INFER_ERR_DEVICE = one did since the last
+ * read, the outputs of that call are undefined, and the word and the ticket counters have
+ * been cleared so that the workspace can be used again.  workspace == NULL reads the
+ * built-in array of infer_paged_decode_noalloc on the current device. */
 INFER_API int infer_paged_decode_status(const void* workspace, void* stream);
+
+/* Page allocator with prefix sharing (host-only).  Replaces BlockManager / Block and the page
+ * arithmetic of Sequence (infer/engine/block_mannager.py:26-133, infer/engine/sequence.py:15-84):
+ * pages leave the front of a FIFO free list; a full page is keyed by the XXH64 digest of the
+ * previous page's digest and its token ids; a prompt whose leading pages carry known digests
+ * and the same token ids shares those pages (reference counts); a page returns to the back of
+ * the free list when its count reaches zero.  Same page ids as the reference for the same call
+ * sequence.  Sequences live inside the manager under the caller's ids.
+ *   allocate      whole-prompt allocation (BlockManager.allocate); returns the number of cached
+ *                 (shared) tokens, or a negative error
+ *   append        for every new token: Sequence.append_token, then BlockManager.may_append (a
+ *                 new page when the token is the first of one, a digest when it fills one);
+ *                 n_new == 0 runs may_append alone
+ *   can_allocate / can_append   1 or 0 (negative on error), as the reference scheduler asks
+ *                 (infer/engine/scheduler.py:27,44)
+ *   deallocate    BlockManager.deallocate, used for finished and for preempted sequences
+ *   block_table / free_ids / ref_counts   copy up to cap entries, return the full count
+ *   set_free_order  replaces the order of the (entirely free) free list: workload generators
+ *                 use it to scatter pages over the pool */
+typedef struct infer_block_manager infer_block_manager_t;
+INFER_API int infer_block_manager_create(infer_block_manager_t** mgr, int64_t num_blocks, int block_size);
+INFER_API int infer_block_manager_destroy(infer_block_manager_t* mgr);
+INFER_API int infer_block_manager_can_allocate(const infer_block_manager_t* mgr, int64_t n_tokens);
+INFER_API int64_t infer_block_manager_allocate(infer_block_manager_t* mgr, int64_t seq_id, const int64_t* token_ids,
+                                     int64_t n_tokens);
+INFER_API int infer_block_manager_can_append(const infer_block_manager_t* mgr, int64_t seq_id);
+INFER_API int infer_block_manager_append(infer_block_manager_t* mgr, int64_t seq_id, const int64_t* token_ids,
+                               int64_t n_new);
+INFER_API int infer_block_manager_deallocate(infer_block_manager_t* mgr, int64_t seq_id);
+INFER_API int64_t infer_block_manager_block_table(const infer_block_manager_t* mgr, int64_t seq_id, int32_t* out,
+                                        int64_t cap);
+INFER_API int64_t infer_block_manager_num_tokens(const infer_block_manager_t* mgr, int64_t seq_id);
+INFER_API int64_t infer_block_manager_num_free(const infer_block_manager_t* mgr);
+INFER_API int64_t infer_block_manager_free_ids(const infer_block_manager_t* mgr, int32_t* out, int64_t cap);
+INFER_API int64_t infer_block_manager_ref_counts(const infer_block_manager_t* mgr, int32_t* out, int64_t cap);
+INFER_API int infer_block_manager_set_free_order(infer_block_manager_t* mgr, const int32_t* ids, int64_t n);
+INFER_API const char* infer_block_manager_last_error(const infer_block_manager_t* mgr);
 
 INFER_API const char* infer_strerror(int code);
 INFER_API int infer_last_cuda_error(void);

@@ -2,11 +2,20 @@
 //
 // bf16 pools: a pure byte copy, one 16-byte load and one 16-byte store per thread and
 // row chunk, K and V in the same thread, two chunks in flight per thread.
-// e4m3 pools: a cleared workspace and three kernels (collect the new rows' amax / 448 per
-// (page, head); raise the scales and re-encode pages whose scale grew; write the new rows) so
-// that the result depends on no scheduling order and matches the CPU oracle bit for bit.  The
-// kernels work on strips of 8 tokens per warp: 16-byte loads, 8 in flight per lane, one atomic
-// per run of tokens that share a page.
+// e4m3 pools: the scale of a (page, head) must be final before any of its new rows is
+// quantised.  A small kernel first cuts the token list into runs (consecutive tokens going to
+// consecutive slots of one page) and finds out whether any page receives more than one run.
+//   * No page does (every prefill chunk, every decode step): fp8_run_kernel gives each (run, head,
+//     k|v) to one thread block, which reads the run's rows ONCE into registers, takes their amax,
+//     settles the scale (re-encoding the page's older rows when a positive scale grew) and
+//     quantises from the registers.
+//   * Otherwise (slots scattered over pages): three kernels - collect the new rows' amax / 448 per
+//     (page, head) with atomics; raise the scales and re-encode pages whose scale grew; write the
+//     new rows - on strips of 8 tokens per warp.
+// Both ways give the bytes and scales of the CPU oracle bit for bit, whatever the scheduling.
+// All five kernels are always launched; those of the way not taken return at once.
+#include <climits>
+
 #include "common.cuh"
 
 namespace ib {
@@ -16,8 +25,12 @@ __global__ void __launch_bounds__(256) append_bf16_kernel(
     const uint4* __restrict__ k, const uint4* __restrict__ v, int64_t k_pitch16, int64_t v_pitch16,
     uint4* __restrict__ k_cache, uint4* __restrict__ v_cache, const int32_t* __restrict__ slot_mapping,
     int64_t n_tokens, int chunks, int64_t num_slots) {
-    pdl_launch_dependents();   // an attention kernel behind this one may run its prologue already
-    pdl_wait();                // launched programmatically itself: the kernel in front may still be reading the pools
+    // Launched programmatically: the kernel in front (the previous step's attention, or the kernel
+    // that advances the step metadata) may still be running.  Wait for it first, and only then let
+    // the attention kernel behind this one start: its prologue reads context_lens, which the kernel
+    // in front may have been writing.
+    pdl_wait();
+    pdl_launch_dependents();
     const int64_t total = n_tokens * chunks;
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
     for (int64_t u0 = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; u0 < total; u0 += 2 * stride) {
@@ -58,6 +71,9 @@ struct Fp8Side {
     float* cand;                   // workspace [num_blocks, Hkv]: this call's amax / 448 per (page, head)
 };
 
+// Control words at the end of the workspace.
+enum { kCtlConflictAcc = 0, kCtlDone = 1, kCtlConflict = 2, kCtlWords = 16 };
+
 struct Fp8Args {
     Fp8Side k, v;
     const int32_t* slot_mapping;
@@ -66,6 +82,8 @@ struct Fp8Args {
     int n_kv_heads;
     int block_size;
     uint64_t page_magic;           // ceil(2^64 / block_size): page = mulhi(slot, page_magic), exact for slot < 2^32
+    int* count;                    // workspace [num_blocks]: runs of this call per page (zero between calls)
+    int* ctl;                      // workspace [kCtlWords]: see the enum above
 
     __device__ __forceinline__ int64_t page_of(int64_t slot) const {
         return int64_t(__umul64hi(uint64_t(slot), page_magic));
@@ -157,6 +175,9 @@ __device__ __forceinline__ void amax_flush(const Fp8Args& a, const StripLane& u,
 
 // cand[page, head] = max over this call's rows on that page of amax(row) / 448
 __global__ void __launch_bounds__(256, 3) fp8_amax_kernel(Fp8Args a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    if (a.ctl[kCtlConflict] == 0) return;      // every page got one run: fp8_run_kernel did the work
     const int64_t strips = (a.n_tokens + kStrip - 1) / kStrip;
     const int64_t stride = int64_t(gridDim.x) * kWarpsPerCta;
     const int lane = threadIdx.x & 31;
@@ -250,6 +271,7 @@ __device__ __forceinline__ void rescale_claim(const Fp8Args& a, const StripLane&
 __global__ void __launch_bounds__(256) fp8_rescale_kernel(Fp8Args a) {
     pdl_launch_dependents();
     pdl_wait();                // the candidates of the kernel in front
+    if (a.ctl[kCtlConflict] == 0) return;
     const int64_t strips = (a.n_tokens + kStrip - 1) / kStrip;
     const int64_t stride = int64_t(gridDim.x) * kWarpsPerCta;
     const int lane = threadIdx.x & 31;
@@ -348,6 +370,7 @@ struct Divisor {
 __global__ void __launch_bounds__(256, 3) fp8_write_kernel(Fp8Args a) {
     pdl_launch_dependents();
     pdl_wait();                // the final scales and re-encoded pages of the kernel in front
+    if (a.ctl[kCtlConflict] == 0) return;
     const int64_t strips = (a.n_tokens + kStrip - 1) / kStrip;
     const int64_t stride = int64_t(gridDim.x) * kWarpsPerCta;
     const int lane = threadIdx.x & 31;
@@ -397,13 +420,169 @@ __global__ void __launch_bounds__(256, 3) fp8_write_kernel(Fp8Args a) {
     }
 }
 
+
+// --------------------------------------------------------------------------- runs
+__device__ __forceinline__ bool slot_valid(const Fp8Args& a, int s) { return s >= 0 && int64_t(s) < a.num_slots; }
+
+// Token i starts a run when its slot is valid and the token in front does not sit in the slot in
+// front of it on the same page.
+__device__ __forceinline__ bool is_run_start(const Fp8Args& a, int64_t i, int& slot) {
+    slot = __ldg(a.slot_mapping + i);
+    if (!slot_valid(a, slot)) return false;
+    if (i == 0) return true;
+    const int prev = __ldg(a.slot_mapping + i - 1);
+    return !(slot_valid(a, prev) && prev + 1 == slot && a.page_of(prev) == a.page_of(slot));
+}
+
+// Counts the runs every page receives.  The block that finishes last publishes whether any page
+// got more than one (kCtlConflict, written afresh by every call) and clears the two accumulators.
+__global__ void __launch_bounds__(256) fp8_classify_kernel(Fp8Args a) {
+    pdl_launch_dependents();
+    const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    int conflict = 0, slot;
+    if (i < a.n_tokens && is_run_start(a, i, slot)) conflict = atomicAdd(a.count + a.page_of(slot), 1) > 0;
+    conflict = __syncthreads_or(conflict);
+    if (threadIdx.x == 0) {
+        if (conflict) atomicOr(a.ctl + kCtlConflictAcc, 1);
+        __threadfence();
+        if (atomicAdd(a.ctl + kCtlDone, 1) == int(gridDim.x) - 1) {
+            __threadfence();
+            a.ctl[kCtlConflict] = atomicExch(a.ctl + kCtlConflictAcc, 0);
+            a.ctl[kCtlDone] = 0;
+        }
+    }
+}
+
+// One thread block per (slice of the token list, head, k|v): it looks for run starts in its slice
+// and handles each run it finds from end to end.  A row of one head is 256 bytes = 16 lanes x 16
+// bytes, THREADS / 16 rows per load instruction, 16 loads in flight per thread: 256 threads hold a
+// whole 256-row run (64 KiB) in registers, so the rows are read from memory once.  Runs longer than
+// the registers hold (32 threads: 32 rows) read the remainder a second time, from L2.
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS, THREADS == 256 ? 2 : 16) fp8_run_kernel(Fp8Args a, int slice_len) {
+    constexpr int kRowsPerLoad = THREADS / 16, kHeld = 16 * kRowsPerLoad, kWarps = THREADS / 32;
+    __shared__ int s_start[64], s_n, s_len;
+    __shared__ float s_red[kWarps], s_scale, s_ratio;
+    pdl_launch_dependents();
+    pdl_wait();                                   // the run counts and the verdict of the kernel in front
+    const bool conflict = a.ctl[kCtlConflict] != 0;
+    if (conflict && blockIdx.y != 0) return;      // the three strip kernels take over; row 0 still clears the counts
+    const int tid = threadIdx.x;
+    const int head = int(blockIdx.y >> 1);
+    const Fp8Side side = (blockIdx.y & 1) ? a.v : a.k;
+    const int64_t tok0 = int64_t(blockIdx.x) * slice_len;
+    if (tid == 0) s_n = 0;
+    __syncthreads();
+    for (int t = tid; t < slice_len; t += THREADS) {
+        int slot;
+        if (tok0 + t < a.n_tokens && is_run_start(a, tok0 + t, slot)) {
+            s_start[atomicAdd(&s_n, 1)] = t;
+            if (blockIdx.y == 0) a.count[a.page_of(slot)] = 0;      // nobody reads the counts any more
+        }
+    }
+    __syncthreads();
+    if (conflict) return;
+    const int n_runs = s_n;
+    const int lane16 = tid & 15, rsub = tid >> 4;
+    const int64_t dst_pitch = int64_t(a.n_kv_heads) * kHeadDim;
+    for (int r = 0; r < n_runs; ++r) {
+        const int64_t start = tok0 + s_start[r];
+        const int slot0 = __ldg(a.slot_mapping + start);
+        const int64_t page = a.page_of(slot0);
+        // length of the run: the first offset whose token does not continue it
+        int len = 1;
+        for (int base = 1;; base += THREADS) {
+            if (tid == 0) s_len = INT_MAX;
+            __syncthreads();
+            const int64_t i = start + base + tid;
+            bool cont = i < a.n_tokens;
+            if (cont) {
+                const int s = __ldg(a.slot_mapping + i);
+                cont = s == slot0 + base + tid && int64_t(s) < a.num_slots && a.page_of(s) == page;
+            }
+            if (!cont) atomicMin(&s_len, base + tid);
+            __syncthreads();
+            const int first_bad = s_len;
+            __syncthreads();
+            if (first_bad != INT_MAX) { len = first_bad; break; }
+            len = base + THREADS;
+        }
+        // pass 1: the rows (the first kHeld stay in registers) and their largest magnitude
+        const __nv_bfloat16* src = side.src + head * kHeadDim + lane16 * 8;
+        uint4 raw[16];
+        __nv_bfloat162 best = __float2bfloat162_rn(0.0f);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int row = rsub + j * kRowsPerLoad;
+            raw[j] = make_uint4(0, 0, 0, 0);
+            if (row < len) raw[j] = __ldg(reinterpret_cast<const uint4*>(src + (start + row) * side.pitch));
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) best = __hmax2(best, amax8(raw[j]));
+        for (int row = kHeld + rsub; row < len; row += kRowsPerLoad)
+            best = __hmax2(best, amax8(__ldg(reinterpret_cast<const uint4*>(src + (start + row) * side.pitch))));
+        float m = fmaxf(__low2float(best), __high2float(best));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if ((tid & 31) == 0) s_red[tid >> 5] = m;
+        __syncthreads();
+        if (tid == 0) {
+#pragma unroll
+            for (int w = 1; w < kWarps; ++w) m = fmaxf(m, s_red[w]);
+            const int64_t e = page * a.n_kv_heads + head;
+            const float old = side.scale[e];
+            float s = old, ratio = -1.0f;
+            if (m > 0.0f) {
+                const float c = __fdiv_rn(m, 448.0f);
+                if (c > old) {
+                    side.scale[e] = c;
+                    s = c;
+                    if (old > 0.0f) ratio = __fdiv_rn(old, c);
+                }
+            }
+            s_scale = s;
+            s_ratio = ratio;
+        }
+        __syncthreads();
+        const float scale = s_scale, ratio = s_ratio;
+        if (ratio >= 0.0f) {
+            // the page's scale grew: re-encode what the page holds for this head (rows this run is about
+            // to overwrite included, which is harmless), before any new row is written
+            uint8_t* base = side.cache + (page * a.block_size * a.n_kv_heads + head) * int64_t(kHeadDim);
+            for (int i = tid; i < a.block_size * 8; i += THREADS) {
+                uint4* p = reinterpret_cast<uint4*>(base + (i >> 3) * dst_pitch + (i & 7) * 16);
+                uint4 q = *p;
+                q.x = rescale4(q.x, ratio);
+                q.y = rescale4(q.y, ratio);
+                q.z = rescale4(q.z, ratio);
+                q.w = rescale4(q.w, ratio);
+                *p = q;
+            }
+            __syncthreads();
+        }
+        // pass 2: quantise with the final scale
+        const Divisor div(scale);
+        uint8_t* dst = side.cache + int64_t(slot0) * dst_pitch + head * kHeadDim + lane16 * 8;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int row = rsub + j * kRowsPerLoad;
+            if (row < len) *reinterpret_cast<uint2*>(dst + row * dst_pitch) = div.quantise8(raw[j]);
+        }
+        for (int row = kHeld + rsub; row < len; row += kRowsPerLoad)
+            *reinterpret_cast<uint2*>(dst + row * dst_pitch) =
+                div.quantise8(__ldg(reinterpret_cast<const uint4*>(src + (start + row) * side.pitch)));
+        __syncthreads();                          // s_red, s_scale and s_ratio are reused by the next run
+    }
+}
+
 }  // namespace ib
 
 extern "C" {
 
 size_t infer_kv_append_workspace_bytes(const infer_kv_pool_t* pool) {
     if (!pool || pool->dtype != INFER_KV_E4M3) return 0;
-    return size_t(2) * pool->num_blocks * pool->n_kv_heads * sizeof(float);
+    // candidates of k and v per (page, head), runs per page, control words
+    return (size_t(2) * pool->num_blocks * pool->n_kv_heads + size_t(pool->num_blocks) + ib::kCtlWords) * 4;
 }
 
 int infer_kv_append(const infer_kv_pool_t* pool, const void* k, const void* v, int64_t k_row_stride,
@@ -454,15 +633,26 @@ int infer_kv_append(const infer_kv_pool_t* pool, const void* k, const void* v, i
     a.block_size = pool->block_size;
     a.page_magic = ~uint64_t(0) / uint64_t(pool->block_size) + 1;
     if (pool->num_slots >= (int64_t(1) << 32)) return INFER_ERR_GEOMETRY;
+    a.count = reinterpret_cast<int*>(cand + 2 * pool->num_blocks * pool->n_kv_heads);
+    a.ctl = a.count + pool->num_blocks;
+    if (2 * pool->n_kv_heads > 65535) return INFER_ERR_GEOMETRY;
+    // runs: how many a page receives, then one thread block per (slice of tokens, head, k|v)
+    ib::fp8_classify_kernel<<<unsigned((n_tokens + 255) / 256), 256, 0, stream>>>(a);
+    if (n_tokens <= 1024) {
+        const dim3 grid{unsigned(n_tokens), unsigned(2 * pool->n_kv_heads), 1u};
+        IB_CUDA(ib::launch_pdl(ib::fp8_run_kernel<32>, grid, dim3(32), 0, stream, a, 1));
+    } else {
+        const dim3 grid{unsigned((n_tokens + 63) / 64), unsigned(2 * pool->n_kv_heads), 1u};
+        IB_CUDA(ib::launch_pdl(ib::fp8_run_kernel<256>, grid, dim3(256), 0, stream, a, 64));
+    }
+    // strips: only when some page received several runs (the kernels return at once otherwise)
     const int64_t strips = (n_tokens + ib::kStrip - 1) / ib::kStrip;
     const int rows = 2 * ((pool->n_kv_heads + 1) / 2);             // grid rows: (k|v) x head pair
     int64_t per_row = (strips + ib::kWarpsPerCta - 1) / ib::kWarpsPerCta;
     const int64_t cap = (int64_t(pool->sm_count) * 12 + rows - 1) / rows;
     if (per_row > cap) per_row = cap;
-    if (rows > 65535) return INFER_ERR_GEOMETRY;
     const dim3 blocks{unsigned(per_row), unsigned(rows), 1u};
-    IB_CUDA(cudaMemsetAsync(workspace, 0, need, stream));
-    ib::fp8_amax_kernel<<<blocks, 256, 0, stream>>>(a);
+    IB_CUDA(ib::launch_pdl(ib::fp8_amax_kernel, blocks, dim3(256), 0, stream, a));
     IB_CUDA(ib::launch_pdl(ib::fp8_rescale_kernel, blocks, dim3(256), 0, stream, a));
     IB_CUDA(ib::launch_pdl(ib::fp8_write_kernel, blocks, dim3(256), 0, stream, a));
     return ib::check_launch();

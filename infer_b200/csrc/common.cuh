@@ -12,12 +12,14 @@
 #include <utility>
 
 #include "../../include/infer_b200.h"
+#include "../../include/infer_b200_selftest.h"
 
 namespace ib {
 
 constexpr int kHeadDim = 128;
 constexpr int kMaxBatch = 2048;      // context-length prefix table kept in shared memory
 constexpr int kMaxGroup = 8;         // query heads per KV head
+constexpr uint32_t kDefaultWaitLimit = 1u << 22;   // polls of a bounded barrier wait (about a second)
 
 // One tensor map per (pool, token-box height): dims {128, n_kv_heads, num_slots},
 // box {inner, 1, rows}, 128-byte swizzle.
@@ -50,6 +52,9 @@ namespace ib {
 
 void set_cuda_error(cudaError_t e);
 int check_launch();
+// Raise the dynamic shared-memory limits of the decode kernels on the current device
+// (called when a pool handle is created, so the per-step entry points only launch).
+int decode_prepare_device();
 // Encodes a 3-D tiled tensor map with 128-byte swizzle; returns INFER_OK or INFER_ERR_CUDA.
 int encode_map_3d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t d0, uint64_t d1,
                   uint64_t d2, uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0,
@@ -99,9 +104,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: returns false when the limit ran out (about a second of polling).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < (1u << 22); ++i) {
+// Bounded wait: returns false when `limit` polls went by without the phase completing (the
+// default is about a second).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit = kDefaultWaitLimit) {
+    for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if (i > 64) __nanosleep(i > 4096 ? 256 : 32);
     }

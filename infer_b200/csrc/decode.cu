@@ -6,11 +6,11 @@
 //    one kv head per tile, run q.K^T and P.V on mma.sync with the query-head group in the M
 //    dimension, and keep the online-softmax state (max, sum, accumulator) in registers,
 //    merging row statistics with quad shuffles.
-//  * decode_simple_kernel   e4m3 pools (dequantise on load) - plain loads, CUDA cores.
-//  * decode_reduce_kernel   merges the partials of (sequence, head group)s that span CTAs.
+//  * decode_tma_fp8_kernel   e4m3 pools: the same ring; K and V bytes go to the tensor cores
+//    as f16, the page scales are folded into the softmax exponent and its correction factor.
 //
-// The work split (equal KV bytes per CTA, two scratch slots per CTA) is described in
-// decode_common.cuh.
+// The work split (equal KV bytes per CTA, two scratch slots per CTA, the last CTA of a split
+// sequence merging its partials) is described in decode_common.cuh.
 #include <cstdlib>
 #include <mutex>
 #include <utility>
@@ -19,159 +19,47 @@
 
 namespace ib {
 
-// =========================================================================== simple kernel
-template <int G, bool FP8>
-__global__ void __launch_bounds__(128) decode_simple_kernel(DecodeParams p) {
-    constexpr int TT = 64;
-    __shared__ int s_tp[kMaxBatch + 1];
-    __shared__ int s_scan[128];
-    __shared__ float s_m[4][G], s_l[4][G];
-    __shared__ float s_o[4][G][kHeadDim];
+constexpr int kStages = 3;
+constexpr int kTileBytes = 32768;                 // K (or V) bytes per stage: 128 rows x 256 B
+constexpr int kConsumerWarps = 8;
+constexpr int kTmaThreads = (kConsumerWarps + 1) * 32;
+constexpr int kMergeSlotFloats = 36 * 32;         // 32 accumulators + up to two maxima and two sums per lane
 
-    build_tile_prefix(p.context_lens, p.batch, TT, s_tp, s_scan);
-    pdl_launch_dependents();
-    pdl_wait();
-    const int ng = p.n_kv_heads;
-    const int total = ng * s_tp[p.batch];
-    const int chunk = max(1, (total + int(gridDim.x) - 1) / int(gridDim.x));
-    if (blockIdx.x == 0) {
-        for (int i = threadIdx.x; i <= p.batch; i += blockDim.x) p.prefix[i] = s_tp[i];
-        if (threadIdx.x == 0) {
-            p.header[1] = total;
-            p.header[2] = chunk;
-            p.header[3] = gridDim.x;
-        }
+// =========================================================================== merge of split (b, hg)
+// Called by all 256 consumer threads of a CTA right after it left a partial for segment `sg`
+// (uniformly: a segment is partial for every warp or for none).  The CTA draws a ticket from
+// the counter of that (sequence, head group); the one that draws the last ticket finds every
+// other partial already in memory, merges them and writes the output rows.  rows = HPC * group;
+// row r belongs to query head hg * rows + r.
+__device__ __forceinline__ void merge_if_last(const DecodeParams& p, const int* s_tp, int ng, const Segment& sg,
+                                              int chunk, int rows, volatile int* s_flag) {
+    const int first = ng * s_tp[sg.b] + sg.hg * sg.ntiles;
+    const int c0 = first / chunk, c1 = (first + sg.ntiles - 1) / chunk;
+    asm volatile("bar.sync 1, 256;" ::: "memory");          // every partial store of this CTA is issued
+    if (threadIdx.x == 0) {
+        __threadfence();                                     // ... and visible before the ticket is
+        const int ticket = atomicAdd(p.counters + c0, 1);
+        const int last = ticket == c1 - c0;
+        if (last) p.counters[c0] = 0;                        // all participants have drawn: ready for the next launch
+        *s_flag = last;
     }
-    const int lo = min(total, int(blockIdx.x) * chunk), hi = min(total, lo + chunk);
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (!*s_flag) return;
+    __threadfence();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int elem = FP8 ? 1 : 2;
-
-    for (int g = lo; g < hi;) {
-        const Segment sg = locate_segment(s_tp, p.batch, ng, g, hi);
-        const int ctx = p.context_lens[sg.b];
-        const int head = sg.hg;
-        float q[G][4], o[G][4], m[G], l[G];
-#pragma unroll
-        for (int j = 0; j < G; ++j) {
-            const uint2 raw = *reinterpret_cast<const uint2*>(
-                p.q + (int64_t(sg.b) * p.n_q_heads + head * G + j) * kHeadDim + lane * 4);
-            const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
-            const __nv_bfloat162 c = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-            q[j][0] = __low2float(a); q[j][1] = __high2float(a);
-            q[j][2] = __low2float(c); q[j][3] = __high2float(c);
-            o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
-            m[j] = -INFINITY;
-            l[j] = 0.f;
-        }
-        for (int t = sg.t0; t < sg.t1; ++t) {
-            for (int i = 0; i < 16; ++i) {
-                const int tok = t * TT + warp * 16 + i;
-                if (tok >= ctx) break;
-                const int page = p.block_tables[int64_t(sg.b) * p.bt_stride + tok / p.block_size];
-                if (page < 0 || page >= p.num_blocks) continue;
-                const int64_t slot = int64_t(page) * p.block_size + tok % p.block_size;
-                const int64_t off = ((slot * p.n_kv_heads + head) * kHeadDim + lane * 4) * elem;
-                float kf[4], vf[4];
-                if (FP8) {
-                    const uint32_t kr = *reinterpret_cast<const uint32_t*>(static_cast<const uint8_t*>(p.k_cache) + off);
-                    const uint32_t vr = *reinterpret_cast<const uint32_t*>(static_cast<const uint8_t*>(p.v_cache) + off);
-                    const float ks = p.k_scale[int64_t(page) * p.n_kv_heads + head];
-                    const float vs = p.v_scale[int64_t(page) * p.n_kv_heads + head];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        __half_raw hk = __nv_cvt_fp8_to_halfraw((kr >> (8 * e)) & 0xff, __NV_E4M3);
-                        __half_raw hv = __nv_cvt_fp8_to_halfraw((vr >> (8 * e)) & 0xff, __NV_E4M3);
-                        kf[e] = __half2float(*reinterpret_cast<__half*>(&hk)) * ks;
-                        vf[e] = __half2float(*reinterpret_cast<__half*>(&hv)) * vs;
-                    }
-                } else {
-                    const uint2 kr = *reinterpret_cast<const uint2*>(static_cast<const uint8_t*>(p.k_cache) + off);
-                    const uint2 vr = *reinterpret_cast<const uint2*>(static_cast<const uint8_t*>(p.v_cache) + off);
-                    const __nv_bfloat162 k0 = *reinterpret_cast<const __nv_bfloat162*>(&kr.x);
-                    const __nv_bfloat162 k1 = *reinterpret_cast<const __nv_bfloat162*>(&kr.y);
-                    const __nv_bfloat162 v0 = *reinterpret_cast<const __nv_bfloat162*>(&vr.x);
-                    const __nv_bfloat162 v1 = *reinterpret_cast<const __nv_bfloat162*>(&vr.y);
-                    kf[0] = __low2float(k0); kf[1] = __high2float(k0); kf[2] = __low2float(k1); kf[3] = __high2float(k1);
-                    vf[0] = __low2float(v0); vf[1] = __high2float(v0); vf[2] = __low2float(v1); vf[3] = __high2float(v1);
-                }
-#pragma unroll
-                for (int j = 0; j < G; ++j) {
-                    float s = q[j][0] * kf[0] + q[j][1] * kf[1] + q[j][2] * kf[2] + q[j][3] * kf[3];
-#pragma unroll
-                    for (int d = 16; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
-                    s *= p.scale_log2;
-                    const float mn = fmaxf(m[j], s);
-                    const float alpha = exp2f(m[j] - mn);
-                    const float pr = exp2f(s - mn);
-                    l[j] = l[j] * alpha + pr;
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) o[j][e] = o[j][e] * alpha + pr * vf[e];
-                    m[j] = mn;
-                }
-            }
-        }
-        // merge the four warps
-        __syncthreads();
-#pragma unroll
-        for (int j = 0; j < G; ++j) {
-            if (lane == 0) { s_m[warp][j] = m[j]; s_l[warp][j] = l[j]; }
-#pragma unroll
-            for (int e = 0; e < 4; ++e) s_o[warp][j][lane * 4 + e] = o[j][e];
-        }
-        __syncthreads();
-        const bool complete = sg.t0 == 0 && sg.t1 == sg.ntiles;
-        const int slot = int(blockIdx.x) * 2 + (sg.t0 > 0 ? 0 : 1);
-        const int d = threadIdx.x;
-        for (int j = 0; j < G; ++j) {
-            float mm = fmaxf(fmaxf(s_m[0][j], s_m[1][j]), fmaxf(s_m[2][j], s_m[3][j]));
-            float ll = 0.f, oo = 0.f;
-#pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                const float a = s_m[w][j] == -INFINITY ? 0.f : exp2f(s_m[w][j] - mm);
-                ll += s_l[w][j] * a;
-                oo += s_o[w][j][d] * a;
-            }
-            if (complete) {
-                p.out[(int64_t(sg.b) * p.n_q_heads + head * G + j) * kHeadDim + d] = __float2bfloat16(oo / ll);
-            } else {
-                p.ws_o[(int64_t(slot) * G + j) * kHeadDim + d] = oo;
-                if (d == 0) {
-                    p.ws_ml[(int64_t(slot) * G + j) * 2 + 0] = mm;
-                    p.ws_ml[(int64_t(slot) * G + j) * 2 + 1] = ll;
-                }
-            }
-        }
-        g += sg.t1 - sg.t0;
-    }
-}
-
-// =========================================================================== reduce kernel
-// grid = batch * NG, 128 threads: warp w merges rows w, w + 4, ...; a lane owns 4 output dims.
-__global__ void __launch_bounds__(128) decode_reduce_kernel(DecodeParams p, int rows) {
-    pdl_launch_dependents();   // the next step's append may become resident; it waits for this grid itself
-    pdl_wait();
-    const int ng = p.n_kv_heads / p.hpc;
-    const int b = blockIdx.x / ng, hg = blockIdx.x - b * ng;
-    const int nt = p.prefix[b + 1] - p.prefix[b];
-    if (nt == 0) return;
-    const int chunk = p.header[2];
-    const int s = ng * p.prefix[b] + hg * nt, e = s + nt;
-    const int c0 = s / chunk, c1 = (e - 1) / chunk;
-    if (c0 == c1) return;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int r = warp; r < rows; r += 4) {
+    for (int r = warp; r < rows; r += kConsumerWarps) {
         float mm = -INFINITY;
         for (int c = c0; c <= c1; ++c) {
             const int slot = c * 2 + (c == c0 ? 1 : 0);
-            mm = fmaxf(mm, p.ws_ml[(int64_t(slot) * rows + r) * 2]);
+            mm = fmaxf(mm, __ldcg(p.ws_ml + (int64_t(slot) * rows + r) * 2));
         }
         float ll = 0.f;
         float4 oo = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int c = c0; c <= c1; ++c) {
             const int slot = c * 2 + (c == c0 ? 1 : 0);
-            const float2 ml = *reinterpret_cast<const float2*>(p.ws_ml + (int64_t(slot) * rows + r) * 2);
+            const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.ws_ml + (int64_t(slot) * rows + r) * 2));
             const float a = ml.x == -INFINITY ? 0.f : exp2f(ml.x - mm);
-            const float4 o = *reinterpret_cast<const float4*>(p.ws_o + (int64_t(slot) * rows + r) * kHeadDim + lane * 4);
+            const float4 o = __ldcg(reinterpret_cast<const float4*>(p.ws_o + (int64_t(slot) * rows + r) * kHeadDim + lane * 4));
             ll += ml.y * a;
             oo.x += o.x * a; oo.y += o.y * a; oo.z += o.z * a; oo.w += o.w * a;
         }
@@ -179,16 +67,11 @@ __global__ void __launch_bounds__(128) decode_reduce_kernel(DecodeParams p, int 
         uint2 packed;
         packed.x = pack_bf16(oo.x * inv, oo.y * inv);
         packed.y = pack_bf16(oo.z * inv, oo.w * inv);
-        *reinterpret_cast<uint2*>(p.out + (int64_t(b) * p.n_q_heads + hg * rows + r) * kHeadDim + lane * 4) = packed;
+        *reinterpret_cast<uint2*>(p.out + (int64_t(sg.b) * p.n_q_heads + sg.hg * rows + r) * kHeadDim + lane * 4) = packed;
     }
 }
 
 // =========================================================================== TMA kernel
-constexpr int kStages = 3;
-constexpr int kTileBytes = 32768;                 // K (or V) bytes per stage: 128 rows x 256 B
-constexpr int kConsumerWarps = 8;
-constexpr int kTmaThreads = (kConsumerWarps + 1) * 32;
-constexpr int kMergeSlotFloats = 36 * 32;         // 32 accumulators + up to two maxima and two sums per lane
 
 struct TmaSmem {
     // dynamic shared memory, 1024-byte aligned base:
@@ -215,6 +98,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_kernel(DecodeParams
     float* s_merge = reinterpret_cast<float*>(smem + TmaSmem::merge);
     int* s_tp = reinterpret_cast<int*>(smem + TmaSmem::prefix);
     int* s_scan = reinterpret_cast<int*>(smem + TmaSmem::scan);
+    volatile int* s_flag = s_scan + 32;             // "this CTA drew the last ticket" (the scan only uses 32 words)
     uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + TmaSmem::bars);
     const uint32_t tiles_u32 = smem_u32(smem);
     const uint32_t full0 = smem_u32(s_bar), empty0 = full0 + kStages * 8;
@@ -237,14 +121,6 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_kernel(DecodeParams
     const int ng = p.n_kv_heads / HPC;
     const int total = ng * s_tp[p.batch];
     const int chunk = max(1, (total + int(gridDim.x) - 1) / int(gridDim.x));
-    if (blockIdx.x == 0) {
-        for (int i = threadIdx.x; i <= p.batch; i += blockDim.x) p.prefix[i] = s_tp[i];
-        if (threadIdx.x == 0) {
-            p.header[1] = total;
-            p.header[2] = chunk;
-            p.header[3] = gridDim.x;
-        }
-    }
     const int lo = min(total, int(blockIdx.x) * chunk), hi = min(total, lo + chunk);
 
     if (warp == kConsumerWarps) {
@@ -259,12 +135,13 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_kernel(DecodeParams
             const int32_t* table = p.block_tables + int64_t(sg.b) * p.bt_stride;
             for (int t = sg.t0; t < sg.t1; ++t, ++it) {
                 const uint32_t s = it % kStages, ph = (it / kStages) & 1;
-                if (!mbar_wait(empty0 + s * 8, ph ^ 1)) { ok = false; break; }
+                if (!mbar_wait(empty0 + s * 8, ph ^ 1, p.wait_limit)) { ok = false; break; }
                 const int tok0 = t * TT;
                 const int page = table[tok0 / p.block_size];
                 const int slot0 = page * p.block_size + tok0 % p.block_size;
                 const uint32_t bar = full0 + s * 8;
                 const uint32_t kdst = tiles_u32 + s * (2 * kTileBytes), vdst = kdst + kTileBytes;
+                if (p.stall_producer) continue;          // self-test: nothing is armed, every wait on this stage runs out
                 mbar_expect_tx(bar, 2 * kTileBytes);
 #pragma unroll
                 for (int hl = 0; hl < HPC; ++hl) {
@@ -279,12 +156,12 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_kernel(DecodeParams
             g += sg.t1 - sg.t0;
         }
         // Do not leave while a copy may still be in flight: wait for the last armed stages.
-        const uint32_t armed = it < uint32_t(kStages) ? it : uint32_t(kStages);
+        const uint32_t armed = p.stall_producer ? 0u : (it < uint32_t(kStages) ? it : uint32_t(kStages));
         for (uint32_t j = 0; j < armed; ++j) {
             const uint32_t i2 = it - 1 - j;
-            if (!mbar_wait(full0 + (i2 % kStages) * 8, (i2 / kStages) & 1)) ok = false;
+            if (!mbar_wait(full0 + (i2 % kStages) * 8, (i2 / kStages) & 1, p.wait_limit)) ok = false;
         }
-        if (!ok) atomicExch(p.header, kStatusMagic | 1);
+        if (!ok) atomicExch(p.status, kStatusMagic | 1);
         return;
     }
 
@@ -319,7 +196,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_kernel(DecodeParams
 
         for (int t = sg.t0; t < sg.t1; ++t, ++it) {
             const uint32_t s = it % kStages, ph = (it / kStages) & 1;
-            if (ok && !mbar_wait(full0 + s * 8, ph)) ok = false;
+            if (ok && !mbar_wait(full0 + s * 8, ph, p.wait_limit)) ok = false;
             const int tok_w = t * TT + tw * 16;            // first token of this warp's 16
             const int valid = ctx - tok_w;                  // tokens of the 16 that exist
             if (ok && valid > 0) {
@@ -433,11 +310,13 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_kernel(DecodeParams
                     p.ws_ml[(slot * rows + r) * 2 + 0] = m_run;
                     p.ws_ml[(slot * rows + r) * 2 + 1] = l_run;
                 }
+                __threadfence();
             }
         }
+        if (!(sg.t0 == 0 && sg.t1 == sg.ntiles)) merge_if_last(p, s_tp, ng, sg, chunk, HPC * p.group, s_flag);
         g += sg.t1 - sg.t0;
     }
-    if (!ok && lane == 0) atomicExch(p.header, kStatusMagic | 2);
+    if (!ok && lane == 0) atomicExch(p.status, kStatusMagic | 2);
 }
 
 // =========================================================================== TMA kernel, e4m3 pools
@@ -487,6 +366,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_fp8_kernel(DecodePa
     float* s_merge = reinterpret_cast<float*>(smem + L::merge);
     int* s_tp = reinterpret_cast<int*>(smem + L::prefix);
     int* s_scan = reinterpret_cast<int*>(smem + L::scan);
+    volatile int* s_flag = s_scan + 32;             // "this CTA drew the last ticket" (the scan only uses 32 words)
     uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + L::bars);
     volatile float* s_meta = reinterpret_cast<volatile float*>(smem + L::meta);
     const uint32_t tiles_u32 = smem_u32(smem);
@@ -508,14 +388,6 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_fp8_kernel(DecodePa
     const int ng = p.n_kv_heads / HPC;
     const int total = ng * s_tp[p.batch];
     const int chunk = max(1, (total + int(gridDim.x) - 1) / int(gridDim.x));
-    if (blockIdx.x == 0) {
-        for (int i = threadIdx.x; i <= p.batch; i += blockDim.x) p.prefix[i] = s_tp[i];
-        if (threadIdx.x == 0) {
-            p.header[1] = total;
-            p.header[2] = chunk;
-            p.header[3] = gridDim.x;
-        }
-    }
     const int lo = min(total, int(blockIdx.x) * chunk), hi = min(total, lo + chunk);
 
     if (warp == W) {
@@ -540,7 +412,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_fp8_kernel(DecodePa
                     ks[hl] = page_ok ? p.k_scale[int64_t(page) * p.n_kv_heads + sg.hg * HPC + hl] : 0.f;
                     vs[hl] = page_ok ? p.v_scale[int64_t(page) * p.n_kv_heads + sg.hg * HPC + hl] : 0.f;
                 }
-                if (!mbar_wait(empty0 + s * 8, ph ^ 1)) { ok = false; break; }
+                if (!mbar_wait(empty0 + s * 8, ph ^ 1, p.wait_limit)) { ok = false; break; }
 #pragma unroll
                 for (int hl = 0; hl < HPC; ++hl) {
                     s_meta[(s * HPC + hl) * 2 + 0] = ks[hl];
@@ -548,6 +420,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_fp8_kernel(DecodePa
                 }
                 const uint32_t bar = full0 + s * 8;
                 const uint32_t kdst = tiles_u32 + s * (2 * kTileBytes), vdst = kdst + kTileBytes;
+                if (p.stall_producer) continue;          // self-test: nothing is armed, every wait on this stage runs out
                 mbar_expect_tx(bar, 2 * kTileBytes);      // release: the scales above are visible to the waiters
 #pragma unroll
                 for (int hl = 0; hl < HPC; ++hl) {        // the heads' boxes back to back: adjacent lines of every token row
@@ -557,12 +430,12 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_fp8_kernel(DecodePa
             }
             g += sg.t1 - sg.t0;
         }
-        const uint32_t armed = it < uint32_t(kStages) ? it : uint32_t(kStages);
+        const uint32_t armed = p.stall_producer ? 0u : (it < uint32_t(kStages) ? it : uint32_t(kStages));
         for (uint32_t j = 0; j < armed; ++j) {
             const uint32_t i2 = it - 1 - j;
-            if (!mbar_wait(full0 + (i2 % kStages) * 8, (i2 / kStages) & 1)) ok = false;
+            if (!mbar_wait(full0 + (i2 % kStages) * 8, (i2 / kStages) & 1, p.wait_limit)) ok = false;
         }
-        if (!ok) atomicExch(p.header, kStatusMagic | 1);
+        if (!ok) atomicExch(p.status, kStatusMagic | 1);
         return;
     }
 
@@ -608,7 +481,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_fp8_kernel(DecodePa
 
         for (int t = sg.t0; t < sg.t1; ++t, ++it) {
             const uint32_t s = it % kStages, ph = (it / kStages) & 1;
-            if (ok && !mbar_wait(full0 + s * 8, ph)) ok = false;
+            if (ok && !mbar_wait(full0 + s * 8, ph, p.wait_limit)) ok = false;
             const float c_k = s_meta[(s * HPC + hl) * 2 + 0] * p.scale_log2;
             const float vs = s_meta[(s * HPC + hl) * 2 + 1];
             const int row0 = tw * TPW;                      // this warp's tokens of the tile
@@ -789,112 +662,102 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_fp8_kernel(DecodePa
                         p.ws_ml[(slot * rows + r) * 2 + 0] = m_run[y];
                         p.ws_ml[(slot * rows + r) * 2 + 1] = l_run[y];
                     }
+                    __threadfence();
                 }
             }
         }
+        if (!(sg.t0 == 0 && sg.t1 == sg.ntiles)) merge_if_last(p, s_tp, ng, sg, chunk, HPC * p.group, s_flag);
         g += sg.t1 - sg.t0;
     }
-    if (!ok && lane == 0) atomicExch(p.header, kStatusMagic | 2);
+    if (!ok && lane == 0) atomicExch(p.status, kStatusMagic | 2);
 }
 
 // =========================================================================== host side
 struct DecodeConfig {
-    int impl;   // 1 = simple, 2 = tma
-    int hpc;
-    int tile_tokens;
+    int hpc;          // kv heads per tile
     int grid;
-    int rows;   // partial rows per scratch slot
+    int rows;         // partial rows per scratch slot
 };
 
-static void set_cuda_error_if(cudaError_t e) {
-    if (e != cudaSuccess) set_cuda_error(e);
-}
-
-static int env_int(const char* name, int dflt) {
-    const char* s = std::getenv(name);
-    return s && *s ? std::atoi(s) : dflt;
-}
-
+// force_hpc: 0 = the measured default, else heads per tile (self-test entry point only).
 // ws_limit: bytes of scratch the caller has (0 = no limit); the e4m3 kernel takes fewer heads per tile
 // when the partial-result slots of more would not fit.
-static DecodeConfig decode_config(const infer_kv_pool* pool, int n_q_heads, size_t ws_limit = 0) {
+static DecodeConfig decode_config(const infer_kv_pool* pool, int n_q_heads, size_t ws_limit, int force_hpc) {
     DecodeConfig c;
     const int group = n_q_heads / pool->n_kv_heads;
-    c.impl = 2;
-    const int forced = env_int("INFER_B200_DECODE_IMPL", 0);   // development switch: 1 = plain-load kernel
-    if (forced == 1 || forced == 2) c.impl = forced;
-    if (c.impl == 2 && pool->dtype == INFER_KV_E4M3) {
+    const bool forced = (force_hpc == 1 || force_hpc == 2 || force_hpc == 4 || force_hpc == 8) &&
+                        pool->n_kv_heads % force_hpc == 0;
+    if (pool->dtype == INFER_KV_E4M3) {
         // several adjacent heads per tile when the head count allows: their boxes fetch neighbouring lines
         // (measured on 8 heads: 1 head 111 us, 2 heads 98.7, 4 heads 96.5, 8 heads 105)
         c.hpc = pool->n_kv_heads % 4 == 0 ? 4 : (pool->n_kv_heads % 2 == 0 ? 2 : 1);
-        const int want8 = env_int("INFER_B200_FP8_HPC", 0);         // development switch
-        if ((want8 == 1 || want8 == 2 || want8 == 4 || want8 == 8) && pool->n_kv_heads % want8 == 0) c.hpc = want8;
+        if (forced) c.hpc = force_hpc;
         while (ws_limit && c.hpc > 1 && decode_layout(pool->sm_count, c.hpc * group).total > ws_limit) c.hpc /= 2;
-        c.tile_tokens = kFp8TileTokens / c.hpc;
-        c.grid = pool->sm_count;
-    } else if (c.impl == 2) {
+    } else {
         // One kv head per tile (128 tokens x 256 B rows) measured fastest at every head count:
         // fewer, larger TMA boxes beat streaming all heads of a token row together.
-        int hpc = 1;
-        const int want = env_int("INFER_B200_DECODE_HPC", 0);
-        if ((want == 1 || want == 2 || want == 4 || want == 8) && pool->n_kv_heads % want == 0) hpc = want;
-        c.hpc = hpc;
-        c.tile_tokens = 128 / hpc;
-        c.grid = pool->sm_count;
-    } else {
-        c.hpc = 1;
-        c.tile_tokens = 64;
-        c.grid = pool->sm_count * 8;
+        c.hpc = forced ? force_hpc : 1;
     }
+    c.grid = pool->sm_count < kMaxDecodeGrid ? pool->sm_count : kMaxDecodeGrid;
     c.rows = c.hpc * group;
     return c;
 }
 
-template <int G, bool FP8>
-static void launch_simple(const DecodeParams& p, int grid, cudaStream_t st) {
-    set_cuda_error_if(launch_pdl(decode_simple_kernel<G, FP8>, dim3(grid), dim3(128), 0, st, p));
-}
-
 template <int HPC>
-static int launch_tma(const DecodeParams& p, const infer_kv_pool* pool, int grid, cudaStream_t st) {
+static int launch_bf16(const DecodeParams& p, const infer_kv_pool* pool, int grid, cudaStream_t st) {
     int idx = 0;
     while ((16 << idx) != 128 / HPC) ++idx;
-    const int smem = TmaSmem::total + 1024;
-    IB_CUDA(cudaFuncSetAttribute(decode_tma_kernel<HPC>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    IB_CUDA(launch_pdl(decode_tma_kernel<HPC>, dim3(grid), dim3(kTmaThreads), smem, st, p, pool->maps[idx].k,
-                       pool->maps[idx].v));
+    IB_CUDA(launch_pdl(decode_tma_kernel<HPC>, dim3(grid), dim3(kTmaThreads), TmaSmem::total + 1024, st, p,
+                       pool->maps[idx].k, pool->maps[idx].v));
     return INFER_OK;
 }
 
-}  // namespace ib
-
-extern "C" {
-
-size_t infer_paged_decode_workspace_bytes(const infer_kv_pool_t* pool, int batch, int n_q_heads) {
-    (void)batch;
-    if (!pool || n_q_heads <= 0 || n_q_heads % pool->n_kv_heads != 0) return 0;
-    // sized for either kernel so that a development switch never outgrows the buffer
-    const int group = n_q_heads / pool->n_kv_heads;
-    const size_t a = ib::decode_layout(pool->sm_count, 8 * group).total;
-    const size_t b = ib::decode_layout(pool->sm_count * 8, group).total;
-    return a > b ? a : b;
+template <int HPC>
+static int launch_fp8(const DecodeParams& p, const infer_kv_pool* pool, int grid, cudaStream_t st) {
+    int idx = 0;
+    while ((16 << idx) != kFp8TileTokens / HPC) ++idx;
+    IB_CUDA(launch_pdl(decode_tma_fp8_kernel<HPC>, dim3(grid), dim3(kTmaThreads), Fp8Smem<HPC>::total + 1024, st, p,
+                       pool->maps[idx].k, pool->maps[idx].v));
+    return INFER_OK;
 }
 
-int infer_paged_decode(const infer_kv_pool_t* pool, void* out, const void* q, const int32_t* context_lens,
-                       const int32_t* block_tables, int64_t bt_stride, int batch, int n_q_heads,
-                       float softmax_scale, void* workspace, size_t workspace_bytes, void* stream_) {
-    using namespace ib;
+template <int HPC>
+static cudaError_t allow_smem() {
+    cudaError_t e = cudaFuncSetAttribute(decode_tma_kernel<HPC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         TmaSmem::total + 1024);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(decode_tma_fp8_kernel<HPC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                Fp8Smem<HPC>::total + 1024);
+}
+
+// Raises the dynamic shared-memory limit of every decode kernel on the current device.  Called once
+// per pool creation so that the per-step entry points make no call but the launches.
+int decode_prepare_device() {
+    cudaError_t e = allow_smem<1>();
+    if (e == cudaSuccess) e = allow_smem<2>();
+    if (e == cudaSuccess) e = allow_smem<4>();
+    if (e == cudaSuccess) e = allow_smem<8>();
+    if (e != cudaSuccess) {
+        set_cuda_error(e);
+        return INFER_ERR_CUDA;
+    }
+    return INFER_OK;
+}
+
+static int paged_decode(const infer_kv_pool_t* pool, void* out, const void* q, const int32_t* context_lens,
+                        const int32_t* block_tables, int64_t bt_stride, int batch, int n_q_heads, float softmax_scale,
+                        void* workspace, size_t workspace_bytes, cudaStream_t st, int force_hpc, uint32_t wait_limit,
+                        int stall_producer) {
     if (!pool || !out || !q || !context_lens || !block_tables) return INFER_ERR_NULL;
     if (batch < 0 || batch > kMaxBatch || n_q_heads <= 0 || n_q_heads % pool->n_kv_heads != 0 || bt_stride <= 0)
         return INFER_ERR_GEOMETRY;
     const int group = n_q_heads / pool->n_kv_heads;
-    if (group > kMaxGroup || (group & (group - 1)) != 0) return INFER_ERR_GEOMETRY;
+    if (group > kMaxGroup) return INFER_ERR_GEOMETRY;
     if (!aligned16(out) || !aligned16(q)) return INFER_ERR_ALIGN;
     if (batch == 0) return INFER_OK;
-    const DecodeConfig cfg = decode_config(pool, n_q_heads, workspace_bytes);
+    const DecodeConfig cfg = decode_config(pool, n_q_heads, workspace_bytes, force_hpc);
     const DecodeLayout lay = decode_layout(cfg.grid, cfg.rows);
     if (!workspace || !aligned16(workspace) || workspace_bytes < lay.total) return INFER_ERR_WORKSPACE;
-    cudaStream_t st = static_cast<cudaStream_t>(stream_);
 
     DecodeParams p;
     p.q = static_cast<const __nv_bfloat16*>(q);
@@ -912,78 +775,35 @@ int infer_paged_decode(const infer_kv_pool_t* pool, void* out, const void* q, co
     p.group = group;
     p.block_size = pool->block_size;
     p.num_blocks = int(pool->num_blocks);
-    p.hpc = cfg.hpc;
-    p.tile_tokens = cfg.tile_tokens;
     p.scale_log2 = softmax_scale * 1.4426950408889634f;
+    p.wait_limit = wait_limit;
+    p.stall_producer = stall_producer;
     uint8_t* ws = static_cast<uint8_t*>(workspace);
-    p.header = reinterpret_cast<int*>(ws + lay.header_off);
-    p.prefix = reinterpret_cast<int*>(ws + lay.prefix_off);
+    p.status = reinterpret_cast<int*>(ws + lay.status_off);
+    p.counters = reinterpret_cast<int*>(ws + lay.counters_off);
     p.ws_ml = reinterpret_cast<float*>(ws + lay.ml_off);
     p.ws_o = reinterpret_cast<float*>(ws + lay.o_off);
 
-    if (cfg.impl == 2 && pool->dtype == INFER_KV_E4M3) {
-        if (cfg.hpc == 8 || cfg.hpc == 4) {
-            const int mi = cfg.hpc == 8 ? 1 : 2;
-            if (cfg.hpc == 8) {
-                const int smem_t = Fp8Smem<8>::total + 1024;
-                IB_CUDA(cudaFuncSetAttribute(decode_tma_fp8_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_t));
-                IB_CUDA(launch_pdl(decode_tma_fp8_kernel<8>, dim3(cfg.grid), dim3(kTmaThreads), smem_t, st, p, pool->maps[mi].k,
-                                   pool->maps[mi].v));
-            } else {
-                const int smem_t = Fp8Smem<4>::total + 1024;
-                IB_CUDA(cudaFuncSetAttribute(decode_tma_fp8_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_t));
-                IB_CUDA(launch_pdl(decode_tma_fp8_kernel<4>, dim3(cfg.grid), dim3(kTmaThreads), smem_t, st, p, pool->maps[mi].k,
-                                   pool->maps[mi].v));
-            }
-        } else if (cfg.hpc == 2) {
-            const int smem_t = Fp8Smem<2>::total + 1024;
-            IB_CUDA(cudaFuncSetAttribute(decode_tma_fp8_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_t));
-            IB_CUDA(launch_pdl(decode_tma_fp8_kernel<2>, dim3(cfg.grid), dim3(kTmaThreads), smem_t, st, p, pool->maps[3].k,
-                               pool->maps[3].v));
-        } else {
-            const int smem_t = Fp8Smem<1>::total + 1024;
-            IB_CUDA(cudaFuncSetAttribute(decode_tma_fp8_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_t));
-            IB_CUDA(launch_pdl(decode_tma_fp8_kernel<1>, dim3(cfg.grid), dim3(kTmaThreads), smem_t, st, p, pool->maps[4].k,
-                               pool->maps[4].v));
-        }
-    } else if (cfg.impl == 2) {
-        int rc = INFER_OK;
+    int rc;
+    if (pool->dtype == INFER_KV_E4M3) {
         switch (cfg.hpc) {
-            case 1: rc = launch_tma<1>(p, pool, cfg.grid, st); break;
-            case 2: rc = launch_tma<2>(p, pool, cfg.grid, st); break;
-            case 4: rc = launch_tma<4>(p, pool, cfg.grid, st); break;
-            default: rc = launch_tma<8>(p, pool, cfg.grid, st); break;
+            case 1: rc = launch_fp8<1>(p, pool, cfg.grid, st); break;
+            case 2: rc = launch_fp8<2>(p, pool, cfg.grid, st); break;
+            case 4: rc = launch_fp8<4>(p, pool, cfg.grid, st); break;
+            default: rc = launch_fp8<8>(p, pool, cfg.grid, st); break;
         }
-        if (rc != INFER_OK) return rc;
     } else {
-        const bool fp8 = pool->dtype == INFER_KV_E4M3;
-#define IB_SIMPLE(G) (fp8 ? launch_simple<G, true>(p, cfg.grid, st) : launch_simple<G, false>(p, cfg.grid, st))
-        switch (group) {
-            case 1: IB_SIMPLE(1); break;
-            case 2: IB_SIMPLE(2); break;
-            case 4: IB_SIMPLE(4); break;
-            default: IB_SIMPLE(8); break;
+        switch (cfg.hpc) {
+            case 1: rc = launch_bf16<1>(p, pool, cfg.grid, st); break;
+            case 2: rc = launch_bf16<2>(p, pool, cfg.grid, st); break;
+            case 4: rc = launch_bf16<4>(p, pool, cfg.grid, st); break;
+            default: rc = launch_bf16<8>(p, pool, cfg.grid, st); break;
         }
-#undef IB_SIMPLE
     }
-    int rc = check_launch();
-    if (rc != INFER_OK) return rc;
-    IB_CUDA(launch_pdl(decode_reduce_kernel, dim3(batch * (pool->n_kv_heads / cfg.hpc)), dim3(128), 0, st, p, cfg.rows));
-    return check_launch();
-}
-
-int infer_paged_decode_status(const void* workspace, void* stream_) {
-    if (!workspace) return INFER_ERR_NULL;
-    int word = 0;
-    cudaStream_t st = static_cast<cudaStream_t>(stream_);
-    IB_CUDA(cudaMemcpyAsync(&word, workspace, sizeof(int), cudaMemcpyDeviceToHost, st));
-    IB_CUDA(cudaStreamSynchronize(st));
-    return (word & 0xFFFF0000) == ib::kStatusMagic ? INFER_ERR_DEVICE : INFER_OK;
+    return rc != INFER_OK ? rc : check_launch();
 }
 
 // ------------------------------------------------------------------ entry point without scratch
-namespace ib {
-
 // Scratch of infer_paged_decode_noalloc: lives in the library's device image, one copy per
 // GPU that loads the library.  In host code the NAME below is only a handle for
 // cudaGetSymbolAddress; kernels must be given the address that call returns.
@@ -994,7 +814,72 @@ constexpr int kMaxDevices = 64;
 static void* g_builtin_scratch_addr[kMaxDevices];   // device address per device ordinal, 0 = not looked up yet
 static std::mutex g_builtin_scratch_mutex;
 
+// Device address of the built-in array on the current device (looked up once per device); dev_out
+// receives the device ordinal.
+static int builtin_scratch(void** addr_out, int* dev_out) {
+    int dev = -1;
+    IB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) {
+        set_cuda_error(cudaErrorInvalidDevice);
+        return INFER_ERR_CUDA;
+    }
+    std::lock_guard<std::mutex> lock(g_builtin_scratch_mutex);
+    if (!g_builtin_scratch_addr[dev]) {
+        void* addr = nullptr;
+        IB_CUDA(cudaGetSymbolAddress(&addr, g_builtin_scratch));
+        g_builtin_scratch_addr[dev] = addr;
+    }
+    *addr_out = g_builtin_scratch_addr[dev];
+    *dev_out = dev;
+    return INFER_OK;
+}
+
 }  // namespace ib
+
+extern "C" {
+
+size_t infer_paged_decode_workspace_bytes(const infer_kv_pool_t* pool, int batch, int n_q_heads) {
+    (void)batch;
+    if (!pool || n_q_heads <= 0 || n_q_heads % pool->n_kv_heads != 0) return 0;
+    // sized for the widest tile (eight kv heads' partial rows per slot) so that no tile shape outgrows it
+    const int group = n_q_heads / pool->n_kv_heads;
+    const int grid = pool->sm_count < ib::kMaxDecodeGrid ? pool->sm_count : ib::kMaxDecodeGrid;
+    return ib::decode_layout(grid, 8 * group).total;
+}
+
+int infer_paged_decode(const infer_kv_pool_t* pool, void* out, const void* q, const int32_t* context_lens,
+                       const int32_t* block_tables, int64_t bt_stride, int batch, int n_q_heads,
+                       float softmax_scale, void* workspace, size_t workspace_bytes, void* stream_) {
+    return ib::paged_decode(pool, out, q, context_lens, block_tables, bt_stride, batch, n_q_heads, softmax_scale,
+                            workspace, workspace_bytes, static_cast<cudaStream_t>(stream_), 0, ib::kDefaultWaitLimit, 0);
+}
+
+int infer_selftest_paged_decode(const infer_kv_pool_t* pool, void* out, const void* q, const int32_t* context_lens,
+                                const int32_t* block_tables, int64_t bt_stride, int batch, int n_q_heads,
+                                float softmax_scale, void* workspace, size_t workspace_bytes, void* stream_,
+                                int heads_per_tile, uint32_t wait_limit, int stall_producer) {
+    return ib::paged_decode(pool, out, q, context_lens, block_tables, bt_stride, batch, n_q_heads, softmax_scale,
+                            workspace, workspace_bytes, static_cast<cudaStream_t>(stream_), heads_per_tile,
+                            wait_limit ? wait_limit : ib::kDefaultWaitLimit, stall_producer);
+}
+
+int infer_paged_decode_status(const void* workspace, void* stream_) {
+    using namespace ib;
+    void* ws = const_cast<void*>(workspace);
+    if (!ws) {                       // the built-in array of infer_paged_decode_noalloc on the current device
+        int dev = -1;
+        const int rc = builtin_scratch(&ws, &dev);
+        if (rc != INFER_OK) return rc;
+    }
+    int word = 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream_);
+    IB_CUDA(cudaMemcpyAsync(&word, ws, sizeof(int), cudaMemcpyDeviceToHost, st));
+    IB_CUDA(cudaStreamSynchronize(st));
+    if ((word & 0xFFFF0000) != kStatusMagic) return INFER_OK;
+    // a launch that gave up may have left tickets behind: clear the word and the counters
+    IB_CUDA(cudaMemsetAsync(ws, 0, decode_layout(1, 1).ml_off, st));
+    return INFER_ERR_DEVICE;
+}
 
 int infer_paged_decode_noalloc(const infer_kv_pool_t* pool, void* out, const void* q, const int32_t* context_lens,
                                const int32_t* block_tables, int64_t bt_stride, int batch, int n_q_heads,
@@ -1003,28 +888,20 @@ int infer_paged_decode_noalloc(const infer_kv_pool_t* pool, void* out, const voi
     if (!pool || !out || !q || !context_lens || !block_tables) return INFER_ERR_NULL;
     if (n_q_heads <= 0 || n_q_heads % pool->n_kv_heads != 0 || batch < 0) return INFER_ERR_GEOMETRY;
     if (batch > kMaxBatch) return INFER_ERR_TOO_LARGE;
-    const DecodeConfig cfg = decode_config(pool, n_q_heads, kBuiltinScratchBytes);
-    if (decode_layout(cfg.grid, cfg.rows).total > kBuiltinScratchBytes) return INFER_ERR_TOO_LARGE;
+    const DecodeConfig cfg = decode_config(pool, n_q_heads, kBuiltinScratchBytes, 0);
+    const DecodeLayout lay = decode_layout(cfg.grid, cfg.rows);
+    if (lay.total > kBuiltinScratchBytes) return INFER_ERR_TOO_LARGE;
 
+    void* scratch = nullptr;
     int dev = -1;
-    IB_CUDA(cudaGetDevice(&dev));
-    if (dev != pool->device || dev < 0 || dev >= kMaxDevices) {
+    const int rc = builtin_scratch(&scratch, &dev);   // once per device, with that device current
+    if (rc != INFER_OK) return rc;
+    if (dev != pool->device) {
         set_cuda_error(cudaErrorInvalidDevice);
         return INFER_ERR_CUDA;
     }
-    void* scratch = nullptr;
-    {
-        // once per device, with that device current: resolve the array's device address
-        std::lock_guard<std::mutex> lock(g_builtin_scratch_mutex);
-        if (!g_builtin_scratch_addr[dev]) {
-            void* addr = nullptr;
-            IB_CUDA(cudaGetSymbolAddress(&addr, g_builtin_scratch));
-            g_builtin_scratch_addr[dev] = addr;
-        }
-        scratch = g_builtin_scratch_addr[dev];
-    }
-    // the array keeps the previous call's bytes: the status word has to start at zero
-    IB_CUDA(cudaMemsetAsync(scratch, 0, 64, static_cast<cudaStream_t>(stream_)));
+    // the array keeps the previous call's bytes: the status word and the ticket counters have to start at zero
+    IB_CUDA(cudaMemsetAsync(scratch, 0, lay.ml_off, static_cast<cudaStream_t>(stream_)));
     return infer_paged_decode(pool, out, q, context_lens, block_tables, bt_stride, batch, n_q_heads, softmax_scale,
                               scratch, kBuiltinScratchBytes, stream_);
 }

@@ -1,4 +1,4 @@
-// Work decomposition shared by the paged decode kernels and their reduce kernel.
+// Work decomposition shared by the paged decode kernels.
 //
 // A "tile" is TT consecutive tokens of one sequence for one group of HPC kv heads.  Tiles
 // are numbered sequence by sequence, head group by head group:
@@ -9,16 +9,18 @@
 // boundaries.  A segment that covers its whole (b, hg) writes the output row directly;
 // otherwise it leaves an un-normalised partial (running max, sum, accumulator) in one of
 // the CTA's two scratch slots: slot 0 when the segment continues a (b, hg) begun by an
-// earlier CTA, slot 1 when it begins one that a later CTA continues.  The reduce kernel
-// merges, for every (b, hg) that spans several CTAs, slot 1 of the first CTA with slot 0
-// of the following ones.
+// earlier CTA, slot 1 when it begins one that a later CTA continues.  Every CTA that leaves
+// a partial then takes a ticket from the counter of that (b, hg) (indexed by the first CTA
+// of its span); the CTA that draws the last ticket merges slot 1 of the first CTA with slot
+// 0 of the following ones and writes the output rows.  No CTA waits for another.
 #pragma once
 
 #include "common.cuh"
 
 namespace ib {
 
-constexpr int kStatusMagic = 0x5AFE0000;   // header[0] == magic | code after a bounded wait ran out
+constexpr int kStatusMagic = 0x5AFE0000;   // status word == magic | code after a bounded wait ran out
+constexpr int kMaxDecodeGrid = 1024;       // ticket counters in the scratch header
 
 struct DecodeParams {
     const __nv_bfloat16* q;
@@ -36,25 +38,28 @@ struct DecodeParams {
     int group;        // query heads per kv head
     int block_size;
     int num_blocks;
-    int hpc;          // kv heads per tile
-    int tile_tokens;  // TT
     float scale_log2; // softmax_scale * log2(e)
+    uint32_t wait_limit;   // polls before a barrier wait gives up
+    int stall_producer;    // self-test only: the producer arms no copy, so every wait runs out
     // scratch
-    int* header;      // [0] status, [1] total tiles, [2] chunk, [3] grid
-    int* prefix;      // [batch + 1] tiles before each sequence
+    int* status;      // one word
+    int* counters;    // [kMaxDecodeGrid] tickets, zero between launches
     float* ws_ml;     // [grid * 2][rows][2]
     float* ws_o;      // [grid * 2][rows][128]
 };
 
+// Scratch layout: 64-byte header (status word), ticket counters, partial maxima/sums, partial
+// accumulators.  Everything up to ml_off must be zero when a launch starts; a launch that ends
+// normally leaves it zero.
 struct DecodeLayout {
-    size_t header_off, prefix_off, ml_off, o_off, total;
+    size_t status_off, counters_off, ml_off, o_off, total;
 };
 
 inline DecodeLayout decode_layout(int grid, int rows) {
     DecodeLayout l;
-    l.header_off = 0;
-    l.prefix_off = 64;
-    l.ml_off = (l.prefix_off + size_t(kMaxBatch + 1) * 4 + 255) / 256 * 256;
+    l.status_off = 0;
+    l.counters_off = 64;
+    l.ml_off = (l.counters_off + size_t(kMaxDecodeGrid) * 4 + 255) / 256 * 256;
     l.o_off = (l.ml_off + size_t(grid) * 2 * rows * 2 * 4 + 255) / 256 * 256;
     l.total = l.o_off + size_t(grid) * 2 * rows * kHeadDim * 4;
     return l;
@@ -63,29 +68,30 @@ inline DecodeLayout decode_layout(int grid, int rows) {
 #ifdef __CUDACC__
 
 // Exclusive prefix of tiles per sequence into shared memory (s_tp[batch] = total).
-// Every thread of the CTA must call it; ends with a __syncthreads().
+// Every thread of the CTA must call it (blockDim.x a multiple of 32, at most 1024); ends with
+// a __syncthreads().  Warp-shuffle scan, then the warp totals through shared memory.
 __device__ inline void build_tile_prefix(const int32_t* __restrict__ context_lens, int batch, int tile_tokens,
-                                         int* s_tp, int* s_scratch /* blockDim.x ints */) {
-    const int nt = blockDim.x, tid = threadIdx.x;
+                                         int* s_tp, int* s_scratch /* 32 ints */) {
+    const int nt = blockDim.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int per = (batch + nt - 1) / nt;
     const int lo = min(batch, tid * per), hi = min(batch, lo + per);
     int sum = 0;
     for (int i = lo; i < hi; ++i) sum += (max(context_lens[i], 0) + tile_tokens - 1) / tile_tokens;
-    s_scratch[tid] = sum;
-    __syncthreads();
-    // Hillis-Steele inclusive scan over nt values
-    for (int off = 1; off < nt; off <<= 1) {
-        int v = tid >= off ? s_scratch[tid - off] : 0;
-        __syncthreads();
-        s_scratch[tid] += v;
-        __syncthreads();
+    int incl = sum;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += v;
     }
-    int run = s_scratch[tid] - sum;
+    if (lane == 31) s_scratch[warp] = incl;
+    __syncthreads();
+    int run = incl - sum;
+    for (int w = 0; w < warp; ++w) run += s_scratch[w];
     for (int i = lo; i < hi; ++i) {
         s_tp[i] = run;
         run += (max(context_lens[i], 0) + tile_tokens - 1) / tile_tokens;
     }
-    if (tid == nt - 1) s_tp[batch] = s_scratch[nt - 1];
+    if (tid == nt - 1) s_tp[batch] = run;
     __syncthreads();
 }
 

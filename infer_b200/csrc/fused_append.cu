@@ -10,9 +10,9 @@
 // bf16 before the bf16 multiply by the weight, and the rotation is three bf16 operations per
 // output (two products, one sum), as rope.cu computes it in its scalar type.
 //
-// Eight lanes per (token, head), four heads per warp: a lane owns dims [8l, 8l+8) and
-// [64+8l, 64+8l+8) (two 16-byte loads), i.e. eight rotation pairs, so the pairing (i, i + 64)
-// never leaves the thread and the sum of squares needs three shuffles.
+// Eight lanes per (token, head), four heads per warp and load instruction: a lane owns dims
+// [8l, 8l+8) and [64+8l, 64+8l+8) (two 16-byte loads), i.e. eight rotation pairs, so the pairing
+// (i, i + 64) never leaves the thread and the sum of squares needs three shuffles.
 #include "common.cuh"
 
 namespace ib {
@@ -84,64 +84,64 @@ __device__ __forceinline__ void norm_rope(const RowPart& r, const __nv_bfloat16*
     }
 }
 
-// Two (token, head) items per lane group, kItems groups apart, so that the loads of both are in
-// flight together: the kernel waits on memory, not on arithmetic (ncu: 14 long-scoreboard
-// stall cycles per issued instruction with one item per group).
-constexpr int kItemsPerGroup = 2;
+// Work item of a warp: one token and a batch of up to 4 * kQuads of its heads (q heads first, then
+// k, then v).  Lane l works on head (l / 8) of each quad of four heads and owns dims [8 s, 8 s + 8)
+// and [64 + 8 s, 64 + 8 s + 8), s = l % 8.  The position's cosines and sines are loaded once per
+// item, the loads of all kQuads rows are issued before any arithmetic (6 KiB in flight per warp),
+// and a token's heads are consecutive in memory, so every load instruction of a warp covers 1 KiB
+// of one contiguous fused qkv row.
+constexpr int kQuads = 6;
 
 __global__ void __launch_bounds__(256) fused_norm_rope_append_kernel(FusedArgs a) {
     pdl_launch_dependents();
     const int heads = a.n_q_heads + 2 * a.n_kv_heads;
     const int qk_heads = a.n_q_heads + a.n_kv_heads;
-    const uint32_t total = uint32_t(a.n_tokens) * uint32_t(heads);       // the host keeps this below 2^28
-    const uint32_t groups = (total + kItemsPerGroup - 1) / kItemsPerGroup;
-    const uint32_t group = (blockIdx.x * blockDim.x + threadIdx.x) >> 3;
-    const int sub = threadIdx.x & 7;
-
-    // phase 1: where the items are, and every load they need
-    bool live[kItemsPerGroup], slot_ok[kItemsPerGroup];
-    int h[kItemsPerGroup];
-    int64_t tok[kItemsPerGroup], slot[kItemsPerGroup];
-    RowPart part[kItemsPerGroup];
+    const int batches = (heads + 4 * kQuads - 1) / (4 * kQuads);
+    const int lane = threadIdx.x & 31, sub = lane & 7, grp = lane >> 3;
+    const int64_t n_items = a.n_tokens * batches;
+    const int64_t n_warps = (int64_t(gridDim.x) * blockDim.x) >> 5;
+    for (int64_t item = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; item < n_items; item += n_warps) {
+        const int64_t tok = item / batches;
+        const int h0 = int(item - tok * batches) * 4 * kQuads;
+        const int64_t pos = min(max(a.positions[tok], int64_t(0)), a.max_position - 1);
+        const int64_t slot = a.slot_mapping[tok];
+        const bool slot_ok = slot >= 0 && slot < a.num_slots;      // false: padding row of a captured batch
+        // phase 1: every load of the item
+        RowPart part[kQuads];
+        int h[kQuads];
 #pragma unroll
-    for (int j = 0; j < kItemsPerGroup; ++j) {
-        const uint32_t item = group + uint32_t(j) * groups;
-        // an item past the end still takes part in the shuffles of its warp
-        live[j] = group < groups && item < total;
-        const uint32_t it = live[j] ? item : total - 1;
-        tok[j] = it / uint32_t(heads);
-        h[j] = int(it - uint32_t(tok[j]) * uint32_t(heads));
-        slot[j] = a.slot_mapping[tok[j]];
-        slot_ok[j] = slot[j] >= 0 && slot[j] < a.num_slots;      // false: padding row of a captured batch
-        const __nv_bfloat16* src = h[j] < a.n_q_heads ? a.q + tok[j] * a.q_pitch + h[j] * kHeadDim
-                                 : h[j] < qk_heads    ? a.k + tok[j] * a.k_pitch + (h[j] - a.n_q_heads) * kHeadDim
-                                                      : a.v + tok[j] * a.v_pitch + (h[j] - qk_heads) * kHeadDim;
-        part[j].x = *reinterpret_cast<const uint4*>(src + 8 * sub);
-        part[j].y = *reinterpret_cast<const uint4*>(src + 64 + 8 * sub);
-        if (h[j] < qk_heads) {
-            const int64_t pos = min(max(a.positions[tok[j]], int64_t(0)), a.max_position - 1);
-            const __nv_bfloat16* cs = a.cos_sin + pos * kHeadDim;
-            part[j].c = *reinterpret_cast<const uint4*>(cs + 8 * sub);
-            part[j].s = *reinterpret_cast<const uint4*>(cs + 64 + 8 * sub);
+        for (int j = 0; j < kQuads; ++j) {
+            h[j] = h0 + 4 * j + grp;
+            const int hh = min(h[j], heads - 1);                   // a lane group past the last head re-reads it and stores nothing
+            const __nv_bfloat16* src = hh < a.n_q_heads ? a.q + tok * a.q_pitch + hh * kHeadDim
+                                     : hh < qk_heads    ? a.k + tok * a.k_pitch + (hh - a.n_q_heads) * kHeadDim
+                                                        : a.v + tok * a.v_pitch + (hh - qk_heads) * kHeadDim;
+            part[j].x = *reinterpret_cast<const uint4*>(src + 8 * sub);
+            part[j].y = *reinterpret_cast<const uint4*>(src + 64 + 8 * sub);
         }
-    }
-    // phase 2: arithmetic and stores
+        const __nv_bfloat16* cs = a.cos_sin + pos * kHeadDim;
+        const uint4 c = *reinterpret_cast<const uint4*>(cs + 8 * sub);
+        const uint4 sn = *reinterpret_cast<const uint4*>(cs + 64 + 8 * sub);
+        // phase 2: arithmetic and stores
 #pragma unroll
-    for (int j = 0; j < kItemsPerGroup; ++j) {
-        if (h[j] < qk_heads) {
-            const bool is_q = h[j] < a.n_q_heads;
-            uint4 lo, hi;
-            norm_rope(part[j], is_q ? a.q_weight : a.k_weight, a.eps, sub, lo, hi);
-            if (!live[j] || (!is_q && !slot_ok[j])) continue;
-            __nv_bfloat16* dst = is_q ? a.q_out + tok[j] * a.q_out_pitch + h[j] * kHeadDim
-                                      : a.k_cache + (slot[j] * a.n_kv_heads + (h[j] - a.n_q_heads)) * int64_t(kHeadDim);
-            *reinterpret_cast<uint4*>(dst + 8 * sub) = lo;
-            *reinterpret_cast<uint4*>(dst + 64 + 8 * sub) = hi;
-        } else {
-            if (!live[j] || !slot_ok[j]) continue;
-            __nv_bfloat16* dst = a.v_cache + (slot[j] * a.n_kv_heads + (h[j] - qk_heads)) * int64_t(kHeadDim);
-            *reinterpret_cast<uint4*>(dst + 8 * sub) = part[j].x;
-            *reinterpret_cast<uint4*>(dst + 64 + 8 * sub) = part[j].y;
+        for (int j = 0; j < kQuads; ++j) {
+            if (h[j] >= heads) continue;                           // uniform over the 8 lanes of a group
+            if (h[j] < qk_heads) {
+                const bool is_q = h[j] < a.n_q_heads;
+                part[j].c = c;
+                part[j].s = sn;
+                uint4 lo, hi;
+                norm_rope(part[j], is_q ? a.q_weight : a.k_weight, a.eps, sub, lo, hi);
+                if (!is_q && !slot_ok) continue;
+                __nv_bfloat16* dst = is_q ? a.q_out + tok * a.q_out_pitch + h[j] * kHeadDim
+                                          : a.k_cache + (slot * a.n_kv_heads + (h[j] - a.n_q_heads)) * int64_t(kHeadDim);
+                *reinterpret_cast<uint4*>(dst + 8 * sub) = lo;
+                *reinterpret_cast<uint4*>(dst + 64 + 8 * sub) = hi;
+            } else if (slot_ok) {
+                __nv_bfloat16* dst = a.v_cache + (slot * a.n_kv_heads + (h[j] - qk_heads)) * int64_t(kHeadDim);
+                *reinterpret_cast<uint4*>(dst + 8 * sub) = part[j].x;
+                *reinterpret_cast<uint4*>(dst + 64 + 8 * sub) = part[j].y;
+            }
         }
     }
 }
@@ -189,10 +189,11 @@ extern "C" int infer_qk_norm_rope_append(const infer_kv_pool_t* pool, void* q_ou
     a.n_q_heads = n_q_heads;
     a.n_kv_heads = pool->n_kv_heads;
     a.eps = eps;
-    const int64_t items = n_tokens * (n_q_heads + 2 * pool->n_kv_heads);
-    const int64_t groups = (items + kItemsPerGroup - 1) / kItemsPerGroup;   // eight lanes each
-    const int64_t blocks = (groups + 31) / 32;
-    if (items >= (int64_t(1) << 28)) return INFER_ERR_GEOMETRY;           // 32-bit item arithmetic in the kernel
+    const int heads = n_q_heads + 2 * pool->n_kv_heads;
+    const int64_t items = n_tokens * ((heads + 4 * kQuads - 1) / (4 * kQuads));      // one warp each
+    int64_t blocks = (items + 7) / 8;
+    const int64_t cap = int64_t(pool->sm_count) * 16;                              // grid-stride beyond that
+    if (blocks > cap) blocks = cap;
     fused_norm_rope_append_kernel<<<unsigned(blocks), 256, 0, static_cast<cudaStream_t>(stream_)>>>(a);
     return check_launch();
 }

@@ -97,6 +97,10 @@ int infer_kv_pool_create(infer_kv_pool_t** out, void* k_cache, void* v_cache, fl
         delete p;
         return INFER_ERR_CUDA;
     }
+    if (ib::decode_prepare_device() != INFER_OK) {
+        delete p;
+        return INFER_ERR_CUDA;
+    }
     // Rows of one head are 128 elements; a swizzled box is 128 bytes wide.
     const uint32_t inner = 128 / p->elem_bytes;
     const uint64_t head_pitch = uint64_t(ib::kHeadDim) * p->elem_bytes;
@@ -136,6 +140,7 @@ const char* infer_strerror(int code) {
         case INFER_ERR_DEVICE: return "a bounded device-side wait ran out";
         case INFER_ERR_TOO_LARGE: return "problem exceeds the 2 MiB built-in scratch of infer_paged_decode_noalloc "
                                          "(batch <= 2048); use infer_paged_decode with a workspace";
+        case INFER_ERR_STATE: return "page allocator: out of pages, unknown or duplicate sequence, or a call out of order";
         default: return "unknown error code";
     }
 }

@@ -1,18 +1,17 @@
 // Entry points of the prefill attention ops: argument checks, tensor maps, kernel choice.
-#include <cstdlib>
 #include <mutex>
 
 #include "prefill.cuh"
 
 namespace ib {
 
-// The tcgen05 kernel is the product path; INFER_B200_PREFILL_IMPL=1 selects the mma.sync kernel
-// (kept as an on-GPU cross-check while the tcgen05 kernel is being tuned).
-static int prefill_impl() {
-    const char* s = std::getenv("INFER_B200_PREFILL_IMPL");
-    const int v = s && *s ? std::atoi(s) : 0;
-    return (v == 1 || v == 2) ? v : 2;
-}
+// The tcgen05 kernel is the product path.  The mma.sync kernel (prefill_mma.cu) is an on-GPU
+// cross-check that only the self-test entry points can select.
+struct PrefillOptions {
+    bool tc = true;
+    uint32_t wait_limit = kDefaultWaitLimit;
+    int stall_producer = 0;
+};
 
 // Status word of the prefill kernels: lives in the library's device image (one per GPU), set to
 // 0x5AFE0000 | code by a kernel whose bounded wait ran out, read and cleared by
@@ -39,27 +38,10 @@ static int* prefill_status_word() {
     return g_prefill_status_addr[dev];
 }
 
-}  // namespace ib
-
-extern "C" {
-
-int infer_prefill_status(void* stream_) {
-    int* word_dev = ib::prefill_status_word();
-    if (!word_dev) return INFER_ERR_CUDA;
-    int word = 0;
-    cudaStream_t st = static_cast<cudaStream_t>(stream_);
-    IB_CUDA(cudaMemcpyAsync(&word, word_dev, sizeof(int), cudaMemcpyDeviceToHost, st));
-    IB_CUDA(cudaStreamSynchronize(st));
-    if ((word & 0xFFFF0000) != 0x5AFE0000) return INFER_OK;
-    IB_CUDA(cudaMemsetAsync(word_dev, 0, sizeof(int), st));
-    return INFER_ERR_DEVICE;
-}
-
-int infer_paged_prefill(const infer_kv_pool_t* pool, void* out, const void* q, int64_t total_q,
-                        const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, const int32_t* block_tables,
-                        int64_t bt_stride, int batch, int max_seqlen_q, int max_seqlen_k, int n_q_heads,
-                        float softmax_scale, void* stream_) {
-    using namespace ib;
+static int paged_prefill(const infer_kv_pool_t* pool, void* out, const void* q, int64_t total_q,
+                         const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, const int32_t* block_tables,
+                         int64_t bt_stride, int batch, int max_seqlen_q, int max_seqlen_k, int n_q_heads,
+                         float softmax_scale, cudaStream_t st, const PrefillOptions& opt) {
     if (!pool || !out || !q || !cu_seqlens_q || !cu_seqlens_k || !block_tables) return INFER_ERR_NULL;
     if (pool->dtype != INFER_KV_BF16) return INFER_ERR_DTYPE;
     if (batch < 0 || n_q_heads <= 0 || n_q_heads % pool->n_kv_heads != 0 || bt_stride <= 0 || max_seqlen_q < 0 ||
@@ -85,8 +67,9 @@ int infer_paged_prefill(const infer_kv_pool_t* pool, void* out, const void* q, i
     p.seq_len = 0;
     p.scale_log2 = softmax_scale * 1.4426950408889634f;
     p.status = prefill_status_word();
-    cudaStream_t st = static_cast<cudaStream_t>(stream_);
-    if (prefill_impl() == 2) {
+    p.wait_limit = opt.wait_limit;
+    p.stall_producer = opt.stall_producer;
+    if (opt.tc) {
         CUtensorMap mq;   // q [total_q, Hq, 128]: rows past total_q are filled with zeros
         int rc = encode_map_3d(&mq, q, 2, kHeadDim, uint64_t(n_q_heads), uint64_t(total_q), 256,
                                uint64_t(n_q_heads) * 256, 64, 1, 128);
@@ -96,15 +79,14 @@ int infer_paged_prefill(const infer_kv_pool_t* pool, void* out, const void* q, i
     return launch_prefill_mma(true, p, pool->maps[2].k, pool->maps[2].v, max_seqlen_q, batch, st);
 }
 
-int infer_flash_attn_prefill(const void* q, const void* k, const void* v, void* o, int batch, int n_q_heads,
-                             int n_kv_heads, int seq_len, void* stream_) {
-    using namespace ib;
+static int dense_prefill(const void* q, const void* k, const void* v, void* o, int batch, int n_q_heads, int n_kv_heads,
+                         int seq_len, cudaStream_t st, const PrefillOptions& opt) {
     if (!q || !k || !v || !o) return INFER_ERR_NULL;
     if (batch <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads != 0 || seq_len <= 0 ||
         batch > 65535 || n_q_heads > 65535)
         return INFER_ERR_GEOMETRY;
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return INFER_ERR_ALIGN;
-    const bool tc = prefill_impl() == 2;
+    const bool tc = opt.tc;
     const uint32_t box_rows = tc ? 128 : 64;
     CUtensorMap mq, mk, mv;
     // K, V [B, Hkv, S, 128]: dims {128, S, B*Hkv}; a box never crosses into the next head,
@@ -131,9 +113,60 @@ int infer_flash_attn_prefill(const void* q, const void* k, const void* v, void* 
     p.seq_len = seq_len;
     p.scale_log2 = 1.4426950408889634f / sqrtf(float(kHeadDim));
     p.status = prefill_status_word();
-    cudaStream_t st = static_cast<cudaStream_t>(stream_);
+    p.wait_limit = opt.wait_limit;
+    p.stall_producer = opt.stall_producer;
     if (tc) return launch_prefill_tc(false, p, mq, mk, mv, seq_len, batch, st);
     return launch_prefill_mma(false, p, mk, mv, seq_len, batch, st);
+}
+
+}  // namespace ib
+
+extern "C" {
+
+int infer_prefill_status(void* stream_) {
+    int* word_dev = ib::prefill_status_word();
+    if (!word_dev) return INFER_ERR_CUDA;
+    int word = 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream_);
+    IB_CUDA(cudaMemcpyAsync(&word, word_dev, sizeof(int), cudaMemcpyDeviceToHost, st));
+    IB_CUDA(cudaStreamSynchronize(st));
+    if ((word & 0xFFFF0000) != 0x5AFE0000) return INFER_OK;
+    IB_CUDA(cudaMemsetAsync(word_dev, 0, sizeof(int), st));
+    return INFER_ERR_DEVICE;
+}
+
+int infer_paged_prefill(const infer_kv_pool_t* pool, void* out, const void* q, int64_t total_q,
+                        const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, const int32_t* block_tables,
+                        int64_t bt_stride, int batch, int max_seqlen_q, int max_seqlen_k, int n_q_heads,
+                        float softmax_scale, void* stream_) {
+    return ib::paged_prefill(pool, out, q, total_q, cu_seqlens_q, cu_seqlens_k, block_tables, bt_stride, batch,
+                             max_seqlen_q, max_seqlen_k, n_q_heads, softmax_scale, static_cast<cudaStream_t>(stream_),
+                             ib::PrefillOptions{});
+}
+
+int infer_flash_attn_prefill(const void* q, const void* k, const void* v, void* o, int batch, int n_q_heads,
+                             int n_kv_heads, int seq_len, void* stream_) {
+    return ib::dense_prefill(q, k, v, o, batch, n_q_heads, n_kv_heads, seq_len, static_cast<cudaStream_t>(stream_),
+                             ib::PrefillOptions{});
+}
+
+int infer_selftest_paged_prefill(const infer_kv_pool_t* pool, void* out, const void* q, int64_t total_q,
+                                 const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, const int32_t* block_tables,
+                                 int64_t bt_stride, int batch, int max_seqlen_q, int max_seqlen_k, int n_q_heads,
+                                 float softmax_scale, void* stream_, int kernel, uint32_t wait_limit, int stall_producer) {
+    ib::PrefillOptions opt;
+    opt.tc = kernel != 1;
+    if (wait_limit) opt.wait_limit = wait_limit;
+    opt.stall_producer = opt.tc ? stall_producer : 0;
+    return ib::paged_prefill(pool, out, q, total_q, cu_seqlens_q, cu_seqlens_k, block_tables, bt_stride, batch,
+                             max_seqlen_q, max_seqlen_k, n_q_heads, softmax_scale, static_cast<cudaStream_t>(stream_), opt);
+}
+
+int infer_selftest_flash_attn_prefill(const void* q, const void* k, const void* v, void* o, int batch, int n_q_heads,
+                                      int n_kv_heads, int seq_len, void* stream_, int kernel) {
+    ib::PrefillOptions opt;
+    opt.tc = kernel != 1;
+    return ib::dense_prefill(q, k, v, o, batch, n_q_heads, n_kv_heads, seq_len, static_cast<cudaStream_t>(stream_), opt);
 }
 
 }  // extern "C"

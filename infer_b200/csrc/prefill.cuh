@@ -22,6 +22,8 @@ struct PrefillParams {
     int seq_len;              // dense only
     float scale_log2;
     int* status;              // may be null
+    uint32_t wait_limit;      // polls before a barrier wait gives up
+    int stall_producer;       // self-test only: the producer loads nothing, so every wait runs out
 };
 
 // mma.sync path (prefill_mma.cu): 64 query rows per CTA.

@@ -26,6 +26,8 @@
 // registers).  The softmax arithmetic uses packed f32x2 instructions and 3-input max.  Every
 // barrier wait is bounded; a wait that runs out raises a CTA-wide abort flag, every role
 // drains to the common epilogue, TMEM is freed and a status is set.
+#include <atomic>
+
 #include "prefill.cuh"
 
 namespace ib {
@@ -156,7 +158,7 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
 // Bounded wait that also gives up as soon as another thread raised the abort flag.  One test
 // in front of the polling loop: a wait on a phase that is already complete then costs a test
 // and a branch (about 35 clocks) instead of a trip through the loop (about 210 as measured).
-__device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t limit) {
     if (mbar_try_wait(bar, parity)) return true;
     uint32_t i = 0;
 #pragma unroll 1
@@ -164,7 +166,7 @@ __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile 
         if (mbar_try_wait(bar, parity)) return true;
         if ((++i & 63) == 0) {
             if (*abort_flag) return false;
-            if (i >= (1u << 22)) break;
+            if (i >= limit) break;
             __nanosleep(i > 4096 ? 256 : 32);
         }
     }
@@ -260,7 +262,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
     asm volatile("setmaxnreg.dec.sync.aligned.u32 104;" ::: "memory");
     if (warp == kTcProducerWarp) {
         // ================================================================= TMA producer
-        if (lane == 0) {
+        if (lane == 0 && !p.stall_producer) {
             tma_prefetch_desc(&map_q);
             tma_prefetch_desc(&map_k);
             tma_prefetch_desc(&map_v);
@@ -291,23 +293,23 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
             // order K0, K1, V0, K2, V1, ...: K of the next tile is needed before V of this one
             for (int j = 0; j <= n_max && ok; ++j) {
                 if (j < n_max) {
-                    if (tc_wait(bar(K_EMPTY, j % kTcKStages), ((j / kTcKStages) & 1) ^ 1, s_abort)) {
+                    if (tc_wait(bar(K_EMPTY, j % kTcKStages), ((j / kTcKStages) & 1) ^ 1, s_abort, p.wait_limit)) {
                         load_tile(&map_k, base + TcSmem::k + (j % kTcKStages) * kTcTile, bar(K_FULL, j % kTcKStages), j);
                         ++k_issued;
                     } else ok = false;
                 }
                 if (j >= 1 && ok) {
                     const int jv = j - 1;
-                    if (tc_wait(bar(V_EMPTY, jv % kTcVStages), ((jv / kTcVStages) & 1) ^ 1, s_abort)) {
+                    if (tc_wait(bar(V_EMPTY, jv % kTcVStages), ((jv / kTcVStages) & 1) ^ 1, s_abort, p.wait_limit)) {
                         load_tile(&map_v, base + TcSmem::v + (jv % kTcVStages) * kTcTile, bar(V_FULL, jv % kTcVStages), jv);
                         ++v_issued;
                     } else ok = false;
                 }
             }
             // never leave with a copy in flight: wait (bounded) for everything that was armed
-            mbar_wait(bar(Q_FULL), 0);
-            for (int j = max(0, k_issued - kTcKStages); j < k_issued; ++j) mbar_wait(bar(K_FULL, j % kTcKStages), (j / kTcKStages) & 1);
-            for (int j = max(0, v_issued - kTcVStages); j < v_issued; ++j) mbar_wait(bar(V_FULL, j % kTcVStages), (j / kTcVStages) & 1);
+            mbar_wait(bar(Q_FULL), 0, p.wait_limit);
+            for (int j = max(0, k_issued - kTcKStages); j < k_issued; ++j) mbar_wait(bar(K_FULL, j % kTcKStages), (j / kTcKStages) & 1, p.wait_limit);
+            for (int j = max(0, v_issued - kTcVStages); j < v_issued; ++j) mbar_wait(bar(V_FULL, j % kTcVStages), (j / kTcVStages) & 1, p.wait_limit);
         }
     } else if (warp == kTcMmaWarp) {
         // ================================================================= MMA issue: the S products
@@ -323,7 +325,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
         const uint64_t q_desc0 = tc_desc(base + TcSmem::q, 16), k_desc0 = tc_desc(base + TcSmem::k, 16);
         int n_s = 0;                               // S products issued so far
         auto issue_s = [&](int i, int stage) {     // S = Q_i K^T  (K_FULL of that stage already awaited)
-            if (n_s > 0 && !tc_wait(bar(S_FREE), (n_s - 1) & 1, s_abort)) { ok = false; return; }
+            if (n_s > 0 && !tc_wait(bar(S_FREE), (n_s - 1) & 1, s_abort, p.wait_limit)) { ok = false; return; }
             ++n_s;
             tc_fence_after();
             if (elect_one()) {
@@ -338,10 +340,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
             }
             __syncwarp();
         };
-        if (!tc_wait(bar(Q_FULL), 0, s_abort)) ok = false;
+        if (!tc_wait(bar(Q_FULL), 0, s_abort, p.wait_limit)) ok = false;
         int ks = 0, kph = 0;                                           // stage and phase of K_j
         for (int j = 0; j < n_max && ok; ++j) {
-            if (!tc_wait(bar(K_FULL, ks), kph, s_abort)) { ok = false; break; }
+            if (!tc_wait(bar(K_FULL, ks), kph, s_abort, p.wait_limit)) { ok = false; break; }
             if (j < kt0) issue_s(0, ks);
             if (ok && j < kt1) issue_s(1, ks);
             if (!ok) break;
@@ -352,7 +354,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
         // all tensor-core work issued by this warp must have retired before TMEM is freed
         if (elect_one()) tc_commit(bar(DRAIN, 0));
         __syncwarp();
-        mbar_wait(bar(DRAIN, 0), 0);
+        mbar_wait(bar(DRAIN, 0), 0, p.wait_limit);
     } else if (warp == kTcMmaWarp + 1) {
         // ================================================================= MMA issue: the P V products
         // P V_0(0) P V_1(0) P V_0(1) ...: each once its warpgroup has written P.
@@ -360,7 +362,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
         const int kt0 = tile[0].n_kt, kt1 = tile[1].n_kt;
         const uint64_t v_desc0 = tc_desc(base + TcSmem::v, kTcHalf);
         auto issue_pv = [&](int i, int stage, int j) {   // O_i += P_i V  (V_FULL of that stage already awaited)
-            if (!tc_wait(bar(P_FULL, i), j & 1, s_abort)) { ok = false; return; }
+            if (!tc_wait(bar(P_FULL, i), j & 1, s_abort, p.wait_limit)) { ok = false; return; }
             tc_fence_after();
             if (elect_one()) {
                 const uint64_t vd = v_desc0 + uint64_t(stage * (kTcTile >> 4));
@@ -375,7 +377,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
         };
         int vs = 0, vph = 0;                                           // stage and phase of V_j
         for (int j = 0; j < n_max && ok; ++j) {
-            if (!tc_wait(bar(V_FULL, vs), vph, s_abort)) { ok = false; break; }
+            if (!tc_wait(bar(V_FULL, vs), vph, s_abort, p.wait_limit)) { ok = false; break; }
             if (PAGED && j == n_max - 1) {
                 // keys past the end of the context: P is 0 there, but 0 * (stale bytes) must not
                 // produce NaN, so clear those V rows before the tensor core reads them
@@ -399,7 +401,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
         }
         if (elect_one()) tc_commit(bar(DRAIN, 1));
         __syncwarp();
-        mbar_wait(bar(DRAIN, 1), 0);
+        mbar_wait(bar(DRAIN, 1), 0, p.wait_limit);
     }
     } else {
         // ================================================================= softmax, one row per thread
@@ -417,7 +419,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
         float m_ref = -INFINITY, l_run = 0.f;                      // reference maximum (log2 domain), row sum
 
         for (int j = 0; j < n_kt; ++j) {
-            if (ok && !tc_wait(bar(S_FULL, g), j & 1, s_abort)) ok = false;
+            if (ok && !tc_wait(bar(S_FULL, g), j & 1, s_abort, p.wait_limit)) ok = false;
             if (!ok) continue;
             tc_fence_after();
             const int limit = pos - j * kTcKeys;                     // columns <= limit are visible
@@ -453,7 +455,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
                 const float alpha = m_ref == -INFINITY ? 0.f : fast_exp2(m_ref - m_new);
                 if (j > 0) {
                     // O holds tiles < j once P V_{j-1} has retired; P V_j cannot start before P_FULL below
-                    if (!tc_wait(bar(PV_DONE, g), (j - 1) & 1, s_abort)) { ok = false; continue; }
+                    if (!tc_wait(bar(PV_DONE, g), (j - 1) & 1, s_abort, p.wait_limit)) { ok = false; continue; }
                     tc_fence_after();
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
@@ -471,7 +473,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
             }
             const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
             // the tensor core must be done reading P of the previous key tile (long since, as a rule)
-            if (j > 0 && !tc_wait(bar(PV_DONE, g), (j - 1) & 1, s_abort)) { ok = false; continue; }
+            if (j > 0 && !tc_wait(bar(PV_DONE, g), (j - 1) & 1, s_abort, p.wait_limit)) { ok = false; continue; }
             // P = exp2(S * c - m) as packed bf16
             uint64_t rsa = pk2(0.f, 0.f), rsb = pk2(0.f, 0.f);
             const uint64_t c2 = pk2(p.scale_log2, p.scale_log2), nm2 = pk2(-m_use, -m_use);
@@ -500,7 +502,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
             mbar_arrive(bar(P_FULL, g));
         }
         // O is complete once the last P V has retired
-        if (n_kt > 0 && ok && !tc_wait(bar(PV_DONE, g), (n_kt - 1) & 1, s_abort)) ok = false;
+        if (n_kt > 0 && ok && !tc_wait(bar(PV_DONE, g), (n_kt - 1) & 1, s_abort, p.wait_limit)) ok = false;
         if (n_kt > 0 && ok) {
             tc_fence_after();
             const float inv = 1.f / l_run;
@@ -548,13 +550,17 @@ int launch_prefill_tc(bool paged, const PrefillParams& p, const CUtensorMap& mq,
     dim3 grid = pair_heads ? dim3((max_q + kTcRows - 1) / kTcRows, p.n_q_heads / 2, batch)
                            : dim3((max_q + kTcQTiles * kTcRows - 1) / (kTcQTiles * kTcRows), p.n_q_heads, batch);
     const int smem = TcSmem::total + 1024;
-    if (paged) {
+    // the shared-memory limit of the two instantiations is raised once per device
+    static std::atomic<bool> prepared[64];
+    int dev = 0;
+    IB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !prepared[dev].load(std::memory_order_acquire)) {
         IB_CUDA(cudaFuncSetAttribute(prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        prefill_tc_kernel<true><<<grid, kTcThreads, smem, st>>>(p, pair_heads, mq, mk, mv);
-    } else {
         IB_CUDA(cudaFuncSetAttribute(prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        prefill_tc_kernel<false><<<grid, kTcThreads, smem, st>>>(p, pair_heads, mq, mk, mv);
+        if (dev >= 0 && dev < 64) prepared[dev].store(true, std::memory_order_release);
     }
+    if (paged) prefill_tc_kernel<true><<<grid, kTcThreads, smem, st>>>(p, pair_heads, mq, mk, mv);
+    else prefill_tc_kernel<false><<<grid, kTcThreads, smem, st>>>(p, pair_heads, mq, mk, mv);
     return check_launch();
 }
 

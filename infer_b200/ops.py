@@ -20,11 +20,78 @@ import torch
 from . import _lib
 
 _POOLS: dict = {}
-_WORKSPACES: dict = {}
+_CHECK = os.environ.get("INFER_B200_CHECK") == "1"    # debugging: read the device status word after each call
 
 
 def _stream():
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class _on_device:
+    """``torch.cuda.device(dev)`` without its cost when ``dev`` is already current (the usual case)."""
+
+    __slots__ = ("guard",)
+
+    def __init__(self, device):
+        self.guard = None if torch.cuda.current_device() == device.index else torch.cuda.device(device)
+
+    def __enter__(self):
+        if self.guard is not None:
+            self.guard.__enter__()
+
+    def __exit__(self, *exc):
+        if self.guard is not None:
+            self.guard.__exit__(*exc)
+
+
+# The three attention entry points are reached through these one-line functions so that the test
+# suite can route a call to the library's self-test entry points (infer_b200/selftest.py).
+def _call_decode(lib, *args):
+    return lib.infer_paged_decode(*args)
+
+
+def _call_prefill(lib, *args):
+    return lib.infer_paged_prefill(*args)
+
+
+def _call_dense(lib, *args):
+    return lib.infer_flash_attn_prefill(*args)
+
+
+class _Scratch:
+    """Zero-initialised scratch buffers, one per (device, purpose), grown on demand.
+
+    A buffer that was handed out once is NEVER freed or moved: a CUDA graph captured earlier keeps
+    launching kernels on its address, so when a later call needs more, the old buffer is retired to
+    ``_retired`` (kept alive for the life of the process) and a larger one takes its place for new
+    calls.  In practice the first call of a model sizes the buffer and it never grows.
+
+    Every call on a device shares the buffer of its purpose: calls must be ordered on ONE stream
+    (or inside one graph).  A caller that runs attention on several streams of one device passes
+    its own ``workspace=`` tensor per stream to the ops instead."""
+
+    def __init__(self):
+        self._live: dict = {}
+        self._retired: list = []
+
+    def get(self, device, purpose: str, nbytes: int) -> torch.Tensor:
+        key = (device.index, purpose)
+        buf = self._live.get(key)
+        if buf is None or buf.numel() < nbytes:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("infer_b200: scratch memory has to be sized before a stream capture: "
+                                   "call the op once eagerly first (the reference's capture loop does)")
+            if buf is not None:
+                self._retired.append(buf)
+            buf = self._live[key] = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        return buf
+
+    def clear(self):
+        self._live.clear()
+        self._retired.clear()
+
+
+_SCRATCH = _Scratch()
 
 
 def _ptr(t):
@@ -58,12 +125,21 @@ class KVPool:
         self.device = k_cache.device
         lib = _lib.load()
         handle = C.c_void_p()
-        with torch.cuda.device(self.device):
+        with _on_device(self.device):
             rc = lib.infer_kv_pool_create(C.byref(handle), _ptr(k_cache), _ptr(v_cache), _ptr(k_scale), _ptr(v_scale),
                                           self.num_blocks, self.block_size, self.n_kv_heads, self.head_dim,
                                           _lib.KV_E4M3 if fp8 else _lib.KV_BF16)
         _lib.check(rc, "infer_kv_pool_create")
         self.handle = handle
+        self._decode_ws_bytes: dict = {}      # n_q_heads -> bytes, asked of the library once
+        self.append_ws_bytes = lib.infer_kv_append_workspace_bytes(handle) if fp8 else 0
+
+    def decode_workspace_bytes(self, batch: int, n_q_heads: int) -> int:
+        need = self._decode_ws_bytes.get(n_q_heads)
+        if need is None:
+            need = self._decode_ws_bytes[n_q_heads] = _lib.load().infer_paged_decode_workspace_bytes(
+                self.handle, batch, n_q_heads)
+        return need
 
     def __del__(self):
         h = getattr(self, "handle", None)
@@ -85,21 +161,15 @@ def pool_of(k_cache, v_cache, k_scale=None, v_scale=None) -> KVPool:
 
 
 def release_pools():
+    """Forgets every pool handle and scratch buffer (only when no captured graph still uses them)."""
     _POOLS.clear()
-    _WORKSPACES.clear()
-
-
-def _workspace(device, nbytes: int) -> torch.Tensor:
-    """Zero-initialised scratch, grown on demand, one per device (never inside a graph
-    capture: call the op once eagerly first, as the reference's capture loop does)."""
-    ws = _WORKSPACES.get(device)
-    if ws is None or ws.numel() < nbytes:
-        ws = _WORKSPACES[device] = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-    return ws
+    _SCRATCH.clear()
 
 
 # --------------------------------------------------------------------------- append
-def store_kvcache(key, value, k_cache, v_cache, slot_mapping, k_scale=None, v_scale=None):
+def store_kvcache(key, value, k_cache, v_cache, slot_mapping, k_scale=None, v_scale=None, workspace=None):
+    """``workspace`` (e4m3 pools only): a zero-initialised uint8 tensor of ``pool.append_ws_bytes``
+    that this caller reserves for its own stream; by default the per-device scratch is used."""
     n, num_heads, head_dim = key.shape
     d = num_heads * head_dim
     assert key.stride(-1) == 1 and value.stride(-1) == 1
@@ -119,9 +189,9 @@ def store_kvcache(key, value, k_cache, v_cache, slot_mapping, k_scale=None, v_sc
     v_pitch = value.stride(0) if n > 1 else d
     ws, ws_bytes = None, 0
     if pool.fp8:
-        ws_bytes = lib.infer_kv_append_workspace_bytes(pool.handle)
-        ws = _workspace(pool.device, ws_bytes)
-    with torch.cuda.device(pool.device):
+        ws_bytes = pool.append_ws_bytes
+        ws = workspace if workspace is not None else _SCRATCH.get(pool.device, "fp8-append", ws_bytes)
+    with _on_device(pool.device):
         rc = lib.infer_kv_append(pool.handle, _ptr(key), _ptr(value), k_pitch, v_pitch,
                                  _ptr(slot_mapping), n, _ptr(ws), ws_bytes, _stream())
     _lib.check(rc, "store_kvcache")
@@ -151,7 +221,7 @@ def qk_norm_rope_append(q, k, v, q_norm_weight, k_norm_weight, eps, positions, c
     pool = pool_of(k_cache, v_cache)
     pitch = lambda x: x.stride(0) if t > 1 else x.shape[1] * d
     lib = _lib.load()
-    with torch.cuda.device(pool.device):
+    with _on_device(pool.device):
         rc = lib.infer_qk_norm_rope_append(pool.handle, _ptr(q_out), pitch(q_out), _ptr(q), _ptr(k), _ptr(v), pitch(q),
                                            pitch(k), pitch(v), _ptr(q_norm_weight), _ptr(k_norm_weight), float(eps),
                                            _ptr(positions), _ptr(cos_sin_cache), cos_sin_cache.shape[0],
@@ -162,8 +232,12 @@ def qk_norm_rope_append(q, k, v, q_norm_weight, k_norm_weight, eps, positions, c
 
 # --------------------------------------------------------------------------- decode
 def paged_attn_decode(q, k_cache, v_cache, cache_seqlens, block_table, softmax_scale,
-                      out=None, k_scale=None, v_scale=None):
-    """q [B, Hq, 128] (or [B, 1, Hq, 128] as the reference passes it) -> same shape."""
+                      out=None, k_scale=None, v_scale=None, workspace=None):
+    """q [B, Hq, 128] (or [B, 1, Hq, 128] as the reference passes it) -> same shape.
+
+    ``workspace``: a zero-initialised uint8 tensor of at least
+    ``pool.decode_workspace_bytes(B, Hq)`` bytes reserved for this caller's stream; by default the
+    per-device scratch is used (see ``_Scratch``: one stream per device)."""
     shape = q.shape
     q3 = q.reshape(shape[0], shape[-2], shape[-1])
     if q3.dtype != torch.bfloat16 or not q3.is_contiguous():
@@ -177,14 +251,12 @@ def paged_attn_decode(q, k_cache, v_cache, cache_seqlens, block_table, softmax_s
     o = torch.empty_like(q3) if out is None else out.view(q3.shape)
     lib = _lib.load()
     b, hq, _ = q3.shape
-    need = lib.infer_paged_decode_workspace_bytes(pool.handle, b, hq)
-    ws = _workspace(pool.device, need)
-    with torch.cuda.device(pool.device):
-        rc = lib.infer_paged_decode(pool.handle, _ptr(o), _ptr(q3), _ptr(cache_seqlens), _ptr(block_table),
-                                    block_table.stride(0), b, hq, float(softmax_scale), _ptr(ws), ws.numel(),
-                                    _stream())
+    ws = workspace if workspace is not None else _SCRATCH.get(pool.device, "decode", pool.decode_workspace_bytes(b, hq))
+    with _on_device(pool.device):
+        rc = _call_decode(lib, pool.handle, _ptr(o), _ptr(q3), _ptr(cache_seqlens), _ptr(block_table),
+                          block_table.stride(0), b, hq, float(softmax_scale), _ptr(ws), ws.numel(), _stream())
         _lib.check(rc, "paged_attn_decode")
-        if os.environ.get("INFER_B200_CHECK") == "1" and not torch.cuda.is_current_stream_capturing():
+        if _CHECK and not torch.cuda.is_current_stream_capturing():
             _lib.check(lib.infer_paged_decode_status(_ptr(ws), _stream()), "paged_attn_decode (device status)")
     return o.view(shape)
 
@@ -202,8 +274,8 @@ def paged_attn_prefill(q, k_cache, v_cache, cu_seqlens_q, cu_seqlens_k, max_seql
     pool = pool_of(k_cache, v_cache)
     o = torch.empty_like(q) if out is None else out
     lib = _lib.load()
-    with torch.cuda.device(pool.device):
-        rc = lib.infer_paged_prefill(pool.handle, _ptr(o), _ptr(q), q.shape[0], _ptr(cu_seqlens_q), _ptr(cu_seqlens_k),
+    with _on_device(pool.device):
+        rc = _call_prefill(lib, pool.handle, _ptr(o), _ptr(q), q.shape[0], _ptr(cu_seqlens_q), _ptr(cu_seqlens_k),
                                      _ptr(block_table), block_table.stride(0), cu_seqlens_q.numel() - 1,
                                      int(max_seqlen_q), int(max_seqlen_k), q.shape[1], float(softmax_scale),
                                      _stream())
@@ -215,7 +287,7 @@ def paged_attn_prefill(q, k_cache, v_cache, cu_seqlens_q, cu_seqlens_k, max_seql
 def _check_prefill_status(lib, what):
     """With INFER_B200_CHECK=1 (and outside stream capture): synchronise and raise if a bounded
     wait inside the prefill kernel ran out."""
-    if os.environ.get("INFER_B200_CHECK") == "1" and not torch.cuda.is_current_stream_capturing():
+    if _CHECK and not torch.cuda.is_current_stream_capturing():
         _lib.check(lib.infer_prefill_status(_stream()), f"{what} (device status)")
 
 
@@ -227,8 +299,8 @@ def flash_attn_prefill(Q, K, V, O):
     if Q.shape[-1] != 128 or K.shape != V.shape or O.shape != Q.shape or K.shape[2] != Q.shape[2]:
         raise RuntimeError("flash_attn_prefill: shape mismatch")
     lib = _lib.load()
-    with torch.cuda.device(Q.device):
-        rc = lib.infer_flash_attn_prefill(_ptr(Q), _ptr(K), _ptr(V), _ptr(O), Q.shape[0], Q.shape[1], K.shape[1],
+    with _on_device(Q.device):
+        rc = _call_dense(lib, _ptr(Q), _ptr(K), _ptr(V), _ptr(O), Q.shape[0], Q.shape[1], K.shape[1],
                                           Q.shape[2], _stream())
         _lib.check(rc, "flash_attn_prefill")
         _check_prefill_status(lib, "flash_attn_prefill")

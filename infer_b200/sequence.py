@@ -1,82 +1,58 @@
-"""Per-request token list and its page table.
+"""``Sequence``: what the host side knows about one request.
 
-Host-side mirror of the reference's ``Sequence`` (infer/engine/sequence.py:15-84):
-same attribute names and the same page arithmetic, so that the page allocator and
-the step-metadata builders of this package read like the reference's callers.
-Only what the paged KV path needs is kept (no sampling state machine).
+It carries the attributes the step-metadata builders read off a request - the token ids, the
+logical -> physical page list the allocator fills in, and the number of prompt tokens whose
+pages were found in the prefix cache - under the names the reference's runner uses
+(infer/engine/model_runner.py:66-126 reads ``len(seq)``, ``seq.block_table``,
+``seq.num_cached_tokens``, ``seq.num_cached_blocks``, ``seq.num_blocks``,
+``seq.last_block_num_tokens``, ``seq.last_token``; infer/engine/sequence.py:15-84 defines them).
+Page allocation itself is native code (``BlockManager``).
 """
 from __future__ import annotations
 
 import itertools
-from dataclasses import dataclass
-from enum import Enum, auto
 
-
-@dataclass
-class SamplingParams:
-    """Mirror of infer/sampling_params.py (fields used by ``Sequence``)."""
-    temperature: float = 1.0
-    max_tokens: int = 64
-    ignore_eos: bool = False
-
-
-class SequenceStatus(Enum):
-    WAITING = auto()
-    RUNNING = auto()
-    FINISHED = auto()
+_next_id = itertools.count()
 
 
 class Sequence:
-    """A request: token ids plus the logical->physical page list.
+    block_size = 256          # page size in tokens (the engine config requires a multiple of 256)
 
-    ``block_size`` is the page size in tokens (reference: 256,
-    infer/engine/sequence.py:16; the engine config requires a multiple of 256,
-    infer/config.py:21).
-    """
-
-    block_size = 256
-    _ids = itertools.count()
-
-    def __init__(self, token_ids, sampling_param: SamplingParams | None = None):
-        sampling_param = sampling_param or SamplingParams()
-        self.seq_id = next(Sequence._ids)
-        self.status = SequenceStatus.WAITING
-        self.token_ids = list(token_ids)
-        self.num_tokens = len(self.token_ids)
-        self.num_prompt_tokens = self.num_tokens
-        self.last_token = self.token_ids[-1]
+    def __init__(self, token_ids, max_tokens: int = 64):
+        self.seq_id = next(_next_id)
+        self.token_ids = [int(t) for t in token_ids]
+        if not self.token_ids:
+            raise ValueError("a sequence needs at least one token")
+        self.num_prompt_tokens = len(self.token_ids)
+        self.max_tokens = max_tokens
         self.num_cached_tokens = 0
         self.block_table: list[int] = []
-        self.temperature = sampling_param.temperature
-        self.max_tokens = sampling_param.max_tokens
-        self.ignore_eos = sampling_param.ignore_eos
 
     def __len__(self):
-        return self.num_tokens
+        return len(self.token_ids)
 
     def __getitem__(self, key):
         return self.token_ids[key]
+
+    @property
+    def last_token(self) -> int:
+        return self.token_ids[-1]
+
+    @property
+    def num_completion_tokens(self) -> int:
+        return len(self.token_ids) - self.num_prompt_tokens
+
+    @property
+    def num_blocks(self) -> int:
+        return -(-len(self.token_ids) // self.block_size)
 
     @property
     def num_cached_blocks(self) -> int:
         return self.num_cached_tokens // self.block_size
 
     @property
-    def num_blocks(self) -> int:
-        return -(-self.num_tokens // self.block_size)
-
-    @property
     def last_block_num_tokens(self) -> int:
-        return self.num_tokens - (self.num_blocks - 1) * self.block_size
-
-    def block(self, i: int):
-        """Token ids held by logical page ``i``."""
-        if not 0 <= i < self.num_blocks:
-            raise IndexError(i)
-        lo = i * self.block_size
-        return self.token_ids[lo:lo + self.block_size]
+        return len(self.token_ids) - (self.num_blocks - 1) * self.block_size
 
     def append_token(self, token_id: int):
-        self.token_ids.append(token_id)
-        self.last_token = token_id
-        self.num_tokens += 1
+        self.token_ids.append(int(token_id))

@@ -14,7 +14,6 @@ sequence are scattered over the pool.
 from __future__ import annotations
 
 import math
-from collections import deque
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -113,7 +112,7 @@ def _allocate(lens, num_blocks, rng, shared_prefix=0, n_shared=0):
     The first ``n_shared`` sequences start with the same ``shared_prefix`` token ids and
     so share those physical pages."""
     mgr = BlockManager(num_blocks, BLOCK_SIZE)
-    mgr.free_block_ids = deque(int(i) for i in rng.permutation(num_blocks))
+    mgr.free_block_ids = [int(i) for i in rng.permutation(num_blocks)]
     common = rng.integers(0, 32000, size=shared_prefix).tolist()
     tables = []
     for i, n in enumerate(lens):
@@ -211,7 +210,7 @@ def config3(device="cpu", seed=1003):
 
 
 def config4(device="cpu", seed=1004, batch=256, cap=32768, with_pool=True, n_kv_heads=8, n_q_heads=64,
-            tensor_seed=None):
+            tensor_seed=None, longest_at_cap=False):
     """Qwen3-32B long-context shape: Hq64/Hkv8, ctx lognormal(median 4096, sigma 0.8) capped
     at 32768; the first half of the batch shares the pages of a 2048-token prefix.
     ``n_kv_heads``/``n_q_heads`` below 8/64 build one KV-head shard directly (see config1)."""
@@ -220,6 +219,8 @@ def config4(device="cpu", seed=1004, batch=256, cap=32768, with_pool=True, n_kv_
     n_shared = batch // 2
     lens[:n_shared] = np.maximum(lens[:n_shared], 2049)
     lens = np.maximum(lens, 2)
+    if longest_at_cap:            # tests: make sure one context really is `cap` tokens long (the draw's maximum may fall short)
+        lens[int(np.argmax(lens))] = cap
     pages = sum(-(-int(n) // BLOCK_SIZE) for n in lens)
     num_blocks = max(pages, math.ceil(1.1 * int(lens.sum()) / BLOCK_SIZE))
     return _decode_workload("qwen3-32b-long-decode", seed, n_q_heads, n_kv_heads, lens, num_blocks, device,

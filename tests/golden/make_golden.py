@@ -209,7 +209,9 @@ def golden_norm_rope():
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <path to a checkout of Graylatzhou/Infer>")
+    root = sys.argv[1]
     BlockManager, ModelRunner, Sequence, SamplingParams, store_kvcache, get_context = import_reference(root)
     result = {
         "norm_rope": golden_norm_rope(),

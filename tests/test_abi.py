@@ -8,8 +8,8 @@ from infer_b200 import _lib
 ROOT = Path(__file__).resolve().parent.parent
 
 
-def declared_symbols():
-    text = (ROOT / "include" / "infer_b200.h").read_text()
+def declared_symbols(header="infer_b200.h"):
+    text = (ROOT / "include" / header).read_text()
     return sorted(set(re.findall(r"INFER_API[^;(]*?\b(infer_\w+)\s*\(", text)))
 
 
@@ -22,12 +22,22 @@ def test_header_declares_the_path():
 
 def test_library_exports_every_declared_symbol():
     lib = ctypes.CDLL(str(_lib.LIB_PATH))
-    for name in declared_symbols():
-        assert hasattr(lib, name), f"{name} declared in include/infer_b200.h but not exported"
+    for name in declared_symbols() + declared_symbols("infer_b200_selftest.h"):
+        assert hasattr(lib, name), f"{name} declared in include/ but not exported"
 
 
 def test_bindings_cover_every_declared_symbol():
     assert sorted(_lib.SIGNATURES) == declared_symbols()
+    assert sorted(_lib.SELFTEST_SIGNATURES) == declared_symbols("infer_b200_selftest.h")
+
+
+def test_product_modules_do_not_reach_the_selftest_entry_points():
+    """Only infer_b200/selftest.py (used by the tests) names the diagnostic entry points."""
+    for path in (ROOT / "infer_b200").glob("*.py"):
+        if path.name in ("selftest.py", "_lib.py"):
+            continue
+        assert "infer_selftest_" not in path.read_text(), path
+    assert "infer_selftest_" not in (ROOT / "bench.py").read_text()
 
 
 def test_error_strings_and_argument_checks_need_no_gpu():

@@ -4,21 +4,26 @@ import pytest
 import torch
 
 from gpu_util import ATOL_BF16, RTOL_BF16, assert_close, to_dev
-from infer_b200 import ops, workloads
+from infer_b200 import ops, selftest, workloads
 from oracle import paged_kv_oracle as oracle
 
 pytestmark = pytest.mark.gpu
 
-VARIANTS = [("2", "0"), ("2", "2"), ("2", "4"), ("2", "8"), ("1", "0")]   # (kernel, heads per tile)
+VARIANTS = [0, 1, 2, 4, 8]   # kv heads per tile: 0 = the regular entry point (one head), others through the self-test call
 
 
-def _step(w, monkeypatch, impl="0", hpc="0"):
+def _decode(hpc, *args, **kw):
+    if hpc == 0:
+        return ops.paged_attn_decode(*args, **kw)
+    with selftest.variant(decode_heads_per_tile=hpc):
+        return ops.paged_attn_decode(*args, **kw)
+
+
+def _step(w, hpc=0):
     """append + decode on the GPU, the same two calls on the oracle."""
-    monkeypatch.setenv("INFER_B200_DECODE_IMPL", impl)
-    monkeypatch.setenv("INFER_B200_DECODE_HPC", hpc)
     d = to_dev(w)
     ops.store_kvcache(d["k"], d["v"], d["k_cache"], d["v_cache"], d["slot_mapping"])
-    got = ops.paged_attn_decode(d["q"], d["k_cache"], d["v_cache"], d["context_lens"], d["block_tables"], w.scale)
+    got = _decode(hpc, d["q"], d["k_cache"], d["v_cache"], d["context_lens"], d["block_tables"], w.scale)
     torch.cuda.synchronize()
     kc, vc = w.k_cache.clone(), w.v_cache.clone()
     oracle.store_kvcache(w.k, w.v, kc, vc, w.slot_mapping)
@@ -26,27 +31,42 @@ def _step(w, monkeypatch, impl="0", hpc="0"):
     return got, want
 
 
-@pytest.mark.parametrize("impl,hpc", VARIANTS)
-def test_decode_config0(monkeypatch, impl, hpc):
-    got, want = _step(workloads.config0(), monkeypatch, impl, hpc)
-    assert_close(got, want, ATOL_BF16, RTOL_BF16, f"config0 impl={impl} hpc={hpc}")
+@pytest.mark.parametrize("hpc", VARIANTS)
+def test_decode_config0(hpc):
+    got, want = _step(workloads.config0(), hpc)
+    assert_close(got, want, ATOL_BF16, RTOL_BF16, f"config0 hpc={hpc}")
 
 
-@pytest.mark.parametrize("impl,hpc", VARIANTS)
-def test_decode_qwen3_8b_shape_reduced(monkeypatch, impl, hpc):
-    got, want = _step(workloads.config1(batch=12, lo=200, hi=3000), monkeypatch, impl, hpc)
-    assert_close(got, want, ATOL_BF16, RTOL_BF16, f"config1/12 impl={impl} hpc={hpc}")
+@pytest.mark.parametrize("hpc", VARIANTS)
+def test_decode_qwen3_8b_shape_reduced(hpc):
+    got, want = _step(workloads.config1(batch=12, lo=200, hi=3000), hpc)
+    assert_close(got, want, ATOL_BF16, RTOL_BF16, f"config1/12 hpc={hpc}")
 
 
-@pytest.mark.parametrize("impl,hpc", [("2", "0"), ("2", "8"), ("1", "0")])
-def test_decode_group8_shared_prefix_reduced(monkeypatch, impl, hpc):
+@pytest.mark.parametrize("hpc", [0, 2, 8])
+def test_decode_group8_shared_prefix_reduced(hpc):
     w = workloads.config4(batch=16, cap=3000)
-    got, want = _step(w, monkeypatch, impl, hpc)
-    assert_close(got, want, ATOL_BF16, RTOL_BF16, f"config4/16 impl={impl} hpc={hpc}")
+    got, want = _step(w, hpc)
+    assert_close(got, want, ATOL_BF16, RTOL_BF16, f"config4/16 hpc={hpc}")
+
+
+@pytest.mark.parametrize("hq,hkv", [(24, 8), (40, 8), (12, 2), (7, 1), (48, 8)])
+@pytest.mark.parametrize("hpc", [0, 2])
+def test_decode_any_group_size(hq, hkv, hpc):
+    """Query-head groups that are not a power of two (3, 5, 6, 7): the reference's decode call
+    (flash_attn_with_kvcache, infer/ops/attention.py:118-120) takes any Hq % Hkv == 0, and
+    Qwen3-14B is 40 query heads over 8 KV heads."""
+    if hkv % max(hpc, 1):
+        pytest.skip("heads per tile must divide the kv heads")
+    rng = np.random.default_rng(hq)
+    lens = rng.integers(100, 2600, size=10)
+    w = workloads._decode_workload("any-group", 77 + hq, hq, hkv, lens, workloads._pool_size(lens), "cpu")
+    got, want = _step(w, hpc)
+    assert_close(got, want, ATOL_BF16, RTOL_BF16, f"{hq}q/{hkv}kv hpc={hpc}")
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_decode_head_shards_match_full(monkeypatch, world):
+def test_decode_head_shards_match_full(world):
     """Each KV-head shard computed on its own equals the matching slice of the oracle."""
     w = workloads.config0()
     kc, vc = w.k_cache.clone(), w.v_cache.clone()
@@ -54,15 +74,13 @@ def test_decode_head_shards_match_full(monkeypatch, world):
     want = oracle.paged_decode(w.q, kc, vc, w.context_lens_tensor(), w.block_tables_tensor(), w.scale)
     per = w.n_q_heads // world
     for r in (0, world - 1):
-        got, _ = _step(w.shard(r, world), monkeypatch)
+        got, _ = _step(w.shard(r, world))
         assert_close(got, want[:, r * per:(r + 1) * per], ATOL_BF16, RTOL_BF16, f"shard {r}/{world}")
 
 
-@pytest.mark.parametrize("impl,hpc", VARIANTS)
-def test_decode_edge_lengths(monkeypatch, impl, hpc):
+@pytest.mark.parametrize("hpc", VARIANTS)
+def test_decode_edge_lengths(hpc):
     """Lengths around tile and page boundaries, an empty row, -1 padding, stale pool bytes."""
-    monkeypatch.setenv("INFER_B200_DECODE_IMPL", impl)
-    monkeypatch.setenv("INFER_B200_DECODE_HPC", hpc)
     lens = [1, 15, 16, 17, 0, 127, 128, 129, 255, 256, 257, 511, 513, 1]
     hq, hkv = 16, 8
     gen = torch.Generator().manual_seed(21)
@@ -86,15 +104,15 @@ def test_decode_edge_lengths(monkeypatch, impl, hpc):
     bt = torch.tensor(tables, dtype=torch.int32)
     cl = torch.tensor(lens, dtype=torch.int32)
     out = torch.full((len(lens), hq, 128), 7.0, dtype=torch.bfloat16, device="cuda")
-    ops.paged_attn_decode(q.cuda(), kc.cuda(), vc.cuda(), cl.cuda(), bt.cuda(), 0.09, out=out)
+    _decode(hpc, q.cuda(), kc.cuda(), vc.cuda(), cl.cuda(), bt.cuda(), 0.09, out=out)
     torch.cuda.synchronize()
     want = oracle.paged_decode(q, kc, vc, cl, bt, 0.09)
     live = cl > 0
-    assert_close(out[live.cuda()], want[live], ATOL_BF16, RTOL_BF16, f"edges impl={impl} hpc={hpc}")
+    assert_close(out[live.cuda()], want[live], ATOL_BF16, RTOL_BF16, f"edges hpc={hpc}")
     assert bool((out[~live.cuda()] == 7.0).all()), "row with context_len == 0 was written"
 
 
-def test_decode_golden_sdpa(golden, monkeypatch):
+def test_decode_golden_sdpa(golden):
     """The SDPA expectations of the golden fixture, keys laid out in scattered pages."""
     from infer_b200 import metadata
     g = golden["attention"]
@@ -122,7 +140,7 @@ def test_decode_golden_sdpa(golden, monkeypatch):
     assert_close(got, want, ATOL_BF16, RTOL_BF16, "golden sdpa")
 
 
-def test_decode_full_size_subset_against_oracle(monkeypatch):
+def test_decode_full_size_subset_against_oracle():
     """Config 2 at full size (64 sequences, ~1.2 GB of KV): every row finite; three
     sequences (shortest, longest, one in between) checked against the oracle, which only
     needs those sequences' pages on the CPU."""
@@ -145,7 +163,7 @@ def test_decode_full_size_subset_against_oracle(monkeypatch):
         assert_close(got[b:b + 1], want, ATOL_BF16, RTOL_BF16, f"full-size seq {b} (len {w.context_lens[b]})")
 
 
-def test_decode_in_cuda_graph(monkeypatch):
+def test_decode_in_cuda_graph():
     """append + decode captured once and replayed with new metadata in the static buffers,
     the way the reference replays its decode graphs (infer/engine/model_runner.py:135-152)."""
     w = workloads.config0()
@@ -177,9 +195,91 @@ def test_decode_in_cuda_graph(monkeypatch):
     assert_close(out, want, ATOL_BF16, RTOL_BF16, "graph replay")
 
 
+def _oracle_rows(w, got, rows, what):
+    """Compare the given sequences of a GPU-resident workload with the oracle, which only needs
+    those sequences' pages on the CPU."""
+    for b in rows:
+        pages = torch.tensor(w.block_tables[b])
+        kc, vc = w.k_cache[pages.cuda()].cpu(), w.v_cache[pages.cuda()].cpu()
+        local = torch.arange(len(pages), dtype=torch.int32)[None]
+        want = oracle.paged_decode(w.q[b:b + 1].cpu(), kc, vc, torch.tensor([w.context_lens[b]], dtype=torch.int32),
+                                   local, w.scale)
+        assert_close(got[b:b + 1], want, ATOL_BF16, RTOL_BF16, f"{what} seq {b} (len {w.context_lens[b]})")
+
+
+def test_decode_long_context_full_size_against_oracle():
+    """The long-context configuration at full size on one GPU (batch 256, 64q/8kv heads, contexts up
+    to 32768 = 128 pages, half the batch sharing the pages of a 2048-token prefix): the longest
+    sequence (its (sequence, head) rows span many thread blocks and go through the ticketed merge),
+    two sequences of the shared-prefix half, the shortest and a median one against the oracle."""
+    w = workloads.config4(device="cuda", longest_at_cap=True)
+    assert max(w.context_lens) == 32768
+    cl, bt = w.context_lens_tensor().cuda(), w.block_tables_tensor().cuda()
+    ops.store_kvcache(w.k, w.v, w.k_cache, w.v_cache, w.slot_mapping.cuda())
+    got = ops.paged_attn_decode(w.q, w.k_cache, w.v_cache, cl, bt, w.scale)
+    torch.cuda.synchronize()
+    assert torch.isfinite(got.float()).all()
+    order = np.argsort(w.context_lens)
+    shared = [b for b in range(w.batch // 2)]
+    rows = {int(order[-1]), int(order[0]), int(order[len(order) // 2]), shared[0], shared[-1]}
+    assert w.block_tables[shared[0]][:8] == w.block_tables[shared[-1]][:8]      # the prefix pages really are shared
+    _oracle_rows(w, got, sorted(rows), "long-context full size")
+    # a second pass over the same scratch must give the same bits (tickets were left at zero)
+    again = ops.paged_attn_decode(w.q, w.k_cache, w.v_cache, cl, bt, w.scale)
+    torch.cuda.synchronize()
+    assert torch.equal(got, again)
+
+
+def test_decode_steps_chained_without_host_sync():
+    """advance -> append -> decode, step after step on one stream with no host synchronisation in
+    between, across a page boundary: the attention kernel's prologue reads context_lens while the
+    kernels in front may still be in flight (programmatic dependent launch), so every step's result
+    depends on the launches being ordered correctly."""
+    from infer_b200.metadata import DecodeState
+    from infer_b200.sequence import Sequence
+    hq, hkv, nb, steps = 16, 8, 24, 24
+    gen = torch.Generator().manual_seed(5)
+    start = [250, 255, 3, 511, 256, 100]                      # several rows cross into a new page within the steps
+    kc = torch.randn(nb, 256, hkv, 128, generator=gen).bfloat16()
+    vc = torch.randn(nb, 256, hkv, 128, generator=gen).bfloat16()
+    perm = torch.randperm(nb, generator=gen).tolist()
+    seqs, at = [], 0
+    for n in start:
+        s = Sequence(list(range(n)))
+        need = -(-(n + steps) // 256)
+        s.block_table = perm[at:at + need]
+        at += need
+        seqs.append(s)
+    state = DecodeState(len(start), 4, 256, "cuda")
+    state.load(seqs)
+    qs = torch.randn(steps, len(start), hq, 128, generator=gen).bfloat16()
+    ks = torch.randn(steps, len(start), hkv, 128, generator=gen).bfloat16()
+    vs = torch.randn(steps, len(start), hkv, 128, generator=gen).bfloat16()
+    dq, dk, dv, dkc, dvc = qs.cuda(), ks.cuda(), vs.cuda(), kc.cuda(), vc.cuda()
+    outs = torch.zeros(steps, len(start), hq, 128, dtype=torch.bfloat16, device="cuda")
+    ops.paged_attn_decode(dq[0], dkc, dvc, torch.ones(len(start), dtype=torch.int32, device="cuda"),
+                          state.block_tables, 0.09)           # sizes the scratch before the chain
+    torch.cuda.synchronize()
+    for t in range(steps):
+        state.advance()
+        ops.store_kvcache(dk[t], dv[t], dkc, dvc, state.slot_mapping)
+        ops.paged_attn_decode(dq[t], dkc, dvc, state.context_lens, state.block_tables, 0.09, out=outs[t])
+    torch.cuda.synchronize()
+    lens = list(start)
+    bt = torch.tensor([s.block_table + [-1] * (4 - len(s.block_table)) for s in seqs], dtype=torch.int32)
+    for t in range(steps):
+        lens = [n + 1 for n in lens]
+        slots = torch.tensor([s.block_table[(n - 1) // 256] * 256 + (n - 1) % 256 for s, n in zip(seqs, lens)],
+                             dtype=torch.int32)
+        oracle.store_kvcache(ks[t], vs[t], kc, vc, slots)
+        want = oracle.paged_decode(qs[t], kc, vc, torch.tensor(lens, dtype=torch.int32), bt, 0.09)
+        assert_close(outs[t], want, ATOL_BF16, RTOL_BF16, f"chained step {t}")
+    assert torch.equal(dkc.cpu().view(torch.int16), kc.view(torch.int16))
+
+
 def test_decode_rejects_bad_arguments():
     kc = torch.zeros(2, 256, 8, 128, dtype=torch.bfloat16, device="cuda")
-    q = torch.zeros(1, 24, 128, dtype=torch.bfloat16, device="cuda")       # 24 % 8 == 0 but group 3
+    q = torch.zeros(1, 72, 128, dtype=torch.bfloat16, device="cuda")       # 72 % 8 == 0 but 9 query heads per kv head
     cl = torch.ones(1, dtype=torch.int32, device="cuda")
     bt = torch.zeros(1, 1, dtype=torch.int32, device="cuda")
     with pytest.raises(RuntimeError, match="geometry"):

@@ -4,7 +4,7 @@ import pytest
 import torch
 
 from gpu_util import ATOL_FP8, RTOL_FP8, assert_close, bits_equal
-from infer_b200 import ops, workloads
+from infer_b200 import ops, selftest, workloads
 from infer_b200.metadata import chunk_slots
 from oracle import paged_kv_oracle as oracle
 
@@ -102,16 +102,22 @@ def test_fp8_append_extreme_magnitudes():
     assert bits_equal(cpu[0], gpu[0]) and bits_equal(cpu[1], gpu[1]), "bytes differ"
 
 
-@pytest.mark.parametrize("impl", ["0", "1"], ids=["tma", "plain-loads"])
-def test_fp8_decode_step(impl, monkeypatch):
-    monkeypatch.setenv("INFER_B200_DECODE_IMPL", impl)
+def _decode(hpc, *args, **kw):
+    if hpc == 0:
+        return ops.paged_attn_decode(*args, **kw)
+    with selftest.variant(decode_heads_per_tile=hpc):
+        return ops.paged_attn_decode(*args, **kw)
+
+
+@pytest.mark.parametrize("hpc", [0, 1, 2, 8], ids=["default-4-heads", "1-head", "2-heads", "8-heads"])
+def test_fp8_decode_step(hpc):
     w = workloads.config3()
     cpu, gpu = _fill_both(w, 3)
     # the decode step's own append, then attention
     oracle.store_kvcache_fp8(w.k, w.v, *cpu, w.slot_mapping)
     ops.store_kvcache(w.k.cuda(), w.v.cuda(), gpu[0], gpu[1], w.slot_mapping.cuda(), gpu[2], gpu[3])
     cl, bt = w.context_lens_tensor(), w.block_tables_tensor()
-    got = ops.paged_attn_decode(w.q.cuda(), gpu[0], gpu[1], cl.cuda(), bt.cuda(), w.scale, k_scale=gpu[2], v_scale=gpu[3])
+    got = _decode(hpc, w.q.cuda(), gpu[0], gpu[1], cl.cuda(), bt.cuda(), w.scale, k_scale=gpu[2], v_scale=gpu[3])
     torch.cuda.synchronize()
     assert bits_equal(cpu[0], gpu[0]) and torch.equal(cpu[2], gpu[2].cpu())
     want = oracle.paged_decode(w.q, cpu[0], cpu[1], cl, bt, w.scale, cpu[2], cpu[3])
@@ -119,14 +125,13 @@ def test_fp8_decode_step(impl, monkeypatch):
 
 
 @pytest.mark.parametrize("hkv", [2, 1, 3, 4], ids=["2-heads-per-tile", "1-head", "3-heads-odd", "4-heads-per-tile"])
-@pytest.mark.parametrize("impl", ["0", "1"], ids=["tma", "plain-loads"])
-def test_fp8_decode_group8_long_contexts(impl, hkv, monkeypatch):
-    """8 query heads per KV head, contexts over several pages with different scales per page,
-    lengths around the 16/32/64/128/256-token boundaries of the FP8 tiles; the KV head count
+@pytest.mark.parametrize("group", [8, 5, 3])
+def test_fp8_decode_long_contexts_any_group(group, hkv):
+    """8, 5 or 3 query heads per KV head, contexts over several pages with different scales per
+    page, lengths around the 16/32/64/128/256-token boundaries of the FP8 tiles; the KV head count
     decides how many heads share a tile (4, 2, or 1 when it is odd)."""
-    monkeypatch.setenv("INFER_B200_DECODE_IMPL", impl)
     gen = torch.Generator().manual_seed(91)
-    hq, nb = 8 * hkv, 40
+    hq, nb = group * hkv, 40
     lens = [1, 17, 255, 256, 257, 600, 1300, 33, 64, 65, 129]
     cpu = _empty_pools(nb, hkv, "cpu")
     gpu = _empty_pools(nb, hkv, "cuda")
@@ -152,4 +157,74 @@ def test_fp8_decode_group8_long_contexts(impl, hkv, monkeypatch):
     torch.cuda.synchronize()
     assert bits_equal(cpu[0], gpu[0]) and bits_equal(cpu[1], gpu[1])
     want = oracle.paged_decode(q, cpu[0], cpu[1], cl, bt, 0.09, cpu[2], cpu[3])
-    assert_close(got, want, ATOL_FP8, RTOL_FP8, f"fp8 decode, group 8, impl {impl}")
+    assert_close(got, want, ATOL_FP8, RTOL_FP8, f"fp8 decode, group {group}, {hkv} kv heads")
+
+
+def test_fp8_steps_scales_grow_under_later_reads():
+    """Prefill a few sequences, then 300 decode-shape appends (one row per sequence and step) in
+    which occasional outlier rows raise a page's scale, so that rows written many steps earlier are
+    re-encoded and later decode passes read them through the new scale.  Pools and scales must stay
+    bit-exact against the oracle stepped the same way, and every tenth step's attention output
+    within the FP8 tolerance of the oracle's."""
+    gen = torch.Generator().manual_seed(1234)
+    hkv, hq, nb, steps = 4, 16, 24, 300
+    start = [200, 255, 40, 511, 1]
+    perm = torch.randperm(nb, generator=gen).tolist()
+    cpu = _empty_pools(nb, hkv, "cpu")
+    gpu = _empty_pools(nb, hkv, "cuda")
+    tables, at = [], 0
+    for n in start:
+        need = -(-(n + steps) // 256)
+        pages = perm[at:at + need]
+        at += need
+        tables.append(pages)
+        k = torch.randn(n, hkv, 128, generator=gen).bfloat16()
+        v = torch.randn(n, hkv, 128, generator=gen).bfloat16()
+        slots = torch.tensor(chunk_slots(pages, 0, n, 256), dtype=torch.int32)
+        oracle.store_kvcache_fp8(k, v, *cpu, slots)
+        ops.store_kvcache(k.cuda(), v.cuda(), gpu[0], gpu[1], slots.cuda(), gpu[2], gpu[3])
+    width = max(len(t) for t in tables)
+    bt = torch.tensor([t + [-1] * (width - len(t)) for t in tables], dtype=torch.int32)
+    bt_d = bt.cuda()
+    lens = list(start)
+    for step in range(steps):
+        lens = [n + 1 for n in lens]
+        k = torch.randn(len(start), hkv, 128, generator=gen)
+        v = torch.randn(len(start), hkv, 128, generator=gen)
+        if step % 7 == 3:                                   # an outlier row: this page's scale has to grow
+            row = step % len(start)
+            k[row] *= 6.0 + step / 20.0
+            v[row, step % hkv] *= 9.0
+        k, v = k.bfloat16(), v.bfloat16()
+        slots = torch.tensor([t[(n - 1) // 256] * 256 + (n - 1) % 256 for t, n in zip(tables, lens)], dtype=torch.int32)
+        oracle.store_kvcache_fp8(k, v, *cpu, slots)
+        ops.store_kvcache(k.cuda(), v.cuda(), gpu[0], gpu[1], slots.cuda(), gpu[2], gpu[3])
+        if step % 10 == 9 or step == steps - 1:
+            q = torch.randn(len(start), hq, 128, generator=gen).bfloat16()
+            cl = torch.tensor(lens, dtype=torch.int32)
+            got = ops.paged_attn_decode(q.cuda(), gpu[0], gpu[1], cl.cuda(), bt_d, 0.09, k_scale=gpu[2], v_scale=gpu[3])
+            torch.cuda.synchronize()
+            assert torch.equal(cpu[2], gpu[2].cpu()) and torch.equal(cpu[3], gpu[3].cpu()), f"scales differ at step {step}"
+            assert bits_equal(cpu[0], gpu[0]) and bits_equal(cpu[1], gpu[1]), f"bytes differ at step {step}"
+            want = oracle.paged_decode(q, cpu[0], cpu[1], cl, bt, 0.09, cpu[2], cpu[3])
+            assert_close(got, want, ATOL_FP8, RTOL_FP8, f"fp8 decode after step {step}")
+
+
+def test_fp8_outlier_stress_qwen3_8b_shape_reduced():
+    """The 1 %-outliers-times-20 stress of the FP8 configuration on the Qwen3-8B head layout
+    (32q/8kv) with contexts of several pages: append bit-exact, decode within tolerance."""
+    w = workloads.config1(batch=10, lo=300, hi=2600, seed=1013)
+    gen = torch.Generator().manual_seed(1013)
+    for t in (w.k, w.k_cache):
+        spike = torch.rand(t.shape, generator=gen) < 0.01
+        t[spike] = (t[spike].float() * 20).to(t.dtype)
+    cpu, gpu = _fill_both(w, 3)
+    oracle.store_kvcache_fp8(w.k, w.v, *cpu, w.slot_mapping)
+    ops.store_kvcache(w.k.cuda(), w.v.cuda(), gpu[0], gpu[1], w.slot_mapping.cuda(), gpu[2], gpu[3])
+    cl, bt = w.context_lens_tensor(), w.block_tables_tensor()
+    got = ops.paged_attn_decode(w.q.cuda(), gpu[0], gpu[1], cl.cuda(), bt.cuda(), w.scale, k_scale=gpu[2], v_scale=gpu[3])
+    torch.cuda.synchronize()
+    assert torch.equal(cpu[2], gpu[2].cpu()) and torch.equal(cpu[3], gpu[3].cpu())
+    assert bits_equal(cpu[0], gpu[0]) and bits_equal(cpu[1], gpu[1])
+    want = oracle.paged_decode(w.q, cpu[0], cpu[1], cl, bt, w.scale, cpu[2], cpu[3])
+    assert_close(got, want, ATOL_FP8, RTOL_FP8, "fp8 outlier stress, 32q/8kv")

@@ -6,17 +6,21 @@ import pytest
 import torch
 
 from gpu_util import ATOL_BF16, RTOL_BF16, assert_close, to_dev
-from infer_b200 import ops, workloads
+from infer_b200 import ops, selftest, workloads
 from oracle import paged_kv_oracle as oracle
 
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=["1", "2"], ids=["mma", "tcgen05"], autouse=True)
-def prefill_impl(request, monkeypatch):
-    """Every test of this file runs on both prefill kernels."""
-    monkeypatch.setenv("INFER_B200_PREFILL_IMPL", request.param)
-    return request.param
+@pytest.fixture(params=[1, 0], ids=["mma", "tcgen05"], autouse=True)
+def prefill_kernel(request):
+    """Every test of this file runs on both prefill kernels: the tcgen05 kernel through the
+    regular entry points, the mma.sync cross-check kernel through the self-test ones."""
+    if request.param == 0:
+        yield 0
+    else:
+        with selftest.variant(prefill_kernel=1):
+            yield 1
 
 
 def _run(w):
@@ -75,28 +79,40 @@ def test_prefill_odd_group_size():
     assert_close(got, want, ATOL_BF16, RTOL_BF16, "prefill, group 3")
 
 
-def test_prefill_full_size_two_kernels_and_decode_agree(prefill_impl, monkeypatch):
-    """The benchmark configuration itself (16 sequences, prefix up to 4096, chunk 2048), too large
-    for the CPU oracle: the tcgen05 kernel and the mma.sync kernel, two independent programs, must
-    agree within the bf16 tolerance on every row, and the last row of every chunk must equal the
-    decode kernel's answer for that position."""
-    if prefill_impl != "2":
+def test_prefill_full_size_against_oracle(prefill_kernel):
+    """The benchmark configuration itself (16 sequences, prefix up to 4096, chunk 2048).  Two whole
+    sequences - the one with the longest prefix (48 key tiles per row, thousands of keys through
+    the lazy rescale) and the one with the shortest - are compared with the CPU oracle, which only
+    needs those sequences' pages; the mma.sync kernel, an independent program, must agree with the
+    tcgen05 kernel on every row; and the last row of every chunk must equal the decode kernel's
+    answer for that position."""
+    if prefill_kernel != 0:
         pytest.skip("one run covers both kernels")
     w = workloads.config2(device="cuda")
     cu_q, cu_k = (t.cuda() for t in w.cu_seqlens())
     bt = w.block_tables_tensor().cuda()
     ops.store_kvcache(w.k, w.v, w.k_cache, w.v_cache, w.slot_mapping.cuda())
-    outs = {}
-    for impl in ("2", "1"):
-        monkeypatch.setenv("INFER_B200_PREFILL_IMPL", impl)
-        outs[impl] = ops.paged_attn_prefill(w.q, w.k_cache, w.v_cache, cu_q, cu_k, max(w.new_lens), max(w.context_lens),
-                                            w.scale, bt)
+    args = (w.q, w.k_cache, w.v_cache, cu_q, cu_k, max(w.new_lens), max(w.context_lens), w.scale, bt)
+    got = ops.paged_attn_prefill(*args)
+    with selftest.variant(prefill_kernel=1):
+        other = ops.paged_attn_prefill(*args)
     torch.cuda.synchronize()
-    assert_close(outs["2"], outs["1"], ATOL_BF16, RTOL_BF16, "tcgen05 vs mma.sync, full size")
+    assert_close(got, other, ATOL_BF16, RTOL_BF16, "tcgen05 vs mma.sync, full size")
+    order = np.argsort(w.context_lens)
+    cu = cu_q.cpu()
+    for b in (int(order[-1]), int(order[0])):
+        pages = torch.tensor(w.block_tables[b])
+        kc, vc = w.k_cache[pages.cuda()].cpu(), w.v_cache[pages.cuda()].cpu()
+        rows = slice(int(cu[b]), int(cu[b + 1]))
+        n_new, n_ctx = w.new_lens[b], w.context_lens[b]
+        want = oracle.paged_prefill(w.q[rows].cpu(), kc, vc, torch.tensor([0, n_new], dtype=torch.int32),
+                                    torch.tensor([0, n_ctx], dtype=torch.int32),
+                                    torch.arange(len(pages), dtype=torch.int32)[None], w.scale)
+        assert_close(got[rows], want, ATOL_BF16, RTOL_BF16, f"full-size prefill seq {b} (ctx {n_ctx}) vs oracle")
     last = (cu_q[1:] - 1).long()
     dec = ops.paged_attn_decode(w.q[last].contiguous(), w.k_cache, w.v_cache,
                                 torch.tensor(w.context_lens, dtype=torch.int32, device="cuda"), bt, w.scale)
-    assert_close(outs["2"][last], dec, ATOL_BF16, RTOL_BF16, "last chunk rows vs decode, full size")
+    assert_close(got[last], dec, ATOL_BF16, RTOL_BF16, "last chunk rows vs decode, full size")
 
 
 def test_prefill_last_row_equals_decode():

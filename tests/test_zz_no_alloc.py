@@ -34,6 +34,8 @@ def _noalloc(w, dev):
                                         w.batch, w.n_q_heads, w.scale, stream)
     assert rc == 0, lib.infer_strerror(rc).decode()
     torch.cuda.synchronize()
+    # a NULL workspace asks for the status word of the built-in array: no bounded wait ran out
+    assert lib.infer_paged_decode_status(None, stream) == 0
     return out, want
 
 
