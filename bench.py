@@ -545,9 +545,9 @@ def main():
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "long"],
                     help="decode = the full line; prefill = only the paged chunked-prefill configuration (single GPU, "
                          "used for profiler captures); long = only the long-context configuration as the headline")
-    ap.add_argument("--only", default="", help="comma-separated sub-benchmarks to keep (prefill,fp8,fused,strong,flash); "
-                                               "default: all")
-    ap.add_argument("--fp8", action="store_true", help="with --profile: also run the e4m3 legs")
+    ap.add_argument("--only", default="", help="comma-separated sub-benchmarks to run (prefill,fp8,fused,strong,flash); "
+                                               "default: all, or none with --profile")
+    ap.add_argument("--fp8", action="store_true", help="same as adding fp8 to --only")
     ap.add_argument("--batch", type=int, default=BASE_BATCH,
                     help="sequences per GPU share (default 64 = the benchmark configuration; smaller values "
                          "give the small case used for profiler captures)")
@@ -587,9 +587,11 @@ def main():
         return
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-    want = set(filter(None, args.only.split(","))) or {"prefill", "fp8", "fused", "strong", "flash"}
-    if args.profile:
-        want = {"fp8"} if args.fp8 else set()
+    want = set(filter(None, args.only.split(",")))
+    if not want and not args.profile:
+        want = {"prefill", "fp8", "fused", "strong", "flash"}
+    if args.fp8:
+        want.add("fp8")
 
     def barrier():
         if world > 1:

@@ -77,7 +77,11 @@ INFER_API int infer_kv_pool_destroy(infer_kv_pool_t* pool);
  * row i of k and v ([n_tokens, n_kv_heads, 128] bf16, row pitch k_row_stride / v_row_stride
  * ELEMENTS, so column slices of a fused qkv output are accepted as the reference accepts
  * them) goes to flat slot slot_mapping[i].  An e4m3 pool quantises on write with one scale
- * per (page, kv head) and needs infer_kv_append_workspace_bytes() of scratch. */
+ * per (page, kv head) and needs infer_kv_append_workspace_bytes() of 16-byte aligned scratch
+ * that belongs to THIS pool: the caller zero-fills it once before its first use, every call
+ * leaves it in the state the next call on the same pool expects, and it must be zero-filled
+ * again before it serves a pool of another geometry.  Appends to one pool that share the
+ * scratch must not overlap on the GPU.  bf16 pools need no scratch (NULL, 0). */
 INFER_API int infer_kv_append(const infer_kv_pool_t* pool, const void* k, const void* v,
                     int64_t k_row_stride, int64_t v_row_stride, const int32_t* slot_mapping,
                     int64_t n_tokens, void* workspace, size_t workspace_bytes, void* stream);

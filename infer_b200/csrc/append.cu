@@ -5,15 +5,16 @@
 // e4m3 pools: the scale of a (page, head) must be final before any of its new rows is
 // quantised.  A small kernel first cuts the token list into runs (consecutive tokens going to
 // consecutive slots of one page) and finds out whether any page receives more than one run.
-//   * No page does (every prefill chunk, every decode step): fp8_run_kernel gives each (run, head,
-//     k|v) to one thread block, which reads the run's rows ONCE into registers, takes their amax,
-//     settles the scale (re-encoding the page's older rows when a positive scale grew) and
-//     quantises from the registers.
+//   * No page does (every prefill chunk, every decode step): fp8_run_kernel's persistent thread
+//     blocks take (run, head, k|v) units off the list the first kernel wrote; a block reads its
+//     run's rows ONCE into registers, takes their amax, settles the scale (re-encoding the page's
+//     older rows when a positive scale grew) and quantises from the registers.
 //   * Otherwise (slots scattered over pages): three kernels - collect the new rows' amax / 448 per
 //     (page, head) with atomics; raise the scales and re-encode pages whose scale grew; write the
 //     new rows - on strips of 8 tokens per warp.
 // Both ways give the bytes and scales of the CPU oracle bit for bit, whatever the scheduling.
 // All five kernels are always launched; those of the way not taken return at once.
+#include <atomic>
 #include <climits>
 
 #include "common.cuh"
@@ -72,7 +73,7 @@ struct Fp8Side {
 };
 
 // Control words at the end of the workspace.
-enum { kCtlConflictAcc = 0, kCtlDone = 1, kCtlConflict = 2, kCtlWords = 16 };
+enum { kCtlConflictAcc = 0, kCtlDone = 1, kCtlConflict = 2, kCtlRunAcc = 3, kCtlRuns = 4, kCtlWords = 16 };
 
 struct Fp8Args {
     Fp8Side k, v;
@@ -83,6 +84,8 @@ struct Fp8Args {
     int block_size;
     uint64_t page_magic;           // ceil(2^64 / block_size): page = mulhi(slot, page_magic), exact for slot < 2^32
     int* count;                    // workspace [num_blocks]: runs of this call per page (zero between calls)
+    int2* run_list;                // workspace [num_blocks]: (first token, its slot) of every run (valid when no page got two)
+    int num_blocks;
     int* ctl;                      // workspace [kCtlWords]: see the enum above
 
     __device__ __forceinline__ int64_t page_of(int64_t slot) const {
@@ -434,13 +437,28 @@ __device__ __forceinline__ bool is_run_start(const Fp8Args& a, int64_t i, int& s
     return !(slot_valid(a, prev) && prev + 1 == slot && a.page_of(prev) == a.page_of(slot));
 }
 
-// Counts the runs every page receives.  The block that finishes last publishes whether any page
-// got more than one (kCtlConflict, written afresh by every call) and clears the two accumulators.
+// Counts the runs every page receives and lists the runs' first tokens (a page that gets one run
+// at most means at most num_blocks runs, so the list has room for all of them in the case that
+// uses it).  The block that finishes last publishes whether any page got more than one run
+// (kCtlConflict) and how many runs there are (kCtlRuns) - both written afresh by every call - and
+// clears the accumulators.
 __global__ void __launch_bounds__(256) fp8_classify_kernel(Fp8Args a) {
     pdl_launch_dependents();
     const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    int conflict = 0, slot;
-    if (i < a.n_tokens && is_run_start(a, i, slot)) conflict = atomicAdd(a.count + a.page_of(slot), 1) > 0;
+    const int lane = threadIdx.x & 31;
+    int slot = -1;
+    const bool starts = i < a.n_tokens && is_run_start(a, i, slot);
+    int conflict = 0;
+    if (starts) conflict = atomicAdd(a.count + a.page_of(slot), 1) > 0;
+    // one atomic per warp for the list positions
+    const uint32_t ballot = __ballot_sync(0xffffffffu, starts);
+    int base = 0;
+    if (ballot && lane == 0) base = atomicAdd(a.ctl + kCtlRunAcc, __popc(ballot));
+    base = __shfl_sync(0xffffffffu, base, 0);
+    if (starts) {
+        const int idx = base + __popc(ballot & ((1u << lane) - 1));
+        if (idx < a.num_blocks) a.run_list[idx] = make_int2(int(i), slot);
+    }
     conflict = __syncthreads_or(conflict);
     if (threadIdx.x == 0) {
         if (conflict) atomicOr(a.ctl + kCtlConflictAcc, 1);
@@ -448,47 +466,49 @@ __global__ void __launch_bounds__(256) fp8_classify_kernel(Fp8Args a) {
         if (atomicAdd(a.ctl + kCtlDone, 1) == int(gridDim.x) - 1) {
             __threadfence();
             a.ctl[kCtlConflict] = atomicExch(a.ctl + kCtlConflictAcc, 0);
+            a.ctl[kCtlRuns] = atomicExch(a.ctl + kCtlRunAcc, 0);
             a.ctl[kCtlDone] = 0;
         }
     }
 }
 
-// One thread block per (slice of the token list, head, k|v): it looks for run starts in its slice
-// and handles each run it finds from end to end.  A row of one head is 256 bytes = 16 lanes x 16
-// bytes, THREADS / 16 rows per load instruction, 16 loads in flight per thread: 256 threads hold a
-// whole 256-row run (64 KiB) in registers, so the rows are read from memory once.  Runs longer than
-// the registers hold (32 threads: 32 rows) read the remainder a second time, from L2.
+// Persistent thread blocks walk the units (run, head, k|v), unit u going to block u mod gridDim.x,
+// the 2 * Hkv units of a run side by side so that neighbouring blocks read neighbouring 256-byte
+// pieces of the same rows at the same time.  A row of one head is 256 bytes = 16 lanes x 16 bytes,
+// THREADS / 16 rows per load instruction, 16 loads in flight per thread: 256 threads hold a whole
+// 256-row run (64 KiB) in registers, so the rows are read from memory once.  Runs longer than the
+// registers hold (32 threads: 32 rows) read the remainder a second time, from L2.
 template <int THREADS>
-__global__ void __launch_bounds__(THREADS, THREADS == 256 ? 2 : 16) fp8_run_kernel(Fp8Args a, int slice_len) {
+__global__ void __launch_bounds__(THREADS, THREADS == 256 ? 2 : 16) fp8_run_kernel(Fp8Args a) {
     constexpr int kRowsPerLoad = THREADS / 16, kHeld = 16 * kRowsPerLoad, kWarps = THREADS / 32;
-    __shared__ int s_start[64], s_n, s_len;
+    __shared__ int s_len;
     __shared__ float s_red[kWarps], s_scale, s_ratio;
     pdl_launch_dependents();
-    pdl_wait();                                   // the run counts and the verdict of the kernel in front
-    const bool conflict = a.ctl[kCtlConflict] != 0;
-    if (conflict && blockIdx.y != 0) return;      // the three strip kernels take over; row 0 still clears the counts
+    pdl_wait();                                   // the run list, the counts and the verdict of the kernel in front
     const int tid = threadIdx.x;
-    const int head = int(blockIdx.y >> 1);
-    const Fp8Side side = (blockIdx.y & 1) ? a.v : a.k;
-    const int64_t tok0 = int64_t(blockIdx.x) * slice_len;
-    if (tid == 0) s_n = 0;
-    __syncthreads();
-    for (int t = tid; t < slice_len; t += THREADS) {
-        int slot;
-        if (tok0 + t < a.n_tokens && is_run_start(a, tok0 + t, slot)) {
-            s_start[atomicAdd(&s_n, 1)] = t;
-            if (blockIdx.y == 0) a.count[a.page_of(slot)] = 0;      // nobody reads the counts any more
+    if (a.ctl[kCtlConflict] != 0) {
+        // some page got several runs: the three strip kernels do the work; all that is left to do here
+        // is to put the run counts back to zero
+        const int64_t stride = int64_t(gridDim.x) * THREADS;
+        for (int64_t i = int64_t(blockIdx.x) * THREADS + tid; i < a.n_tokens; i += stride) {
+            int slot;
+            if (is_run_start(a, i, slot)) a.count[a.page_of(slot)] = 0;
         }
+        return;
     }
-    __syncthreads();
-    if (conflict) return;
-    const int n_runs = s_n;
+    const int sides = 2 * a.n_kv_heads;
+    const int64_t n_units = int64_t(a.ctl[kCtlRuns]) * sides;
     const int lane16 = tid & 15, rsub = tid >> 4;
     const int64_t dst_pitch = int64_t(a.n_kv_heads) * kHeadDim;
-    for (int r = 0; r < n_runs; ++r) {
-        const int64_t start = tok0 + s_start[r];
-        const int slot0 = __ldg(a.slot_mapping + start);
+    for (int64_t unit = blockIdx.x; unit < n_units; unit += gridDim.x) {
+        const int run = int(unit / sides), y = int(unit - int64_t(run) * sides);
+        const int head = y >> 1;
+        const Fp8Side side = (y & 1) ? a.v : a.k;
+        const int2 first = a.run_list[run];
+        const int64_t start = first.x;
+        const int slot0 = first.y;
         const int64_t page = a.page_of(slot0);
+        if (y == 0 && tid == 0) a.count[page] = 0;          // nobody reads the counts any more
         // length of the run: the first offset whose token does not continue it
         int len = 1;
         for (int base = 1;; base += THREADS) {
@@ -517,6 +537,9 @@ __global__ void __launch_bounds__(THREADS, THREADS == 256 ? 2 : 16) fp8_run_kern
             raw[j] = make_uint4(0, 0, 0, 0);
             if (row < len) raw[j] = __ldg(reinterpret_cast<const uint4*>(src + (start + row) * side.pitch));
         }
+        // the page's present scale travels with the rows
+        const int64_t e = page * a.n_kv_heads + head;
+        const float old = side.scale[e];
 #pragma unroll
         for (int j = 0; j < 16; ++j) best = __hmax2(best, amax8(raw[j]));
         for (int row = kHeld + rsub; row < len; row += kRowsPerLoad)
@@ -529,8 +552,6 @@ __global__ void __launch_bounds__(THREADS, THREADS == 256 ? 2 : 16) fp8_run_kern
         if (tid == 0) {
 #pragma unroll
             for (int w = 1; w < kWarps; ++w) m = fmaxf(m, s_red[w]);
-            const int64_t e = page * a.n_kv_heads + head;
-            const float old = side.scale[e];
             float s = old, ratio = -1.0f;
             if (m > 0.0f) {
                 const float c = __fdiv_rn(m, 448.0f);
@@ -571,8 +592,237 @@ __global__ void __launch_bounds__(THREADS, THREADS == 256 ? 2 : 16) fp8_run_kern
         for (int row = kHeld + rsub; row < len; row += kRowsPerLoad)
             *reinterpret_cast<uint2*>(dst + row * dst_pitch) =
                 div.quantise8(__ldg(reinterpret_cast<const uint4*>(src + (start + row) * side.pitch)));
-        __syncthreads();                          // s_red, s_scale and s_ratio are reused by the next run
+        __syncthreads();                          // s_red, s_scale and s_ratio are reused by the next unit
     }
+}
+
+
+// --------------------------------------------------------------------------- runs, staged in shared memory
+// The same units as fp8_run_kernel for pools whose pages hold 256 tokens, with asynchronous copies
+// doing the loads.  A scout warp works out units ahead of time (first token, length, the page's
+// present scale) into a small ring; sixteen worker warps issue the 16-byte asynchronous copies
+// (cp.async) of the unit two places ahead into one of three 64 KiB shared-memory buffers, then
+// take the amax of the current buffer, settle the scale, quantise from the buffer and store.  The
+// rows of the next two units are in flight while one is being quantised, so the kernel is bound by
+// the quantisation arithmetic or by HBM, not by the latency of either.
+constexpr int kStagedRows = 256;
+constexpr int kStagedBufBytes = kStagedRows * 256;
+constexpr int kStagedBufs = 3;
+constexpr int kStagedMetaSlots = 4;
+constexpr int kStagedWorkerWarps = 16;
+constexpr int kStagedWorkers = kStagedWorkerWarps * 32;
+constexpr int kStagedThreads = kStagedWorkers + 32;
+
+struct StagedMeta {
+    int start;        // first token of the run
+    int len;          // rows of the unit (1..256)
+    int slot0;
+    int head;
+    int side;         // 0 = k, 1 = v
+    float old_scale;
+    int pad[2];
+};
+
+struct StagedSmem {
+    static constexpr int meta = kStagedBufs * kStagedBufBytes;
+    static constexpr int bars = meta + kStagedMetaSlots * int(sizeof(StagedMeta));
+    static constexpr int red = bars + 2 * kStagedMetaSlots * 8;
+    static constexpr int total = red + (kStagedWorkerWarps + 2) * 4;
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void worker_bar() { asm volatile("bar.sync 1, %0;" ::"n"(kStagedWorkers) : "memory"); }
+// barrier over the worker threads that also tells every one of them whether all of them passed `ok`
+__device__ __forceinline__ bool __syncthreads_and_workers(bool ok) {
+    uint32_t all;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\t"
+        "bar.red.and.pred q, 1, %2, p;\n\t"
+        "selp.u32 %0, 1, 0, q;\n\t}"
+        : "=r"(all)
+        : "r"(uint32_t(ok)), "n"(kStagedWorkers)
+        : "memory");
+    return all != 0;
+}
+
+__global__ void __launch_bounds__(kStagedThreads, 1) fp8_run_staged_kernel(Fp8Args a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    volatile StagedMeta* s_meta = reinterpret_cast<volatile StagedMeta*>(smem + StagedSmem::meta);
+    float* s_red = reinterpret_cast<float*>(smem + StagedSmem::red);      // [warps] maxima, then scale, ratio
+    const uint32_t base = smem_u32(smem);
+    const uint32_t full0 = base + StagedSmem::bars, empty0 = full0 + kStagedMetaSlots * 8;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        for (int s = 0; s < kStagedMetaSlots; ++s) {
+            mbar_init(full0 + s * 8, 1);
+            mbar_init(empty0 + s * 8, kStagedWorkerWarps);
+        }
+        fence_mbar_init();
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+    pdl_wait();                                   // the run list, the counts and the verdict of the kernel in front
+    if (a.ctl[kCtlConflict] != 0) {
+        // the three strip kernels do the work; all that is left to do here is to zero the run counts
+        const int64_t stride = int64_t(gridDim.x) * kStagedThreads;
+        for (int64_t i = int64_t(blockIdx.x) * kStagedThreads + tid; i < a.n_tokens; i += stride) {
+            int slot;
+            if (is_run_start(a, i, slot)) a.count[a.page_of(slot)] = 0;
+        }
+        return;
+    }
+    const int sides = 2 * a.n_kv_heads;
+    const int64_t n_units = int64_t(a.ctl[kCtlRuns]) * sides;
+    const int64_t dst_pitch = int64_t(a.n_kv_heads) * kHeadDim;
+    // units of this thread block: blockIdx.x, blockIdx.x + gridDim.x, ...
+    const int64_t mine = n_units > int64_t(blockIdx.x) ? (n_units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+
+    if (warp == kStagedWorkerWarps) {
+        // ------------------------------------------------------------ scout warp
+        // the run-list entry of the next unit is fetched one unit ahead: one memory round trip per unit, not two
+        int2 next_first = mine > 0 ? a.run_list[int(int64_t(blockIdx.x) / sides)] : make_int2(0, 0);
+        for (int64_t n = 0; n < mine; ++n) {
+            const int64_t unit = blockIdx.x + n * gridDim.x;
+            const int run = int(unit / sides), y = int(unit - int64_t(run) * sides);
+            const int head = y >> 1;
+            const Fp8Side side = (y & 1) ? a.v : a.k;
+            const int2 first = next_first;
+            if (n + 1 < mine) next_first = a.run_list[int((unit + gridDim.x) / sides)];
+            const int64_t start = first.x;
+            const int slot0 = first.y;
+            const int64_t page = a.page_of(slot0);
+            if (y == 0 && lane == 0) a.count[page] = 0;                // nobody reads the counts any more
+            const float old = side.scale[page * a.n_kv_heads + head];
+            // length of the run: lane l looks at offsets l + 1, l + 33, ... (8 loads in flight); a run ends
+            // with its page at the latest, so 256 offsets cover it
+            int first_bad = kStagedRows;
+#pragma unroll
+            for (int j = 7; j >= 0; --j) {
+                const int off = 1 + lane + 32 * j;
+                const int64_t i = start + off;
+                bool cont = off < kStagedRows && i < a.n_tokens;
+                if (cont) {
+                    const int s = __ldg(a.slot_mapping + i);
+                    cont = s == slot0 + off && int64_t(s) < a.num_slots && a.page_of(s) == page;
+                }
+                if (!cont) first_bad = off;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) first_bad = min(first_bad, __shfl_xor_sync(0xffffffffu, first_bad, o));
+            const uint32_t s = uint32_t(n) % kStagedMetaSlots, ph = (uint32_t(n) / kStagedMetaSlots) & 1;
+            bool ok = mbar_wait(empty0 + s * 8, ph ^ 1);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) return;                                           // the workers give up on their own wait
+            if (lane == 0) {
+                s_meta[s].start = int(start);
+                s_meta[s].len = first_bad;
+                s_meta[s].slot0 = slot0;
+                s_meta[s].head = head;
+                s_meta[s].side = y & 1;
+                s_meta[s].old_scale = old;
+                mbar_arrive(full0 + s * 8);                            // release: the fields above are visible to the waiters
+            }
+            __syncwarp();
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------- workers: 512 threads, 32 rows per pass
+    const int lane16 = tid & 15, rsub = tid >> 4;                     // rows rsub, rsub + 32, ... of a buffer
+    // asynchronous copies of unit n into buffer n % kStagedBufs (nothing for n >= mine); false: the wait ran out
+    auto issue = [&](int64_t n) -> bool {
+        if (n >= mine) return true;
+        const uint32_t s = uint32_t(n) % kStagedMetaSlots, ph = (uint32_t(n) / kStagedMetaSlots) & 1;
+        if (!mbar_wait(full0 + s * 8, ph)) return false;
+        const int start = s_meta[s].start, len = s_meta[s].len, head = s_meta[s].head;
+        const Fp8Side side = s_meta[s].side ? a.v : a.k;
+        const __nv_bfloat16* src = side.src + head * kHeadDim + lane16 * 8;
+        const uint32_t dst = base + uint32_t(n % kStagedBufs) * kStagedBufBytes + lane16 * 16;
+#pragma unroll
+        for (int j = 0; j < kStagedRows / 32; ++j) {
+            const int row = rsub + 32 * j;
+            if (row < len) cp_async16(dst + row * 256, src + (int64_t(start) + row) * side.pitch);
+        }
+        return true;
+    };
+    bool ok = issue(0);
+    cp_async_commit();
+    ok = issue(1) && ok;
+    cp_async_commit();
+    for (int64_t n = 0; n < mine; ++n) {
+        cp_async_wait<1>();                                            // this thread's copies of unit n have landed
+        ok = __syncthreads_and_workers(ok);
+        if (!ok) return;
+        // every worker is past unit n - 1: its buffer may take unit n + 2
+        ok = issue(n + 2);
+        cp_async_commit();
+        const uint32_t s = uint32_t(n) % kStagedMetaSlots;
+        const int len = s_meta[s].len, slot0 = s_meta[s].slot0, head = s_meta[s].head;
+        const float old_scale = s_meta[s].old_scale;
+        const Fp8Side side = s_meta[s].side ? a.v : a.k;
+        const uint8_t* buf = smem + (n % kStagedBufs) * kStagedBufBytes + lane16 * 16;
+        // pass 1: largest magnitude of the unit's rows
+        __nv_bfloat162 best = __float2bfloat162_rn(0.0f);
+#pragma unroll
+        for (int j = 0; j < kStagedRows / 32; ++j) {
+            const int row = rsub + 32 * j;
+            if (row < len) best = __hmax2(best, amax8(*reinterpret_cast<const uint4*>(buf + row * 256)));
+        }
+        float mx = fmaxf(__low2float(best), __high2float(best));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        if (lane == 0) s_red[warp] = mx;
+        worker_bar();
+        if (tid == 0) {
+#pragma unroll
+            for (int w = 1; w < kStagedWorkerWarps; ++w) mx = fmaxf(mx, s_red[w]);
+            const int64_t e = a.page_of(slot0) * a.n_kv_heads + head;
+            float sc = old_scale, ratio = -1.0f;
+            if (mx > 0.0f) {
+                const float c = __fdiv_rn(mx, 448.0f);
+                if (c > old_scale) {
+                    side.scale[e] = c;
+                    sc = c;
+                    if (old_scale > 0.0f) ratio = __fdiv_rn(old_scale, c);
+                }
+            }
+            s_red[kStagedWorkerWarps] = sc;
+            s_red[kStagedWorkerWarps + 1] = ratio;
+        }
+        worker_bar();
+        const float scale = s_red[kStagedWorkerWarps], ratio = s_red[kStagedWorkerWarps + 1];
+        if (ratio >= 0.0f) {
+            // the page's scale grew: re-encode what the page holds for this head before any new row is written
+            uint8_t* pbase = side.cache + (a.page_of(slot0) * a.block_size * a.n_kv_heads + head) * int64_t(kHeadDim);
+            for (int i = tid; i < a.block_size * 8; i += kStagedWorkers) {
+                uint4* p = reinterpret_cast<uint4*>(pbase + (i >> 3) * dst_pitch + (i & 7) * 16);
+                uint4 q = *p;
+                q.x = rescale4(q.x, ratio);
+                q.y = rescale4(q.y, ratio);
+                q.z = rescale4(q.z, ratio);
+                q.w = rescale4(q.w, ratio);
+                *p = q;
+            }
+            worker_bar();
+        }
+        // pass 2: quantise with the final scale
+        const Divisor div(scale);
+        uint8_t* dst = side.cache + int64_t(slot0) * dst_pitch + head * kHeadDim + lane16 * 8;
+#pragma unroll
+        for (int j = 0; j < kStagedRows / 32; ++j) {
+            const int row = rsub + 32 * j;
+            if (row < len)
+                *reinterpret_cast<uint2*>(dst + row * dst_pitch) = div.quantise8(*reinterpret_cast<const uint4*>(buf + row * 256));
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty0 + s * 8);                   // this warp is done with the unit's ring entry
+    }
+    cp_async_wait<0>();
 }
 
 }  // namespace ib
@@ -581,8 +831,8 @@ extern "C" {
 
 size_t infer_kv_append_workspace_bytes(const infer_kv_pool_t* pool) {
     if (!pool || pool->dtype != INFER_KV_E4M3) return 0;
-    // candidates of k and v per (page, head), runs per page, control words
-    return (size_t(2) * pool->num_blocks * pool->n_kv_heads + size_t(pool->num_blocks) + ib::kCtlWords) * 4;
+    // candidates of k and v per (page, head), runs per page, the run list, control words
+    return (size_t(2) * pool->num_blocks * pool->n_kv_heads + size_t(3) * pool->num_blocks + ib::kCtlWords) * 4 + 8;
 }
 
 int infer_kv_append(const infer_kv_pool_t* pool, const void* k, const void* v, int64_t k_row_stride,
@@ -634,16 +884,30 @@ int infer_kv_append(const infer_kv_pool_t* pool, const void* k, const void* v, i
     a.page_magic = ~uint64_t(0) / uint64_t(pool->block_size) + 1;
     if (pool->num_slots >= (int64_t(1) << 32)) return INFER_ERR_GEOMETRY;
     a.count = reinterpret_cast<int*>(cand + 2 * pool->num_blocks * pool->n_kv_heads);
-    a.ctl = a.count + pool->num_blocks;
-    if (2 * pool->n_kv_heads > 65535) return INFER_ERR_GEOMETRY;
-    // runs: how many a page receives, then one thread block per (slice of tokens, head, k|v)
+    // the run list holds 8-byte entries: start it on the next 8-byte boundary after the counts
+    a.run_list = reinterpret_cast<int2*>((reinterpret_cast<uintptr_t>(a.count + pool->num_blocks) + 7) & ~uintptr_t(7));
+    a.ctl = reinterpret_cast<int*>(a.run_list + pool->num_blocks);
+    a.num_blocks = int(pool->num_blocks);
+    // runs: count and list them, then persistent thread blocks take (run, head, k|v) units
     ib::fp8_classify_kernel<<<unsigned((n_tokens + 255) / 256), 256, 0, stream>>>(a);
     if (n_tokens <= 1024) {
-        const dim3 grid{unsigned(n_tokens), unsigned(2 * pool->n_kv_heads), 1u};
-        IB_CUDA(ib::launch_pdl(ib::fp8_run_kernel<32>, grid, dim3(32), 0, stream, a, 1));
+        int64_t grid = n_tokens * 2 * pool->n_kv_heads;              // at most one unit per block
+        if (grid > int64_t(pool->sm_count) * 16) grid = int64_t(pool->sm_count) * 16;
+        IB_CUDA(ib::launch_pdl(ib::fp8_run_kernel<32>, dim3(unsigned(grid)), dim3(32), 0, stream, a));
+    } else if (pool->block_size == ib::kStagedRows) {
+        // pages of 256 tokens (the engine's page size): rows staged in shared memory by the copy engine
+        static std::atomic<bool> prepared[64];
+        int dev = 0;
+        IB_CUDA(cudaGetDevice(&dev));
+        if (dev < 0 || dev >= 64 || !prepared[dev].load(std::memory_order_acquire)) {
+            IB_CUDA(cudaFuncSetAttribute(ib::fp8_run_staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         ib::StagedSmem::total));
+            if (dev >= 0 && dev < 64) prepared[dev].store(true, std::memory_order_release);
+        }
+        IB_CUDA(ib::launch_pdl(ib::fp8_run_staged_kernel, dim3(unsigned(pool->sm_count)), dim3(ib::kStagedThreads),
+                               ib::StagedSmem::total, stream, a));
     } else {
-        const dim3 grid{unsigned((n_tokens + 63) / 64), unsigned(2 * pool->n_kv_heads), 1u};
-        IB_CUDA(ib::launch_pdl(ib::fp8_run_kernel<256>, grid, dim3(256), 0, stream, a, 64));
+        IB_CUDA(ib::launch_pdl(ib::fp8_run_kernel<256>, dim3(unsigned(pool->sm_count) * 2), dim3(256), 0, stream, a));
     }
     // strips: only when some page received several runs (the kernels return at once otherwise)
     const int64_t strips = (n_tokens + ib::kStrip - 1) / ib::kStrip;

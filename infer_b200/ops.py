@@ -66,9 +66,10 @@ class _Scratch:
     ``_retired`` (kept alive for the life of the process) and a larger one takes its place for new
     calls.  In practice the first call of a model sizes the buffer and it never grows.
 
-    Every call on a device shares the buffer of its purpose: calls must be ordered on ONE stream
-    (or inside one graph).  A caller that runs attention on several streams of one device passes
-    its own ``workspace=`` tensor per stream to the ops instead."""
+    Every decode call on a device shares one buffer: calls must be ordered on ONE stream (or inside
+    one graph).  A caller that runs attention on several streams of one device passes its own
+    ``workspace=`` tensor per stream to the ops instead.  (The e4m3 append scratch is not kept here:
+    its contents are tied to one pool's geometry, so every ``KVPool`` owns its own.)"""
 
     def __init__(self):
         self._live: dict = {}
@@ -132,7 +133,10 @@ class KVPool:
         _lib.check(rc, "infer_kv_pool_create")
         self.handle = handle
         self._decode_ws_bytes: dict = {}      # n_q_heads -> bytes, asked of the library once
+        # e4m3 append scratch: its layout follows the pool's geometry and every call leaves it in the state
+        # the next call on the SAME pool expects, so each pool owns one (sized here, never re-allocated)
         self.append_ws_bytes = lib.infer_kv_append_workspace_bytes(handle) if fp8 else 0
+        self.append_ws = torch.zeros(self.append_ws_bytes, dtype=torch.uint8, device=self.device) if fp8 else None
 
     def decode_workspace_bytes(self, batch: int, n_q_heads: int) -> int:
         need = self._decode_ws_bytes.get(n_q_heads)
@@ -169,7 +173,8 @@ def release_pools():
 # --------------------------------------------------------------------------- append
 def store_kvcache(key, value, k_cache, v_cache, slot_mapping, k_scale=None, v_scale=None, workspace=None):
     """``workspace`` (e4m3 pools only): a zero-initialised uint8 tensor of ``pool.append_ws_bytes``
-    that this caller reserves for its own stream; by default the per-device scratch is used."""
+    that this caller reserves for its own stream and this pool; by default the pool's own scratch is
+    used (appends to one pool must then be ordered on one stream)."""
     n, num_heads, head_dim = key.shape
     d = num_heads * head_dim
     assert key.stride(-1) == 1 and value.stride(-1) == 1
@@ -190,7 +195,7 @@ def store_kvcache(key, value, k_cache, v_cache, slot_mapping, k_scale=None, v_sc
     ws, ws_bytes = None, 0
     if pool.fp8:
         ws_bytes = pool.append_ws_bytes
-        ws = workspace if workspace is not None else _SCRATCH.get(pool.device, "fp8-append", ws_bytes)
+        ws = workspace if workspace is not None else pool.append_ws
     with _on_device(pool.device):
         rc = lib.infer_kv_append(pool.handle, _ptr(key), _ptr(value), k_pitch, v_pitch,
                                  _ptr(slot_mapping), n, _ptr(ws), ws_bytes, _stream())
