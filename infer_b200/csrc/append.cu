@@ -14,7 +14,6 @@
 //     new rows - on strips of 8 tokens per warp.
 // Both ways give the bytes and scales of the CPU oracle bit for bit, whatever the scheduling.
 // All five kernels are always launched; those of the way not taken return at once.
-#include <atomic>
 #include <climits>
 
 #include "common.cuh"
@@ -367,6 +366,26 @@ struct Divisor {
         if (!(s > 0.0f)) return make_uint2(0, 0);
         return make_uint2(quantise4(raw.x, raw.y), quantise4(raw.z, raw.w));
     }
+    // The same for a scale known to be in the range of the short sequence (`fast`): straight-line code, so a
+    // loop over many rows carries no test per quotient.  Callers test `fast` once, outside their loop.
+    __device__ __forceinline__ uint32_t quantise4_fast(uint32_t w0, uint32_t w1) const {
+        const uint64_t x0 = pk2(__uint_as_float(w0 << 16), __uint_as_float(w0 & 0xffff0000u));
+        const uint64_t x1 = pk2(__uint_as_float(w1 << 16), __uint_as_float(w1 & 0xffff0000u));
+        const uint64_t a0 = fmul2(x0, r2), b0 = fmul2(x1, r2);
+        const uint64_t a = ffma2(ffma2(neg_s2, a0, x0), r2, a0), b = ffma2(ffma2(neg_s2, b0, x1), r2, b0);
+        uint32_t out;
+        asm("{\n\t.reg .b16 lo, hi;\n\t.reg .f32 ax, ay, bx, by;\n\t"
+            "mov.b64 {ax, ay}, %1;\n\tmov.b64 {bx, by}, %2;\n\t"
+            "cvt.rn.satfinite.e4m3x2.f32 lo, ay, ax;\n\t"
+            "cvt.rn.satfinite.e4m3x2.f32 hi, by, bx;\n\t"
+            "mov.b32 %0, {lo, hi};\n\t}"
+            : "=r"(out)
+            : "l"(a), "l"(b));
+        return out;
+    }
+    __device__ __forceinline__ uint2 quantise8_fast(const uint4& raw) const {
+        return make_uint2(quantise4_fast(raw.x, raw.y), quantise4_fast(raw.z, raw.w));
+    }
 };
 
 // quantise the new rows with their page's final scale
@@ -431,9 +450,8 @@ __device__ __forceinline__ bool slot_valid(const Fp8Args& a, int s) { return s >
 // front of it on the same page.
 __device__ __forceinline__ bool is_run_start(const Fp8Args& a, int64_t i, int& slot) {
     slot = __ldg(a.slot_mapping + i);
+    const int prev = i > 0 ? __ldg(a.slot_mapping + i - 1) : -1;       // both loads in flight together
     if (!slot_valid(a, slot)) return false;
-    if (i == 0) return true;
-    const int prev = __ldg(a.slot_mapping + i - 1);
     return !(slot_valid(a, prev) && prev + 1 == slot && a.page_of(prev) == a.page_of(slot));
 }
 
@@ -478,6 +496,8 @@ __global__ void __launch_bounds__(256) fp8_classify_kernel(Fp8Args a) {
 // THREADS / 16 rows per load instruction, 16 loads in flight per thread: 256 threads hold a whole
 // 256-row run (64 KiB) in registers, so the rows are read from memory once.  Runs longer than the
 // registers hold (32 threads: 32 rows) read the remainder a second time, from L2.
+// (Staging the rows in shared memory with asynchronous copies, three 64 KiB buffers and one 17-warp block per
+// SM, was built and measured slower: 70.8 us against 43.2 us for this kernel on 32768 rows x 8 heads.)
 template <int THREADS>
 __global__ void __launch_bounds__(THREADS, THREADS == 256 ? 2 : 16) fp8_run_kernel(Fp8Args a) {
     constexpr int kRowsPerLoad = THREADS / 16, kHeld = 16 * kRowsPerLoad, kWarps = THREADS / 32;
@@ -584,10 +604,18 @@ __global__ void __launch_bounds__(THREADS, THREADS == 256 ? 2 : 16) fp8_run_kern
         // pass 2: quantise with the final scale
         const Divisor div(scale);
         uint8_t* dst = side.cache + int64_t(slot0) * dst_pitch + head * kHeadDim + lane16 * 8;
+        if (div.fast) {                                // uniform over the block: one test for the whole run
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const int row = rsub + j * kRowsPerLoad;
-            if (row < len) *reinterpret_cast<uint2*>(dst + row * dst_pitch) = div.quantise8(raw[j]);
+            for (int j = 0; j < 16; ++j) {
+                const int row = rsub + j * kRowsPerLoad;
+                if (row < len) *reinterpret_cast<uint2*>(dst + row * dst_pitch) = div.quantise8_fast(raw[j]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const int row = rsub + j * kRowsPerLoad;
+                if (row < len) *reinterpret_cast<uint2*>(dst + row * dst_pitch) = div.quantise8(raw[j]);
+            }
         }
         for (int row = kHeld + rsub; row < len; row += kRowsPerLoad)
             *reinterpret_cast<uint2*>(dst + row * dst_pitch) =
@@ -596,234 +624,6 @@ __global__ void __launch_bounds__(THREADS, THREADS == 256 ? 2 : 16) fp8_run_kern
     }
 }
 
-
-// --------------------------------------------------------------------------- runs, staged in shared memory
-// The same units as fp8_run_kernel for pools whose pages hold 256 tokens, with asynchronous copies
-// doing the loads.  A scout warp works out units ahead of time (first token, length, the page's
-// present scale) into a small ring; sixteen worker warps issue the 16-byte asynchronous copies
-// (cp.async) of the unit two places ahead into one of three 64 KiB shared-memory buffers, then
-// take the amax of the current buffer, settle the scale, quantise from the buffer and store.  The
-// rows of the next two units are in flight while one is being quantised, so the kernel is bound by
-// the quantisation arithmetic or by HBM, not by the latency of either.
-constexpr int kStagedRows = 256;
-constexpr int kStagedBufBytes = kStagedRows * 256;
-constexpr int kStagedBufs = 3;
-constexpr int kStagedMetaSlots = 4;
-constexpr int kStagedWorkerWarps = 16;
-constexpr int kStagedWorkers = kStagedWorkerWarps * 32;
-constexpr int kStagedThreads = kStagedWorkers + 32;
-
-struct StagedMeta {
-    int start;        // first token of the run
-    int len;          // rows of the unit (1..256)
-    int slot0;
-    int head;
-    int side;         // 0 = k, 1 = v
-    float old_scale;
-    int pad[2];
-};
-
-struct StagedSmem {
-    static constexpr int meta = kStagedBufs * kStagedBufBytes;
-    static constexpr int bars = meta + kStagedMetaSlots * int(sizeof(StagedMeta));
-    static constexpr int red = bars + 2 * kStagedMetaSlots * 8;
-    static constexpr int total = red + (kStagedWorkerWarps + 2) * 4;
-};
-
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-__device__ __forceinline__ void worker_bar() { asm volatile("bar.sync 1, %0;" ::"n"(kStagedWorkers) : "memory"); }
-// barrier over the worker threads that also tells every one of them whether all of them passed `ok`
-__device__ __forceinline__ bool __syncthreads_and_workers(bool ok) {
-    uint32_t all;
-    asm volatile(
-        "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\t"
-        "bar.red.and.pred q, 1, %2, p;\n\t"
-        "selp.u32 %0, 1, 0, q;\n\t}"
-        : "=r"(all)
-        : "r"(uint32_t(ok)), "n"(kStagedWorkers)
-        : "memory");
-    return all != 0;
-}
-
-__global__ void __launch_bounds__(kStagedThreads, 1) fp8_run_staged_kernel(Fp8Args a) {
-    extern __shared__ __align__(128) uint8_t smem[];
-    volatile StagedMeta* s_meta = reinterpret_cast<volatile StagedMeta*>(smem + StagedSmem::meta);
-    float* s_red = reinterpret_cast<float*>(smem + StagedSmem::red);      // [warps] maxima, then scale, ratio
-    const uint32_t base = smem_u32(smem);
-    const uint32_t full0 = base + StagedSmem::bars, empty0 = full0 + kStagedMetaSlots * 8;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    if (tid == 0) {
-        for (int s = 0; s < kStagedMetaSlots; ++s) {
-            mbar_init(full0 + s * 8, 1);
-            mbar_init(empty0 + s * 8, kStagedWorkerWarps);
-        }
-        fence_mbar_init();
-    }
-    __syncthreads();
-    pdl_launch_dependents();
-    pdl_wait();                                   // the run list, the counts and the verdict of the kernel in front
-    if (a.ctl[kCtlConflict] != 0) {
-        // the three strip kernels do the work; all that is left to do here is to zero the run counts
-        const int64_t stride = int64_t(gridDim.x) * kStagedThreads;
-        for (int64_t i = int64_t(blockIdx.x) * kStagedThreads + tid; i < a.n_tokens; i += stride) {
-            int slot;
-            if (is_run_start(a, i, slot)) a.count[a.page_of(slot)] = 0;
-        }
-        return;
-    }
-    const int sides = 2 * a.n_kv_heads;
-    const int64_t n_units = int64_t(a.ctl[kCtlRuns]) * sides;
-    const int64_t dst_pitch = int64_t(a.n_kv_heads) * kHeadDim;
-    // units of this thread block: blockIdx.x, blockIdx.x + gridDim.x, ...
-    const int64_t mine = n_units > int64_t(blockIdx.x) ? (n_units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-
-    if (warp == kStagedWorkerWarps) {
-        // ------------------------------------------------------------ scout warp
-        // the run-list entry of the next unit is fetched one unit ahead: one memory round trip per unit, not two
-        int2 next_first = mine > 0 ? a.run_list[int(int64_t(blockIdx.x) / sides)] : make_int2(0, 0);
-        for (int64_t n = 0; n < mine; ++n) {
-            const int64_t unit = blockIdx.x + n * gridDim.x;
-            const int run = int(unit / sides), y = int(unit - int64_t(run) * sides);
-            const int head = y >> 1;
-            const Fp8Side side = (y & 1) ? a.v : a.k;
-            const int2 first = next_first;
-            if (n + 1 < mine) next_first = a.run_list[int((unit + gridDim.x) / sides)];
-            const int64_t start = first.x;
-            const int slot0 = first.y;
-            const int64_t page = a.page_of(slot0);
-            if (y == 0 && lane == 0) a.count[page] = 0;                // nobody reads the counts any more
-            const float old = side.scale[page * a.n_kv_heads + head];
-            // length of the run: lane l looks at offsets l + 1, l + 33, ... (8 loads in flight); a run ends
-            // with its page at the latest, so 256 offsets cover it
-            int first_bad = kStagedRows;
-#pragma unroll
-            for (int j = 7; j >= 0; --j) {
-                const int off = 1 + lane + 32 * j;
-                const int64_t i = start + off;
-                bool cont = off < kStagedRows && i < a.n_tokens;
-                if (cont) {
-                    const int s = __ldg(a.slot_mapping + i);
-                    cont = s == slot0 + off && int64_t(s) < a.num_slots && a.page_of(s) == page;
-                }
-                if (!cont) first_bad = off;
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) first_bad = min(first_bad, __shfl_xor_sync(0xffffffffu, first_bad, o));
-            const uint32_t s = uint32_t(n) % kStagedMetaSlots, ph = (uint32_t(n) / kStagedMetaSlots) & 1;
-            bool ok = mbar_wait(empty0 + s * 8, ph ^ 1);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) return;                                           // the workers give up on their own wait
-            if (lane == 0) {
-                s_meta[s].start = int(start);
-                s_meta[s].len = first_bad;
-                s_meta[s].slot0 = slot0;
-                s_meta[s].head = head;
-                s_meta[s].side = y & 1;
-                s_meta[s].old_scale = old;
-                mbar_arrive(full0 + s * 8);                            // release: the fields above are visible to the waiters
-            }
-            __syncwarp();
-        }
-        return;
-    }
-
-    // ---------------------------------------------------------------- workers: 512 threads, 32 rows per pass
-    const int lane16 = tid & 15, rsub = tid >> 4;                     // rows rsub, rsub + 32, ... of a buffer
-    // asynchronous copies of unit n into buffer n % kStagedBufs (nothing for n >= mine); false: the wait ran out
-    auto issue = [&](int64_t n) -> bool {
-        if (n >= mine) return true;
-        const uint32_t s = uint32_t(n) % kStagedMetaSlots, ph = (uint32_t(n) / kStagedMetaSlots) & 1;
-        if (!mbar_wait(full0 + s * 8, ph)) return false;
-        const int start = s_meta[s].start, len = s_meta[s].len, head = s_meta[s].head;
-        const Fp8Side side = s_meta[s].side ? a.v : a.k;
-        const __nv_bfloat16* src = side.src + head * kHeadDim + lane16 * 8;
-        const uint32_t dst = base + uint32_t(n % kStagedBufs) * kStagedBufBytes + lane16 * 16;
-#pragma unroll
-        for (int j = 0; j < kStagedRows / 32; ++j) {
-            const int row = rsub + 32 * j;
-            if (row < len) cp_async16(dst + row * 256, src + (int64_t(start) + row) * side.pitch);
-        }
-        return true;
-    };
-    bool ok = issue(0);
-    cp_async_commit();
-    ok = issue(1) && ok;
-    cp_async_commit();
-    for (int64_t n = 0; n < mine; ++n) {
-        cp_async_wait<1>();                                            // this thread's copies of unit n have landed
-        ok = __syncthreads_and_workers(ok);
-        if (!ok) return;
-        // every worker is past unit n - 1: its buffer may take unit n + 2
-        ok = issue(n + 2);
-        cp_async_commit();
-        const uint32_t s = uint32_t(n) % kStagedMetaSlots;
-        const int len = s_meta[s].len, slot0 = s_meta[s].slot0, head = s_meta[s].head;
-        const float old_scale = s_meta[s].old_scale;
-        const Fp8Side side = s_meta[s].side ? a.v : a.k;
-        const uint8_t* buf = smem + (n % kStagedBufs) * kStagedBufBytes + lane16 * 16;
-        // pass 1: largest magnitude of the unit's rows
-        __nv_bfloat162 best = __float2bfloat162_rn(0.0f);
-#pragma unroll
-        for (int j = 0; j < kStagedRows / 32; ++j) {
-            const int row = rsub + 32 * j;
-            if (row < len) best = __hmax2(best, amax8(*reinterpret_cast<const uint4*>(buf + row * 256)));
-        }
-        float mx = fmaxf(__low2float(best), __high2float(best));
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        if (lane == 0) s_red[warp] = mx;
-        worker_bar();
-        if (tid == 0) {
-#pragma unroll
-            for (int w = 1; w < kStagedWorkerWarps; ++w) mx = fmaxf(mx, s_red[w]);
-            const int64_t e = a.page_of(slot0) * a.n_kv_heads + head;
-            float sc = old_scale, ratio = -1.0f;
-            if (mx > 0.0f) {
-                const float c = __fdiv_rn(mx, 448.0f);
-                if (c > old_scale) {
-                    side.scale[e] = c;
-                    sc = c;
-                    if (old_scale > 0.0f) ratio = __fdiv_rn(old_scale, c);
-                }
-            }
-            s_red[kStagedWorkerWarps] = sc;
-            s_red[kStagedWorkerWarps + 1] = ratio;
-        }
-        worker_bar();
-        const float scale = s_red[kStagedWorkerWarps], ratio = s_red[kStagedWorkerWarps + 1];
-        if (ratio >= 0.0f) {
-            // the page's scale grew: re-encode what the page holds for this head before any new row is written
-            uint8_t* pbase = side.cache + (a.page_of(slot0) * a.block_size * a.n_kv_heads + head) * int64_t(kHeadDim);
-            for (int i = tid; i < a.block_size * 8; i += kStagedWorkers) {
-                uint4* p = reinterpret_cast<uint4*>(pbase + (i >> 3) * dst_pitch + (i & 7) * 16);
-                uint4 q = *p;
-                q.x = rescale4(q.x, ratio);
-                q.y = rescale4(q.y, ratio);
-                q.z = rescale4(q.z, ratio);
-                q.w = rescale4(q.w, ratio);
-                *p = q;
-            }
-            worker_bar();
-        }
-        // pass 2: quantise with the final scale
-        const Divisor div(scale);
-        uint8_t* dst = side.cache + int64_t(slot0) * dst_pitch + head * kHeadDim + lane16 * 8;
-#pragma unroll
-        for (int j = 0; j < kStagedRows / 32; ++j) {
-            const int row = rsub + 32 * j;
-            if (row < len)
-                *reinterpret_cast<uint2*>(dst + row * dst_pitch) = div.quantise8(*reinterpret_cast<const uint4*>(buf + row * 256));
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(empty0 + s * 8);                   // this warp is done with the unit's ring entry
-    }
-    cp_async_wait<0>();
-}
 
 }  // namespace ib
 
@@ -894,18 +694,6 @@ int infer_kv_append(const infer_kv_pool_t* pool, const void* k, const void* v, i
         int64_t grid = n_tokens * 2 * pool->n_kv_heads;              // at most one unit per block
         if (grid > int64_t(pool->sm_count) * 16) grid = int64_t(pool->sm_count) * 16;
         IB_CUDA(ib::launch_pdl(ib::fp8_run_kernel<32>, dim3(unsigned(grid)), dim3(32), 0, stream, a));
-    } else if (pool->block_size == ib::kStagedRows) {
-        // pages of 256 tokens (the engine's page size): rows staged in shared memory by the copy engine
-        static std::atomic<bool> prepared[64];
-        int dev = 0;
-        IB_CUDA(cudaGetDevice(&dev));
-        if (dev < 0 || dev >= 64 || !prepared[dev].load(std::memory_order_acquire)) {
-            IB_CUDA(cudaFuncSetAttribute(ib::fp8_run_staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         ib::StagedSmem::total));
-            if (dev >= 0 && dev < 64) prepared[dev].store(true, std::memory_order_release);
-        }
-        IB_CUDA(ib::launch_pdl(ib::fp8_run_staged_kernel, dim3(unsigned(pool->sm_count)), dim3(ib::kStagedThreads),
-                               ib::StagedSmem::total, stream, a));
     } else {
         IB_CUDA(ib::launch_pdl(ib::fp8_run_kernel<256>, dim3(unsigned(pool->sm_count) * 2), dim3(256), 0, stream, a));
     }
@@ -913,7 +701,10 @@ int infer_kv_append(const infer_kv_pool_t* pool, const void* k, const void* v, i
     const int64_t strips = (n_tokens + ib::kStrip - 1) / ib::kStrip;
     const int rows = 2 * ((pool->n_kv_heads + 1) / 2);             // grid rows: (k|v) x head pair
     int64_t per_row = (strips + ib::kWarpsPerCta - 1) / ib::kWarpsPerCta;
-    const int64_t cap = (int64_t(pool->sm_count) * 12 + rows - 1) / rows;
+    // The strip kernels stride over their strips, so any grid works; they only have work when slots are
+    // scattered, and otherwise every block of theirs just reads a flag and leaves: 6 blocks per SM keeps
+    // that cheap and still fills the machine when they do run.
+    const int64_t cap = (int64_t(pool->sm_count) * 6 + rows - 1) / rows;
     if (per_row > cap) per_row = cap;
     const dim3 blocks{unsigned(per_row), unsigned(rows), 1u};
     IB_CUDA(ib::launch_pdl(ib::fp8_amax_kernel, blocks, dim3(256), 0, stream, a));
