@@ -13,7 +13,9 @@
 //     (page, head) with atomics; raise the scales and re-encode pages whose scale grew; write the
 //     new rows - on strips of 8 tokens per warp.
 // Both ways give the bytes and scales of the CPU oracle bit for bit, whatever the scheduling.
-// All five kernels are always launched; those of the way not taken return at once.
+// The kernels of both ways are always launched; those of the way not taken return at once.  Calls of
+// at most 1024 tokens (a decode step) run the three strip phases in one thread block, separated by
+// block-wide barriers: three launches per call instead of five.
 #include <climits>
 
 #include "common.cuh"
@@ -111,10 +113,10 @@ struct StripLane {
     bool active;                   // false: the odd head of the last pair when Hkv is odd
 };
 
-__device__ __forceinline__ StripLane strip_lane(const Fp8Args& a, int lane) {
+__device__ __forceinline__ StripLane strip_lane(const Fp8Args& a, int lane, int by) {
     StripLane u;
-    u.side = (blockIdx.y & 1) ? a.v : a.k;          // selected by value: no indexed access to the parameter block
-    u.head = int(blockIdx.y >> 1) * 2 + (lane >> 4);
+    u.side = (by & 1) ? a.v : a.k;                  // selected by value: no indexed access to the parameter block
+    u.head = int(by >> 1) * 2 + (lane >> 4);
     u.sub = lane & 15;
     u.active = u.head < a.n_kv_heads;
     u.src = u.side.src + u.head * kHeadDim + u.sub * 8;
@@ -176,15 +178,12 @@ __device__ __forceinline__ void amax_flush(const Fp8Args& a, const StripLane& u,
 }
 
 // cand[page, head] = max over this call's rows on that page of amax(row) / 448
-__global__ void __launch_bounds__(256, 3) fp8_amax_kernel(Fp8Args a) {
-    pdl_launch_dependents();
-    pdl_wait();
-    if (a.ctl[kCtlConflict] == 0) return;      // every page got one run: fp8_run_kernel did the work
+// The warps of grid row `by` ((k|v) x head pair) walk the strips first_strip, first_strip + stride, ...
+__device__ __forceinline__ void fp8_amax_body(const Fp8Args& a, int by, int64_t first_strip, int64_t stride) {
     const int64_t strips = (a.n_tokens + kStrip - 1) / kStrip;
-    const int64_t stride = int64_t(gridDim.x) * kWarpsPerCta;
     const int lane = threadIdx.x & 31;
-    const StripLane u = strip_lane(a, lane);
-    int64_t strip = int64_t(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
+    const StripLane u = strip_lane(a, lane, by);
+    int64_t strip = first_strip;
     int next[kStrip];
     strip_slots(a, strip, strips, next);
     for (; strip < strips; strip += stride) {
@@ -222,6 +221,13 @@ __global__ void __launch_bounds__(256, 3) fp8_amax_kernel(Fp8Args a) {
             if (t < kStrip) best = __hmax2(best, amax8(raw[t]));
         }
     }
+}
+
+__global__ void __launch_bounds__(256, 3) fp8_amax_kernel(Fp8Args a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    if (a.ctl[kCtlConflict] == 0) return;      // every page got one run: fp8_run_kernel did the work
+    fp8_amax_body(a, int(blockIdx.y), int64_t(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5), int64_t(gridDim.x) * kWarpsPerCta);
 }
 
 __device__ __forceinline__ uint32_t rescale4(uint32_t q, float ratio) {
@@ -270,15 +276,11 @@ __device__ __forceinline__ void rescale_claim(const Fp8Args& a, const StripLane&
 
 // Raises scale[page, head] to the call's candidate; a warp looks at a page only where a run
 // of tokens on that page starts (the token in front maps elsewhere).
-__global__ void __launch_bounds__(256) fp8_rescale_kernel(Fp8Args a) {
-    pdl_launch_dependents();
-    pdl_wait();                // the candidates of the kernel in front
-    if (a.ctl[kCtlConflict] == 0) return;
+__device__ __forceinline__ void fp8_rescale_body(const Fp8Args& a, int by, int64_t first_strip, int64_t stride) {
     const int64_t strips = (a.n_tokens + kStrip - 1) / kStrip;
-    const int64_t stride = int64_t(gridDim.x) * kWarpsPerCta;
     const int lane = threadIdx.x & 31;
-    const StripLane u = strip_lane(a, lane);
-    for (int64_t strip = int64_t(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5); strip < strips; strip += stride) {
+    const StripLane u = strip_lane(a, lane, by);
+    for (int64_t strip = first_strip; strip < strips; strip += stride) {
         int slot[kStrip];
         strip_slots(a, strip, strips, slot);
         int64_t cur = -1;                              // page of the token in front of the strip
@@ -300,6 +302,13 @@ __global__ void __launch_bounds__(256) fp8_rescale_kernel(Fp8Args a) {
             if (starts) rescale_claim(a, u, page, lane);
         }
     }
+}
+
+__global__ void __launch_bounds__(256) fp8_rescale_kernel(Fp8Args a) {
+    pdl_launch_dependents();
+    pdl_wait();                // the candidates of the kernel in front
+    if (a.ctl[kCtlConflict] == 0) return;
+    fp8_rescale_body(a, int(blockIdx.y), int64_t(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5), int64_t(gridDim.x) * kWarpsPerCta);
 }
 
 __device__ __forceinline__ uint64_t pk2(float a, float b) {
@@ -389,17 +398,13 @@ struct Divisor {
 };
 
 // quantise the new rows with their page's final scale
-__global__ void __launch_bounds__(256, 3) fp8_write_kernel(Fp8Args a) {
-    pdl_launch_dependents();
-    pdl_wait();                // the final scales and re-encoded pages of the kernel in front
-    if (a.ctl[kCtlConflict] == 0) return;
+__device__ __forceinline__ void fp8_write_body(const Fp8Args& a, int by, int64_t first_strip, int64_t stride) {
     const int64_t strips = (a.n_tokens + kStrip - 1) / kStrip;
-    const int64_t stride = int64_t(gridDim.x) * kWarpsPerCta;
     const int lane = threadIdx.x & 31;
-    const StripLane u = strip_lane(a, lane);
+    const StripLane u = strip_lane(a, lane, by);
     uint8_t* const dst = u.side.cache + u.head * kHeadDim + u.sub * 8;
     const int64_t dst_pitch = int64_t(a.n_kv_heads) * kHeadDim;
-    int64_t strip = int64_t(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
+    int64_t strip = first_strip;
     int next[kStrip];
     strip_slots(a, strip, strips, next);
     for (; strip < strips; strip += stride) {
@@ -442,6 +447,27 @@ __global__ void __launch_bounds__(256, 3) fp8_write_kernel(Fp8Args a) {
     }
 }
 
+__global__ void __launch_bounds__(256, 3) fp8_write_kernel(Fp8Args a) {
+    pdl_launch_dependents();
+    pdl_wait();                // the final scales and re-encoded pages of the kernel in front
+    if (a.ctl[kCtlConflict] == 0) return;
+    fp8_write_body(a, int(blockIdx.y), int64_t(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5), int64_t(gridDim.x) * kWarpsPerCta);
+}
+
+// The three strip phases in ONE thread block, for calls of few tokens (a decode step): the phases are
+// separated by block-wide barriers instead of kernel boundaries, so such a call is three launches
+// (classify, runs, this) instead of five.  It only has work when some page received several runs.
+__global__ void __launch_bounds__(256) fp8_strips_one_block_kernel(Fp8Args a, int grid_rows) {
+    pdl_launch_dependents();
+    pdl_wait();
+    if (a.ctl[kCtlConflict] == 0) return;
+    const int64_t first = threadIdx.x >> 5;
+    for (int by = 0; by < grid_rows; ++by) fp8_amax_body(a, by, first, kWarpsPerCta);
+    __syncthreads();
+    for (int by = 0; by < grid_rows; ++by) fp8_rescale_body(a, by, first, kWarpsPerCta);
+    __syncthreads();
+    for (int by = 0; by < grid_rows; ++by) fp8_write_body(a, by, first, kWarpsPerCta);
+}
 
 // --------------------------------------------------------------------------- runs
 __device__ __forceinline__ bool slot_valid(const Fp8Args& a, int s) { return s >= 0 && int64_t(s) < a.num_slots; }
@@ -700,6 +726,10 @@ int infer_kv_append(const infer_kv_pool_t* pool, const void* k, const void* v, i
     // strips: only when some page received several runs (the kernels return at once otherwise)
     const int64_t strips = (n_tokens + ib::kStrip - 1) / ib::kStrip;
     const int rows = 2 * ((pool->n_kv_heads + 1) / 2);             // grid rows: (k|v) x head pair
+    if (n_tokens <= 1024) {
+        IB_CUDA(ib::launch_pdl(ib::fp8_strips_one_block_kernel, dim3(1), dim3(256), 0, stream, a, rows));
+        return ib::check_launch();
+    }
     int64_t per_row = (strips + ib::kWarpsPerCta - 1) / ib::kWarpsPerCta;
     // The strip kernels stride over their strips, so any grid works; they only have work when slots are
     // scattered, and otherwise every block of theirs just reads a flag and leaves: 6 blocks per SM keeps
