@@ -66,7 +66,7 @@ def test_fused_golden_bits(golden):
     assert bits_equal(kc.view(-1, 128)[:t], q_out[:, 0])      # k went through the same arithmetic into its slots
 
 
-@pytest.mark.parametrize("t,hq,hkv", [(64, 32, 8), (1, 16, 8), (700, 16, 8), (33, 2, 1), (5, 6, 3)])
+@pytest.mark.parametrize("t,hq,hkv", [(64, 32, 8), (1, 16, 8), (700, 16, 8), (33, 2, 1), (5, 6, 3), (17, 40, 8), (9, 4, 1)])
 def test_fused_matches_oracle(t, hq, hkv):
     gen = torch.Generator().manual_seed(t * 7 + hq)
     d, nb = 128, 8
