@@ -486,21 +486,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc_kernel(PrefillParams
                     const uint64_t x2 = ffma2(pk2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), c2, nm2);
                     float e0, e1;
                     upk2(x2, e0, e1);
-#ifdef IB_EX2_BF16X2
-                    // one exp2 instruction for the pair, in and out as packed bf16: P is bf16 anyway
-                    uint32_t xb, pb;
-                    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(xb) : "f"(e1), "f"(e0));
-                    asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(pb) : "r"(xb));
-                    e0 = __uint_as_float(pb << 16);
-                    e1 = __uint_as_float(pb & 0xffff0000u);
-                    if (i & 1) rsb = fadd2(rsb, pk2(e0, e1)); else rsa = fadd2(rsa, pk2(e0, e1));
-                    pk[i] = pb;
-#else
                     e0 = fast_exp2(e0);
                     e1 = fast_exp2(e1);
                     if (i & 1) rsb = fadd2(rsb, pk2(e0, e1)); else rsa = fadd2(rsa, pk2(e0, e1));
                     pk[i] = pack_bf16(e0, e1);
-#endif
                 }
                 tc_st32(p_addr + h * 32, pk);
             }
