@@ -388,6 +388,20 @@ def bench_prefill(ops, device, n_seqs, steps, warmup, dense=True, sample_clocks=
                    "gbs": n_tok * w.n_kv_heads * 128 * 2 * 4 / (append_ms * 1e-3) / 1e9},
         "clocks": clocks.summary(),
     }
+    # the library call the reference makes for this step (infer/ops/attention.py:113-116), on the same tensors
+    try:
+        import flash_attn
+        from flash_attn import flash_attn_varlen_func
+        fa = lambda: flash_attn_varlen_func(w.q, w.k_cache, w.v_cache, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k, max_seqlen_q=mq,
+                                            max_seqlen_k=mk, softmax_scale=w.scale, causal=True, block_table=bt)
+        ref = fa()
+        torch.cuda.synchronize()
+        fa_ms = _timed(fa, 5, 2, stream)
+        res["reference_gpu"] = {"kind": f"flash_attn {getattr(flash_attn, '__version__', '?')} flash_attn_varlen_func with block_table",
+                                "attn_ms": fa_ms, "tflops": flops / (fa_ms * 1e-3) / 1e12,
+                                "max_abs_diff_vs_this_library": float((ref.float() - out.float()).abs().max())}
+    except Exception as exc:
+        res["reference_gpu"] = {"unavailable": f"{type(exc).__name__}: {str(exc)[:120]}"}
     del w
     if dense:
         gen = torch.Generator(device=device).manual_seed(7)

@@ -530,7 +530,7 @@ __global__ void __launch_bounds__(THREADS, THREADS == 256 ? 2 : 16) fp8_run_kern
     __shared__ int s_len;
     __shared__ float s_red[kWarps], s_scale, s_ratio;
     pdl_launch_dependents();
-    pdl_wait();                                   // the run list, the counts and the verdict of the kernel in front
+    pdl_wait();                                   // the run list, the counts and the conflict flag of the kernel in front
     const int tid = threadIdx.x;
     if (a.ctl[kCtlConflict] != 0) {
         // some page got several runs: the three strip kernels do the work; all that is left to do here
