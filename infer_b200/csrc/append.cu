@@ -522,8 +522,9 @@ __global__ void __launch_bounds__(256) fp8_classify_kernel(Fp8Args a) {
 // THREADS / 16 rows per load instruction, 16 loads in flight per thread: 256 threads hold a whole
 // 256-row run (64 KiB) in registers, so the rows are read from memory once.  Runs longer than the
 // registers hold (32 threads: 32 rows) read the remainder a second time, from L2.
-// (Staging the rows in shared memory with asynchronous copies, three 64 KiB buffers and one 17-warp block per
-// SM, was built and measured slower: 70.8 us against 43.2 us for this kernel on 32768 rows x 8 heads.)
+// (Measured slower on 32768 rows x 8 heads, 43.2 us for this kernel: the rows parked in shared memory by 512
+// threads, two blocks per SM, 51 us - 24.5 M executed instructions against 18.9 M, the kernel is bound by its
+// instruction count; asynchronous copies into three 64 KiB buffers, one 17-warp block per SM, 70.8 us.)
 template <int THREADS>
 __global__ void __launch_bounds__(THREADS, THREADS == 256 ? 2 : 16) fp8_run_kernel(Fp8Args a) {
     constexpr int kRowsPerLoad = THREADS / 16, kHeld = 16 * kRowsPerLoad, kWarps = THREADS / 32;
