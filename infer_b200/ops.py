@@ -240,6 +240,10 @@ def paged_attn_decode(q, k_cache, v_cache, cache_seqlens, block_table, softmax_s
                       out=None, k_scale=None, v_scale=None, workspace=None):
     """q [B, Hq, 128] (or [B, 1, Hq, 128] as the reference passes it) -> same shape.
 
+    ``q`` and ``out`` may also be pinned host tensors: the kernel then reads the queries from, and writes the
+    output rows straight into, host memory (a pinned tensor's address is valid on the device), which saves
+    the separate copies of a host-fed step; pass ``out`` explicitly in that case.
+
     ``workspace``: a zero-initialised uint8 tensor of at least
     ``pool.decode_workspace_bytes(B, Hq)`` bytes reserved for this caller's stream; by default the
     per-device scratch is used (see ``_Scratch``: one stream per device)."""
@@ -247,13 +251,16 @@ def paged_attn_decode(q, k_cache, v_cache, cache_seqlens, block_table, softmax_s
     q3 = q.reshape(shape[0], shape[-2], shape[-1])
     if q3.dtype != torch.bfloat16 or not q3.is_contiguous():
         raise RuntimeError("paged_attn_decode: q must be contiguous bf16")
+    for name, t in (("q", q3), ("out", out)):
+        if t is not None and not t.is_cuda and not t.is_pinned():
+            raise RuntimeError(f"paged_attn_decode: {name} must live on the GPU or in pinned host memory")
     for name, t in (("cache_seqlens", cache_seqlens), ("block_table", block_table)):
         if t.dtype != torch.int32 or not t.is_cuda:
             raise RuntimeError(f"paged_attn_decode: {name} must be an int32 CUDA tensor")
     if block_table.stride(-1) != 1:
         raise RuntimeError("paged_attn_decode: block_table rows must be contiguous")
     pool = pool_of(k_cache, v_cache, k_scale, v_scale)
-    o = torch.empty_like(q3) if out is None else out.view(q3.shape)
+    o = torch.empty(q3.shape, dtype=q3.dtype, device=pool.device) if out is None else out.view(q3.shape)
     lib = _lib.load()
     b, hq, _ = q3.shape
     ws = workspace if workspace is not None else _SCRATCH.get(pool.device, "decode", pool.decode_workspace_bytes(b, hq))

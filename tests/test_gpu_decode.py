@@ -286,3 +286,18 @@ def test_decode_rejects_bad_arguments():
         ops.paged_attn_decode(q, kc, kc, cl, bt, 0.1)
     with pytest.raises(RuntimeError):
         ops.paged_attn_decode(q[:, :16].contiguous(), kc, kc, cl.long(), bt, 0.1)
+
+
+def test_decode_reads_q_from_and_writes_out_to_pinned_host_memory():
+    """A host-fed step can skip two copies: q stays in pinned host memory and the kernel writes the output rows
+    straight into a pinned host tensor; the bits equal those of the all-device call."""
+    w = workloads.config1(batch=12, lo=200, hi=3000)
+    d = to_dev(w)
+    want = ops.paged_attn_decode(d["q"], d["k_cache"], d["v_cache"], d["context_lens"], d["block_tables"], w.scale)
+    q_host = w.q.clone().pin_memory()
+    out_host = torch.zeros(w.q.shape, dtype=torch.bfloat16).pin_memory()
+    ops.paged_attn_decode(q_host, d["k_cache"], d["v_cache"], d["context_lens"], d["block_tables"], w.scale, out=out_host)
+    torch.cuda.synchronize()
+    assert torch.equal(out_host, want.cpu())
+    with pytest.raises(RuntimeError, match="pinned"):
+        ops.paged_attn_decode(w.q, d["k_cache"], d["v_cache"], d["context_lens"], d["block_tables"], w.scale, out=out_host)
