@@ -9,7 +9,8 @@
 //     blocks take (run, head, k|v) units off the list the first kernel wrote; a block reads its
 //     run's rows ONCE into registers, takes their amax, settles the scale (re-encoding the page's
 //     older rows when a positive scale grew) and quantises from the registers.
-//   * Otherwise (slots scattered over pages): three kernels - collect the new rows' amax / 448 per
+//   * Otherwise (slots scattered over pages; also a call of more than 1024 tokens in runs of fewer than 64 rows on
+//     average): three kernels - collect the new rows' amax / 448 per
 //     (page, head) with atomics; raise the scales and re-encode pages whose scale grew; write the
 //     new rows - on strips of 8 tokens per warp.
 // Both ways give the bytes and scales of the CPU oracle bit for bit, whatever the scheduling.
@@ -509,8 +510,15 @@ __global__ void __launch_bounds__(256) fp8_classify_kernel(Fp8Args a) {
         __threadfence();
         if (atomicAdd(a.ctl + kCtlDone, 1) == int(gridDim.x) - 1) {
             __threadfence();
-            a.ctl[kCtlConflict] = atomicExch(a.ctl + kCtlConflictAcc, 0);
-            a.ctl[kCtlRuns] = atomicExch(a.ctl + kCtlRunAcc, 0);
+            int scattered = atomicExch(a.ctl + kCtlConflictAcc, 0);
+            const int runs = atomicExch(a.ctl + kCtlRunAcc, 0);
+            // A large call whose runs are short (fewer than 64 rows on average: the step of a decode batch of
+            // more than 1024 sequences) also goes to the strip kernels: fp8_run_kernel gives a whole thread block
+            // to every (run, head, k|v), most of it idle on a one-row run (measured: 2048 rows on pages of their
+            // own 266 us, 46 us as units of single warps, less again on strips).
+            if (a.n_tokens > 1024 && int64_t(runs) * 64 > a.n_tokens) scattered = 1;
+            a.ctl[kCtlConflict] = scattered;
+            a.ctl[kCtlRuns] = runs;
             a.ctl[kCtlDone] = 0;
         }
     }

@@ -228,3 +228,26 @@ def test_fp8_outlier_stress_qwen3_8b_shape_reduced():
     assert bits_equal(cpu[0], gpu[0]) and bits_equal(cpu[1], gpu[1])
     want = oracle.paged_decode(w.q, cpu[0], cpu[1], cl, bt, w.scale, cpu[2], cpu[3])
     assert_close(got, want, ATOL_FP8, RTOL_FP8, "fp8 outlier stress, 32q/8kv")
+
+
+@pytest.mark.parametrize("n_seqs,run_len", [(2048, 1), (1500, 3), (40, 40)])
+def test_fp8_append_large_calls_in_short_runs(n_seqs, run_len):
+    """Calls of more than 1024 tokens whose runs are short (the step of a large decode batch: one row per
+    sequence, every sequence on pages of its own; a few rows each; 40-row runs) are routed to other kernels than
+    a chunk's long runs: three calls on the same pages, magnitudes growing, so that scales grow and pages are
+    re-encoded; bytes and scales bit-exact."""
+    hkv = 2
+    gen = torch.Generator().manual_seed(n_seqs * 7 + run_len)
+    pages = torch.randperm(n_seqs, generator=gen)
+    cpu = _empty_pools(n_seqs, hkv, "cpu")
+    gpu = _empty_pools(n_seqs, hkv, "cuda")
+    for step in range(3):
+        first = 11 + step * run_len
+        slots = (pages[:, None] * 256 + first + torch.arange(run_len)[None, :]).reshape(-1).to(torch.int32)
+        k = (torch.randn(slots.numel(), hkv, 128, generator=gen) * (1.0 + step)).bfloat16()
+        v = (torch.randn(slots.numel(), hkv, 128, generator=gen) * (3.0 - step)).bfloat16()
+        oracle.store_kvcache_fp8(k, v, *cpu, slots)
+        ops.store_kvcache(k.cuda(), v.cuda(), gpu[0], gpu[1], slots.cuda(), gpu[2], gpu[3])
+    torch.cuda.synchronize()
+    assert torch.equal(cpu[2], gpu[2].cpu()) and torch.equal(cpu[3], gpu[3].cpu()), "scales differ"
+    assert bits_equal(cpu[0], gpu[0]) and bits_equal(cpu[1], gpu[1]), "bytes differ"
