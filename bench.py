@@ -215,33 +215,41 @@ def _timed(fn, reps, warm, stream):
 
 
 def time_decode_steps(ops, w, cl, bt, slots, out, steps, warmup, barrier, window_s=0.5, min_replays=50, graph=True):
-    """Times ``steps`` steps (append + decode) of one workload three ways:
+    """Times ``steps`` steps (append + decode, in one launch: ``paged_attn_decode_append``) of one workload three ways:
       * captured once as ONE CUDA graph of ``steps`` steps and replayed R >= min_replays times (at least
         ``window_s`` seconds), an event pair around every replay: median / min / max ms per step;
       * launched kernel by kernel, one event pair around the whole run: ms per step;
       * launched kernel by kernel with events around every decode call: the decode kernel's own time."""
     stream = torch.cuda.current_stream()
 
-    def step():
+    def step_two():                                           # the reference's two calls (infer/ops/attention.py:109, :117-121)
         ops.store_kvcache(w.k, w.v, w.k_cache, w.v_cache, slots)
         ops.paged_attn_decode(w.q, w.k_cache, w.v_cache, cl, bt, w.scale, out=out)
 
+    def step():                                               # the same step in one launch
+        ops.paged_attn_decode_append(w.q, w.k, w.v, w.k_cache, w.v_cache, cl, bt, w.scale, out=out)
+
     for _ in range(warmup):
+        step_two()
         step()
     barrier()
-    res = {"graph": None}
-    g = None
-    if graph:
+    res = {"graph": None, "graph_two_launches": None, "launches_per_step": 1}
+
+    def capture(fn):
         try:
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            cg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(cg):
                 for _ in range(steps):
-                    step()
-            g.replay()                                        # untimed: the first replay uploads the graph
+                    fn()
+            cg.replay()                                       # untimed: the first replay uploads the graph
             torch.cuda.synchronize()
+            return cg
         except Exception as exc:                              # pragma: no cover - reported as absent
             print(f"[bench] CUDA-graph capture of the device-resident steps failed ({exc})", file=sys.stderr)
-            g = None
+            return None
+
+    g = capture(step) if graph else None
+    g2 = capture(step_two) if graph else None
     t_begin = time.time()
     if g is not None:
         # how many replays fill the window: one timed probe
@@ -252,16 +260,25 @@ def time_decode_steps(ops, w, cl, bt, slots, out, steps, warmup, barrier, window
         torch.cuda.synchronize()
         replays = max(min_replays, int(math.ceil(window_s * 1e3 / max(p0.elapsed_time(p1), 1e-3))))
         replays = min(replays, 2000)
-        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(replays)]
+        mk = lambda: [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(replays)]
+        evs, evs2 = mk(), mk() if g2 is not None else []
         barrier()
-        for e0, e1 in evs:
+        # the one-launch step and the two-launch step take turns, replay by replay, so that both see the same clocks
+        for i, (e0, e1) in enumerate(evs):
             e0.record(stream)
             g.replay()
             e1.record(stream)
+            if g2 is not None:
+                f0, f1 = evs2[i]
+                f0.record(stream)
+                g2.replay()
+                f1.record(stream)
         barrier()
         per_step = sorted(e0.elapsed_time(e1) / steps for e0, e1 in evs)
         res["graph"] = {"median": statistics.median(per_step), "min": per_step[0], "max": per_step[-1],
                         "replays": replays, "timed_s": sum(per_step) * steps / 1e3}
+        if g2 is not None:
+            res["graph_two_launches"] = statistics.median(f0.elapsed_time(f1) / steps for f0, f1 in evs2)
     # launched one by one, no events in between (events between kernels would break their overlap)
     reps = max(1, int(math.ceil(0.1 / max(1e-6, steps * 2e-4)))) if window_s > 0 else 1      # about 0.1 s of steps
     s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -645,6 +662,8 @@ def main():
     #   out_host   same upload; the attention kernel writes its output rows straight into pinned host memory
     #              (the pointer of a pinned tensor is valid on the device), so the read-back overlaps the kernel
     #   q_out_host additionally the kernel reads q from pinned host memory; only k, v and the metadata are copied
+    #   all_host   the one-launch step (append + attention) reads q, k and v from pinned host memory and writes its
+    #              output there; only lengths and block tables are copied
     small = {k: v for k, v in src.items() if k != "q"}
     stage_small = StepStaging({k: (tuple(v.shape), v.dtype) for k, v in small.items()}, device)
     for k, v in small.items():
@@ -667,6 +686,18 @@ def main():
         stage_small.upload()
         ops.store_kvcache(ds["k"], ds["v"], w.k_cache, w.v_cache, ds["slots"])
         ops.paged_attn_decode(q_host, w.k_cache, w.v_cache, ds["cl"], ds["bt"], w.scale, out=out_host)
+
+    kv_host = {"k": stage.host["k"], "v": stage.host["v"]}
+    meta = {k: v for k, v in src.items() if k in ("cl", "bt")}
+    stage_meta = StepStaging({k: (tuple(v.shape), v.dtype) for k, v in meta.items()}, device)
+    for k, v in meta.items():
+        stage_meta.host[k].copy_(v)
+
+    def body_all_host():
+        dm = stage_meta.dev
+        stage_meta.upload()                                   # lengths and block tables: 9 KB
+        ops.paged_attn_decode_append(q_host, kv_host["k"], kv_host["v"], w.k_cache, w.v_cache, dm["cl"], dm["bt"], w.scale,
+                                     out=out_host)
 
     def time_e2e(body):
         """ms per step: the step captured once in a CUDA graph (the way the reference replays its decode graphs,
@@ -704,7 +735,8 @@ def main():
 
     e2e_ms, e2e_steps, e2e_graphed, e2e_mode, e2e_all = 1e-6, 0, False, "none", {}
     if not args.profile:
-        for mode, body in (("staged", body_staged), ("out_host", body_out_host), ("q_out_host", body_q_out_host)):
+        for mode, body in (("staged", body_staged), ("out_host", body_out_host), ("q_out_host", body_q_out_host),
+                           ("all_host", body_all_host)):
             ms, e2e_steps, graphed = time_e2e(body)
             e2e_all[mode] = ms
             # every rank must pick the same mode: decide on the maximum over ranks
@@ -716,10 +748,12 @@ def main():
         body_staged()
         torch.cuda.synchronize()
         ref_rows = out_host.clone()
-        body_q_out_host()
-        torch.cuda.synchronize()
-        if not torch.equal(ref_rows, out_host):
-            raise SystemExit("bench: the output written straight to host memory differs from the copied one")
+        for body in (body_q_out_host, body_all_host):
+            out_host.zero_()
+            body()
+            torch.cuda.synchronize()
+            if not torch.equal(ref_rows, out_host):
+                raise SystemExit("bench: the output written straight to host memory differs from the copied one")
 
     # ---- bulk append (the chunked-prefill append: 32768 rows)
     n_bulk = 32768
@@ -803,7 +837,7 @@ def main():
                        "l2": f"KV per step ({kv_bytes / 1e9:.1f} GB per GPU) exceeds L2 (126 MB); no flush needed",
                        "parallelism": f"kv-head-shard{world}"},
             "timing": {"method": f"one CUDA graph of {args.steps} steps replayed {n_replays} times, an event pair per replay; "
-                                 "value from the median replay (max over ranks)" if g else "kernels launched one by one",
+                                 "value from the median replay (max over ranks); the two-launch form of the step is replayed in turn with it" if g else "kernels launched one by one",
                        "replays": n_replays, "ms_per_step_min": step_min, "ms_per_step_max": step_max,
                        "timed_region_s": g["timed_s"] if g else eager_ms * args.steps / 1e3},
             "e2e": {"value": job_bytes / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
@@ -811,8 +845,13 @@ def main():
                     "launch": "cuda graph replay" if e2e_graphed else "eager", "mode": e2e_mode,
                     "ms_per_step_by_mode": e2e_all,
                     "modes": "staged = one H2D copy of all inputs + one D2H copy of the output; out_host = the kernel "
-                             "writes the output into pinned host memory; q_out_host = it also reads q from pinned host memory"},
-            "gpu_launches": 2 * args.steps * max(n_replays, 1),
+                             "writes the output into pinned host memory; q_out_host = it also reads q from pinned host memory; "
+                             "all_host = the one-launch step reads q, k, v from pinned host memory, only lengths and block "
+                             "tables are copied"},
+            "gpu_launches": args.steps * max(n_replays, 1),
+            "step": "append + paged decode attention in ONE launch (paged_attn_decode_append); the same step as the "
+                    "reference's two calls (store_kvcache, then attention) is timed beside it",
+            "ms_per_step_two_launches": r["graph_two_launches"],
             "launch": "cuda graph replay of the K steps" if g else "one launch per kernel",
             "value_launched_one_by_one": job_bytes / (eager_ms * 1e-3) / 1e9, "ms_per_step_launched_one_by_one": eager_ms,
             "roofline": {"bound": "hbm", "kernel": "decode_tma_kernel", "achieved": achieved,

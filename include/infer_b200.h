@@ -130,6 +130,25 @@ INFER_API int infer_paged_decode(const infer_kv_pool_t* pool, void* out, const v
                        const int32_t* context_lens, const int32_t* block_tables,
                        int64_t bt_stride, int batch, int n_q_heads, float softmax_scale,
                        void* workspace, size_t workspace_bytes, void* stream);
+
+/* One decode step in one launch, bf16 pools: infer_kv_append of the step's new rows followed by
+ * infer_paged_decode.  Replaces the two calls the reference makes per layer and decode step,
+ * store_kvcache(k, v, k_cache, v_cache, slot_mapping) and flash_attn_with_kvcache(...)
+ * (infer/ops/attention.py:109 and :117-121; the decode batch is one row per sequence,
+ * infer/engine/model_runner.py:110-126).
+ * k, v: bf16 [batch, n_kv_heads, 128], heads contiguous, k_row_stride / v_row_stride elements between the rows
+ * of consecutive sequences (column slices of a fused qkv output are fine); row b is the token at position
+ * context_lens[b] - 1 of sequence b, whose slot is read off block_tables (no slot_mapping).  Rows of sequences
+ * with context_lens[b] <= 0 or without a page for that position are not written.  The pools end up
+ * byte for byte as after infer_kv_append, the output as after infer_paged_decode.  context_lens and
+ * block_tables may be written by the kernel directly in front of this call in the stream.
+ * INFER_ERR_DTYPE for an e4m3 pool (append and decode stay two calls there).  Workspace, stream and
+ * capture rules as for infer_paged_decode. */
+INFER_API int infer_paged_decode_append(const infer_kv_pool_t* pool, void* out, const void* q, const void* k,
+                              const void* v, int64_t k_row_stride, int64_t v_row_stride,
+                              const int32_t* context_lens, const int32_t* block_tables, int64_t bt_stride,
+                              int batch, int n_q_heads, float softmax_scale, void* workspace,
+                              size_t workspace_bytes, void* stream);
 INFER_API size_t infer_paged_decode_workspace_bytes(const infer_kv_pool_t* pool, int batch, int n_q_heads);
 
 /* Paged chunked-prefill attention.  Replaces the prefill branch

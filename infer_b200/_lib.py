@@ -29,6 +29,7 @@ SIGNATURES = {
                                          _vp, _i64, _i32, _vp]),
     "infer_decode_step_advance": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp]),
     "infer_paged_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _f32, _vp, _sz, _vp]),
+    "infer_paged_decode_append": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _i64, _i32, _i32, _f32, _vp, _sz, _vp]),
     "infer_paged_decode_workspace_bytes": (_sz, [_vp, _i32, _i32]),
     "infer_paged_decode_noalloc": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _f32, _vp]),
     "infer_paged_prefill": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _f32, _vp]),

@@ -23,6 +23,14 @@ class Attention(torch.nn.Module):
         ctx = get_context()
         if not (self.k_cache.numel() and self.v_cache.numel()):
             raise RuntimeError("Attention: the layer has no page pools (allocate_kv_cache not run)")
+        if not ctx.is_prefill and self.k_scale is None:
+            # bf16 decode step: append and attention in one launch.  The slot of a sequence's new token follows from
+            # context_lens and block_tables (position context_len - 1), which is what prepare_decode's slot_mapping
+            # holds as well (infer/engine/model_runner.py:110-126); rows with context_len 0 (the padding of a
+            # captured batch, slot -1 there) are skipped by both.
+            O = ops.paged_attn_decode_append(Q.contiguous(), K, V, self.k_cache, self.v_cache, ctx.context_lens,
+                                             ctx.block_tables, self.scale)
+            return O.view(-1, self.num_heads * self.head_dim)
         ops.store_kvcache(K, V, self.k_cache, self.v_cache, ctx.slot_mapping, self.k_scale, self.v_scale)
         if ctx.is_prefill:
             block_tables = ctx.block_tables

@@ -81,8 +81,11 @@ struct TmaSmem {
     static constexpr int prefix = merge + 4 * kMergeSlotFloats * 4;
     static constexpr int scan = prefix + (kMaxBatch + 1) * 4 + 12;
     static constexpr int bars = scan + kTmaThreads * 4;
-    static constexpr int total = bars + 2 * kStages * 8 + 16;
+    static constexpr int pages = bars + 2 * kStages * 8 + 16;      // page of the tile in each stage (fused append)
+    static constexpr int patch = pages + 16;                        // 512 bytes per consumer warp: a new k row and v row
+    static constexpr int total = patch + kConsumerWarps * 512;
 };
+static_assert(TmaSmem::patch % 16 == 0, "the staging rows are written by 16-byte asynchronous copies");
 
 __device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
@@ -100,6 +103,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_kernel(DecodeParams
     int* s_scan = reinterpret_cast<int*>(smem + TmaSmem::scan);
     volatile int* s_flag = s_scan + 32;             // "this CTA drew the last ticket" (the scan only uses 32 words)
     uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + TmaSmem::bars);
+    volatile int* s_page = reinterpret_cast<volatile int*>(smem + TmaSmem::pages);
     const uint32_t tiles_u32 = smem_u32(smem);
     const uint32_t full0 = smem_u32(s_bar), empty0 = full0 + kStages * 8;
 
@@ -112,6 +116,10 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_kernel(DecodeParams
         fence_mbar_init();
         fence_proxy_async();
     }
+    // With the append fused in, the lengths this launch reads include the token it appends, and whatever wrote
+    // them may be the kernel directly in front: wait for it before the first look at them.  (Two attention
+    // launches never share an SM - each takes nearly all of its shared memory - so nothing is lost.)
+    if (p.new_k != nullptr) pdl_wait();
     build_tile_prefix(p.context_lens, p.batch, TT, s_tp, s_scan);   // ends with __syncthreads
     // Everything above only reads step metadata; the pools and q may still be written by the
     // kernel in front of this one (the append) when this kernel was launched programmatically.
@@ -142,6 +150,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_kernel(DecodeParams
                 const uint32_t bar = full0 + s * 8;
                 const uint32_t kdst = tiles_u32 + s * (2 * kTileBytes), vdst = kdst + kTileBytes;
                 if (p.stall_producer) continue;          // self-test: nothing is armed, every wait on this stage runs out
+                s_page[s] = page;                         // for the warp that appends into this tile; released by the arrival below
                 mbar_expect_tx(bar, 2 * kTileBytes);
 #pragma unroll
                 for (int hl = 0; hl < HPC; ++hl) {
@@ -194,6 +203,23 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_kernel(DecodeParams
         for (int j = 0; j < 16; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
         float m_run = -INFINITY, l_run = 0.f;
 
+        // Fused append.  The token at position ctx - 1 is not in the pool yet: its k and v rows come with the call.
+        // Every warp of a segment that ends its sequence starts an asynchronous copy of this head's two rows into
+        // its 512 bytes of staging memory (lanes 0-15 sixteen bytes of k each, lanes 16-31 of v): no register and
+        // no instruction waits for them (a plain load here costs microseconds behind the bulk copies queued on
+        // this SM).  The warp whose 16 tokens of the last tile include the position moves the rows, once the tile
+        // has arrived, into the tile in shared memory, where the products below find them, and into the pool, where
+        // the next step will.  The last tile of a (sequence, head) belongs to one CTA and a tile's rows to one warp,
+        // so each row is written once; what the bulk copy brought for that row (stale or half-written) is replaced.
+        const bool appends = p.new_k != nullptr && sg.t1 == sg.ntiles;
+        const uint32_t stage_row = tiles_u32 + TmaSmem::patch + warp * 512 + lane * 16;
+        if (appends) {
+            cp_async_wait_all();                     // an earlier segment's copy into the same bytes (long done)
+            const __nv_bfloat16* src = lane < 16 ? p.new_k + int64_t(sg.b) * p.new_k_stride
+                                                 : p.new_v + int64_t(sg.b) * p.new_v_stride;
+            cp_async_16(stage_row, src + head * kHeadDim + (lane & 15) * 8);
+        }
+
         for (int t = sg.t0; t < sg.t1; ++t, ++it) {
             const uint32_t s = it % kStages, ph = (it / kStages) & 1;
             if (ok && !mbar_wait(full0 + s * 8, ph, p.wait_limit)) ok = false;
@@ -202,6 +228,20 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_kernel(DecodeParams
             if (ok && valid > 0) {
                 const uint32_t kbase = tiles_u32 + s * (2 * kTileBytes) + (hl * 2) * SUB;
                 const uint32_t vbase = kbase + kTileBytes;
+                if (appends && t == sg.ntiles - 1 && ((ctx - 1) % TT) / 16 == tw) {
+                    cp_async_wait_all();
+                    const uint4 new_row = ld_shared_v4(stage_row);
+                    const int c = lane & 15, r = (ctx - 1) % TT;
+                    st_shared_v4((lane < 16 ? kbase : vbase) + (c >> 3) * SUB + swz128(r, c & 7), new_row);
+                    fence_proxy_async();          // this stage's next filling is a bulk copy: order the write before it
+                    __syncwarp();
+                    const int page = s_page[s];
+                    if (page >= 0 && page < p.num_blocks) {
+                        const int64_t slot = int64_t(page) * p.block_size + (ctx - 1) % p.block_size;
+                        __nv_bfloat16* pool = static_cast<__nv_bfloat16*>(const_cast<void*>(lane < 16 ? p.k_cache : p.v_cache));
+                        *reinterpret_cast<uint4*>(pool + (slot * p.n_kv_heads + head) * kHeadDim + c * 8) = new_row;
+                    }
+                }
                 float sc[2][4];
 #pragma unroll
                 for (int j = 0; j < 2; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
@@ -744,11 +784,25 @@ int decode_prepare_device() {
     return INFER_OK;
 }
 
+// The step's new k and v rows for a launch that also appends them (null: the pools already hold them).
+struct NewRows {
+    const void* k = nullptr;
+    const void* v = nullptr;
+    int64_t k_stride = 0, v_stride = 0;
+};
+
 static int paged_decode(const infer_kv_pool_t* pool, void* out, const void* q, const int32_t* context_lens,
                         const int32_t* block_tables, int64_t bt_stride, int batch, int n_q_heads, float softmax_scale,
                         void* workspace, size_t workspace_bytes, cudaStream_t st, int force_hpc, uint32_t wait_limit,
-                        int stall_producer) {
+                        int stall_producer, const NewRows& rows = NewRows()) {
     if (!pool || !out || !q || !context_lens || !block_tables) return INFER_ERR_NULL;
+    if (rows.k || rows.v) {
+        if (!rows.k || !rows.v) return INFER_ERR_NULL;
+        if (pool->dtype != INFER_KV_BF16) return INFER_ERR_DTYPE;
+        const int64_t row = int64_t(pool->n_kv_heads) * kHeadDim;
+        if (rows.k_stride < row || rows.v_stride < row) return INFER_ERR_STRIDE;
+        if (!aligned16(rows.k) || !aligned16(rows.v) || rows.k_stride % 8 || rows.v_stride % 8) return INFER_ERR_ALIGN;
+    }
     if (batch < 0 || batch > kMaxBatch || n_q_heads <= 0 || n_q_heads % pool->n_kv_heads != 0 || bt_stride <= 0)
         return INFER_ERR_GEOMETRY;
     const int group = n_q_heads / pool->n_kv_heads;
@@ -778,6 +832,10 @@ static int paged_decode(const infer_kv_pool_t* pool, void* out, const void* q, c
     p.scale_log2 = softmax_scale * 1.4426950408889634f;
     p.wait_limit = wait_limit;
     p.stall_producer = stall_producer;
+    p.new_k = static_cast<const __nv_bfloat16*>(rows.k);
+    p.new_v = static_cast<const __nv_bfloat16*>(rows.v);
+    p.new_k_stride = rows.k_stride;
+    p.new_v_stride = rows.v_stride;
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     p.status = reinterpret_cast<int*>(ws + lay.status_off);
     p.counters = reinterpret_cast<int*>(ws + lay.counters_off);
@@ -852,6 +910,20 @@ int infer_paged_decode(const infer_kv_pool_t* pool, void* out, const void* q, co
                        float softmax_scale, void* workspace, size_t workspace_bytes, void* stream_) {
     return ib::paged_decode(pool, out, q, context_lens, block_tables, bt_stride, batch, n_q_heads, softmax_scale,
                             workspace, workspace_bytes, static_cast<cudaStream_t>(stream_), 0, ib::kDefaultWaitLimit, 0);
+}
+
+int infer_paged_decode_append(const infer_kv_pool_t* pool, void* out, const void* q, const void* k, const void* v,
+                              int64_t k_row_stride, int64_t v_row_stride, const int32_t* context_lens,
+                              const int32_t* block_tables, int64_t bt_stride, int batch, int n_q_heads,
+                              float softmax_scale, void* workspace, size_t workspace_bytes, void* stream_) {
+    if (!k || !v) return INFER_ERR_NULL;
+    ib::NewRows rows;
+    rows.k = k;
+    rows.v = v;
+    rows.k_stride = k_row_stride;
+    rows.v_stride = v_row_stride;
+    return ib::paged_decode(pool, out, q, context_lens, block_tables, bt_stride, batch, n_q_heads, softmax_scale,
+                            workspace, workspace_bytes, static_cast<cudaStream_t>(stream_), 0, ib::kDefaultWaitLimit, 0, rows);
 }
 
 int infer_selftest_paged_decode(const infer_kv_pool_t* pool, void* out, const void* q, const int32_t* context_lens,

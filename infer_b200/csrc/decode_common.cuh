@@ -41,6 +41,11 @@ struct DecodeParams {
     float scale_log2; // softmax_scale * log2(e)
     uint32_t wait_limit;   // polls before a barrier wait gives up
     int stall_producer;    // self-test only: the producer arms no copy, so every wait runs out
+    // fused append (bf16 pools): the step's new rows [batch][n_kv_heads][128], row b going to position
+    // context_lens[b] - 1 of sequence b; null = the pools already hold them
+    const __nv_bfloat16* new_k;
+    const __nv_bfloat16* new_v;
+    int64_t new_k_stride, new_v_stride;   // elements between the rows of consecutive sequences
     // scratch
     int* status;      // one word
     int* counters;    // [kMaxDecodeGrid] tickets, zero between launches

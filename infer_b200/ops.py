@@ -273,6 +273,49 @@ def paged_attn_decode(q, k_cache, v_cache, cache_seqlens, block_table, softmax_s
     return o.view(shape)
 
 
+def paged_attn_decode_append(q, key, value, k_cache, v_cache, cache_seqlens, block_table, softmax_scale,
+                             out=None, workspace=None):
+    """``store_kvcache(key, value, ...)`` and ``paged_attn_decode(q, ...)`` of one decode step in ONE launch
+    (bf16 pools; the two calls of infer/ops/attention.py:109 and :117-121).  ``key`` / ``value`` are the step's
+    new rows ``[B, Hkv, 128]`` (column slices of a fused qkv output are fine), row b belonging to position
+    ``cache_seqlens[b] - 1`` of sequence b; the slot is read off ``block_table``, so no ``slot_mapping`` is
+    needed.  The pools end up as after ``store_kvcache``.  ``q``, ``key``, ``value`` and ``out`` may be pinned
+    host tensors (see ``paged_attn_decode``)."""
+    shape = q.shape
+    q3 = q.reshape(shape[0], shape[-2], shape[-1])
+    if q3.dtype != torch.bfloat16 or not q3.is_contiguous():
+        raise RuntimeError("paged_attn_decode_append: q must be contiguous bf16")
+    b, hq, d = q3.shape
+    for name, t in (("key", key), ("value", value)):
+        if t.dtype != torch.bfloat16 or t.dim() != 3 or t.shape[0] != b or t.stride(-1) != 1 or t.stride(1) != d:
+            raise RuntimeError(f"paged_attn_decode_append: {name} must be bf16 [B, Hkv, 128] with contiguous heads")
+    for name, t in (("q", q3), ("key", key), ("value", value), ("out", out)):
+        if t is not None and not t.is_cuda and not t.is_pinned():
+            raise RuntimeError(f"paged_attn_decode_append: {name} must live on the GPU or in pinned host memory")
+    for name, t in (("cache_seqlens", cache_seqlens), ("block_table", block_table)):
+        if t.dtype != torch.int32 or not t.is_cuda:
+            raise RuntimeError(f"paged_attn_decode_append: {name} must be an int32 CUDA tensor")
+    pool = pool_of(k_cache, v_cache)
+    if pool.fp8:
+        raise RuntimeError("paged_attn_decode_append: bf16 pools only (store_kvcache + paged_attn_decode for e4m3 pools)")
+    if key.shape[1] != pool.n_kv_heads or value.shape != key.shape:
+        raise RuntimeError("paged_attn_decode_append: key / value head count differs from the pool's")
+    o = torch.empty(q3.shape, dtype=q3.dtype, device=pool.device) if out is None else out.view(q3.shape)
+    lib = _lib.load()
+    row = key.shape[1] * d
+    k_pitch = key.stride(0) if b > 1 else row
+    v_pitch = value.stride(0) if b > 1 else row
+    ws = workspace if workspace is not None else _SCRATCH.get(pool.device, "decode", pool.decode_workspace_bytes(b, hq))
+    with _on_device(pool.device):
+        rc = lib.infer_paged_decode_append(pool.handle, _ptr(o), _ptr(q3), _ptr(key), _ptr(value), k_pitch, v_pitch,
+                                           _ptr(cache_seqlens), _ptr(block_table), block_table.stride(0), b, hq,
+                                           float(softmax_scale), _ptr(ws), ws.numel(), _stream())
+        _lib.check(rc, "paged_attn_decode_append")
+        if _CHECK and not torch.cuda.is_current_stream_capturing():
+            _lib.check(lib.infer_paged_decode_status(_ptr(ws), _stream()), "paged_attn_decode_append (device status)")
+    return o.view(shape)
+
+
 # --------------------------------------------------------------------------- prefill
 def paged_attn_prefill(q, k_cache, v_cache, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
                        softmax_scale, block_table, out=None):

@@ -301,3 +301,193 @@ def test_decode_reads_q_from_and_writes_out_to_pinned_host_memory():
     assert torch.equal(out_host, want.cpu())
     with pytest.raises(RuntimeError, match="pinned"):
         ops.paged_attn_decode(w.q, d["k_cache"], d["v_cache"], d["context_lens"], d["block_tables"], w.scale, out=out_host)
+
+
+def _fused_step(w, strided=False):
+    """One decode step through the fused op, against oracle append + oracle decode."""
+    d = to_dev(w)
+    if strided:          # k and v as column slices of a wider row, the way they come out of a fused qkv projection
+        hkv = w.n_kv_heads
+        wide = torch.zeros(w.batch, 3 * hkv * 128 + 64, dtype=torch.bfloat16, device="cuda")
+        wide[:, 64:64 + hkv * 128] = d["k"].reshape(w.batch, -1)
+        wide[:, 64 + hkv * 128:64 + 2 * hkv * 128] = d["v"].reshape(w.batch, -1)
+        k = wide[:, 64:64 + hkv * 128].view(w.batch, hkv, 128)
+        v = wide[:, 64 + hkv * 128:64 + 2 * hkv * 128].view(w.batch, hkv, 128)
+    else:
+        k, v = d["k"], d["v"]
+    got = ops.paged_attn_decode_append(d["q"], k, v, d["k_cache"], d["v_cache"], d["context_lens"], d["block_tables"], w.scale)
+    torch.cuda.synchronize()
+    kc, vc = w.k_cache.clone(), w.v_cache.clone()
+    oracle.store_kvcache(w.k, w.v, kc, vc, w.slot_mapping)
+    want = oracle.paged_decode(w.q, kc, vc, w.context_lens_tensor(), w.block_tables_tensor(), w.scale)
+    assert torch.equal(d["k_cache"].cpu().view(torch.int16), kc.view(torch.int16)), "k pool differs from the oracle's append"
+    assert torch.equal(d["v_cache"].cpu().view(torch.int16), vc.view(torch.int16)), "v pool differs from the oracle's append"
+    return got, want
+
+
+@pytest.mark.parametrize("strided", [False, True])
+def test_fused_append_decode_matches_oracle(strided):
+    """store_kvcache + paged_attn_decode in one launch (infer/ops/attention.py:109 and :117-121): pools bit-exact,
+    outputs within tolerance; the shared-prefix workload has far more sequences ending in a CTA's range than
+    the sixteen the appending lanes look up at a time."""
+    for w in (workloads.config0(), workloads.config1(batch=12, lo=200, hi=3000), workloads.config4(batch=16, cap=3000)):
+        got, want = _fused_step(w, strided)
+        assert_close(got, want, ATOL_BF16, RTOL_BF16, f"fused append + decode, {w.name}")
+
+
+def test_fused_append_decode_many_short_sequences():
+    """700 sequences of 1 to 300 tokens: dozens of sequences end inside every CTA's range."""
+    gen = torch.Generator().manual_seed(700)
+    b, hq, hkv = 700, 8, 2
+    lens = torch.randint(1, 301, (b,), generator=gen)
+    nb = int((-(-lens // 256)).sum()) + 3
+    kc = torch.randn(nb, 256, hkv, 128, generator=gen).bfloat16()
+    vc = torch.randn(nb, 256, hkv, 128, generator=gen).bfloat16()
+    perm = torch.randperm(nb, generator=gen).tolist()
+    bt = torch.full((b, 2), -1, dtype=torch.int32)
+    at = 0
+    for i, n in enumerate(lens.tolist()):
+        for j in range(-(-n // 256)):
+            bt[i, j] = perm[at]
+            at += 1
+    slots = torch.tensor([int(bt[i, (n - 1) // 256]) * 256 + (n - 1) % 256 for i, n in enumerate(lens.tolist())], dtype=torch.int32)
+    q = torch.randn(b, hq, 128, generator=gen).bfloat16()
+    k = torch.randn(b, hkv, 128, generator=gen).bfloat16()
+    v = torch.randn(b, hkv, 128, generator=gen).bfloat16()
+    cl = lens.to(torch.int32)
+    dkc, dvc = kc.cuda(), vc.cuda()
+    got = ops.paged_attn_decode_append(q.cuda(), k.cuda(), v.cuda(), dkc, dvc, cl.cuda(), bt.cuda(), 0.09)
+    torch.cuda.synchronize()
+    oracle.store_kvcache(k, v, kc, vc, slots)
+    assert torch.equal(dkc.cpu().view(torch.int16), kc.view(torch.int16)) and torch.equal(dvc.cpu().view(torch.int16), vc.view(torch.int16))
+    want = oracle.paged_decode(q, kc, vc, cl, bt, 0.09)
+    assert_close(got, want, ATOL_BF16, RTOL_BF16, "fused step, 700 short sequences")
+
+
+def test_fused_append_decode_edge_lengths_and_stale_rows():
+    """The appended token alone in its sequence, alone on a fresh page, at tile and page ends; an empty row;
+    every slot no sequence owns - the new tokens' slots included - holds NaN patterns before the call."""
+    lens = [1, 2, 128, 129, 256, 257, 0, 513, 1, 300]
+    hq, hkv, nb = 16, 8, 40
+    gen = torch.Generator().manual_seed(77)
+    kc = torch.randn(nb, 256, hkv, 128, generator=gen).bfloat16()
+    vc = torch.randn(nb, 256, hkv, 128, generator=gen).bfloat16()
+    perm = torch.randperm(nb, generator=gen).tolist()
+    tables, slots, at = [], [], 0
+    owned = torch.zeros(nb * 256, dtype=torch.bool)
+    for n in lens:
+        need = -(-n // 256)
+        pages = perm[at:at + need]
+        at += need
+        tables.append(pages + [-1] * (4 - need))
+        for pos in range(n - 1):                       # the rows that exist before the step
+            owned[pages[pos // 256] * 256 + pos % 256] = True
+        slots.append(pages[(n - 1) // 256] * 256 + (n - 1) % 256 if n > 0 else -1)
+    kc.view(-1, hkv, 128)[~owned] = float("nan")
+    vc.view(-1, hkv, 128)[~owned] = float("nan")
+    q = torch.randn(len(lens), hq, 128, generator=gen).bfloat16()
+    k = torch.randn(len(lens), hkv, 128, generator=gen).bfloat16()
+    v = torch.randn(len(lens), hkv, 128, generator=gen).bfloat16()
+    bt, cl = torch.tensor(tables, dtype=torch.int32), torch.tensor(lens, dtype=torch.int32)
+    dkc, dvc = kc.cuda(), vc.cuda()
+    out = torch.full((len(lens), hq, 128), 7.0, dtype=torch.bfloat16, device="cuda")
+    ops.paged_attn_decode_append(q.cuda(), k.cuda(), v.cuda(), dkc, dvc, cl.cuda(), bt.cuda(), 0.09, out=out)
+    torch.cuda.synchronize()
+    oracle.store_kvcache(k, v, kc, vc, torch.tensor(slots, dtype=torch.int32))
+    assert torch.equal(dkc.cpu().view(torch.int16), kc.view(torch.int16)) and torch.equal(dvc.cpu().view(torch.int16), vc.view(torch.int16))
+    want = oracle.paged_decode(q, kc, vc, cl, bt, 0.09)
+    live = cl > 0
+    assert_close(out[live.cuda()], want[live], ATOL_BF16, RTOL_BF16, "fused step, edge lengths")
+    assert bool((out[~live.cuda()] == 7.0).all())
+
+
+def test_fused_append_decode_in_cuda_graph_over_steps():
+    """The fused step captured once and replayed for 20 steps, lengths advanced on the device between replays
+    (DecodeState) by the kernel directly in front of it, new rows written into static buffers: pools and outputs
+    follow the oracle step by step, across page boundaries."""
+    from infer_b200.metadata import DecodeState
+    from infer_b200.sequence import Sequence
+    hq, hkv, nb, steps = 16, 8, 16, 20
+    gen = torch.Generator().manual_seed(9)
+    start = [250, 255, 3, 100]
+    kc = torch.randn(nb, 256, hkv, 128, generator=gen).bfloat16()
+    vc = torch.randn(nb, 256, hkv, 128, generator=gen).bfloat16()
+    perm = torch.randperm(nb, generator=gen).tolist()
+    seqs, at = [], 0
+    for n in start:
+        s = Sequence(list(range(n)))
+        need = -(-(n + steps) // 256)
+        s.block_table = perm[at:at + need]
+        at += need
+        seqs.append(s)
+    state = DecodeState(len(start), 3, 256, "cuda")
+    state.load(seqs)
+    dq = torch.zeros(len(start), hq, 128, dtype=torch.bfloat16, device="cuda")
+    dk = torch.zeros(len(start), hkv, 128, dtype=torch.bfloat16, device="cuda")
+    dv = torch.zeros_like(dk)
+    out = torch.zeros_like(dq)
+    dkc, dvc = kc.cuda(), vc.cuda()
+    ops.paged_attn_decode(dq, dkc, dvc, torch.ones(len(start), dtype=torch.int32, device="cuda"), state.block_tables, 0.09)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        state.advance()
+        ops.paged_attn_decode_append(dq, dk, dv, dkc, dvc, state.context_lens, state.block_tables, 0.09, out=out)
+    state.load(seqs)                                       # capture launches nothing: lengths are still the start lengths
+    torch.cuda.synchronize()
+    lens = list(start)
+    bt = torch.tensor([s.block_table + [-1] * (3 - len(s.block_table)) for s in seqs], dtype=torch.int32)
+    for t in range(steps):
+        q = torch.randn(len(start), hq, 128, generator=gen).bfloat16()
+        k = torch.randn(len(start), hkv, 128, generator=gen).bfloat16()
+        v = torch.randn(len(start), hkv, 128, generator=gen).bfloat16()
+        dq.copy_(q); dk.copy_(k); dv.copy_(v)
+        graph.replay()
+        torch.cuda.synchronize()
+        lens = [n + 1 for n in lens]
+        slots = torch.tensor([s.block_table[(n - 1) // 256] * 256 + (n - 1) % 256 for s, n in zip(seqs, lens)], dtype=torch.int32)
+        oracle.store_kvcache(k, v, kc, vc, slots)
+        want = oracle.paged_decode(q, kc, vc, torch.tensor(lens, dtype=torch.int32), bt, 0.09)
+        assert_close(out, want, ATOL_BF16, RTOL_BF16, f"fused step {t} in a graph")
+    assert torch.equal(dkc.cpu().view(torch.int16), kc.view(torch.int16)) and torch.equal(dvc.cpu().view(torch.int16), vc.view(torch.int16))
+
+
+def test_fused_append_decode_rejects_e4m3_pools():
+    """Through the C ABI: an e4m3 pool handle is turned down with INFER_ERR_DTYPE before anything is launched."""
+    import ctypes as C
+    from infer_b200 import _lib
+    k8 = torch.zeros(4, 256, 2, 128, dtype=torch.uint8, device="cuda")
+    v8 = torch.zeros_like(k8)
+    ks = torch.zeros(4, 2, device="cuda")
+    vs = torch.zeros_like(ks)
+    pool = ops.pool_of(k8, v8, ks, vs)
+    q = torch.zeros(1, 4, 128, dtype=torch.bfloat16, device="cuda")
+    kv = torch.zeros(1, 2, 128, dtype=torch.bfloat16, device="cuda")
+    out = torch.zeros_like(q)
+    cl = torch.ones(1, dtype=torch.int32, device="cuda")
+    bt = torch.zeros(1, 1, dtype=torch.int32, device="cuda")
+    ws = torch.zeros(pool.decode_workspace_bytes(1, 4), dtype=torch.uint8, device="cuda")
+    p = lambda t: C.c_void_p(t.data_ptr())
+    rc = _lib.load().infer_paged_decode_append(pool.handle, p(out), p(q), p(kv), p(kv), 256, 256, p(cl), p(bt), 1, 1, 4,
+                                               0.09, p(ws), ws.numel(), C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == _lib.ERR_DTYPE
+    torch.cuda.synchronize()
+    assert bool((k8 == 0).all())
+
+
+def test_fused_append_decode_rows_and_output_in_pinned_host_memory():
+    """q, the new k and v rows and the output in pinned host memory (the kernel reads and writes them over PCIe):
+    the same pools and rows as with device tensors."""
+    w = workloads.config1(batch=12, lo=200, hi=3000)
+    d = to_dev(w)
+    q_h, k_h, v_h = w.q.clone().pin_memory(), w.k.clone().pin_memory(), w.v.clone().pin_memory()
+    out_h = torch.zeros(w.q.shape, dtype=torch.bfloat16).pin_memory()
+    ops.paged_attn_decode_append(q_h, k_h, v_h, d["k_cache"], d["v_cache"], d["context_lens"], d["block_tables"], w.scale, out=out_h)
+    torch.cuda.synchronize()
+    d2 = to_dev(w)
+    want = ops.paged_attn_decode_append(d2["q"], d2["k"], d2["v"], d2["k_cache"], d2["v_cache"], d2["context_lens"],
+                                        d2["block_tables"], w.scale)
+    torch.cuda.synchronize()
+    assert torch.equal(out_h, want.cpu())
+    assert torch.equal(d["k_cache"].view(torch.int16), d2["k_cache"].view(torch.int16))
+    assert torch.equal(d["v_cache"].view(torch.int16), d2["v_cache"].view(torch.int16))
