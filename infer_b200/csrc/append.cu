@@ -14,9 +14,9 @@
 //     (page, head) with atomics; raise the scales and re-encode pages whose scale grew; write the
 //     new rows - on strips of 8 tokens per warp.
 // Both ways give the bytes and scales of the CPU oracle bit for bit, whatever the scheduling.
-// The kernels of both ways are always launched; those of the way not taken return at once.  Calls of
-// at most 1024 tokens (a decode step) run the three strip phases in one thread block, separated by
-// block-wide barriers: three launches per call instead of five.
+// Calls of more than 1024 tokens launch the kernels of both ways; those of the way not taken return at once
+// (the host never reads device data).  Calls of at most 1024 tokens (a decode step) are ONE launch
+// (fp8_small_kernel): every block finds the runs for itself in shared memory.
 #include <climits>
 
 #include "common.cuh"
@@ -455,21 +455,6 @@ __global__ void __launch_bounds__(256, 3) fp8_write_kernel(Fp8Args a) {
     fp8_write_body(a, int(blockIdx.y), int64_t(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5), int64_t(gridDim.x) * kWarpsPerCta);
 }
 
-// The three strip phases in ONE thread block, for calls of few tokens (a decode step): the phases are
-// separated by block-wide barriers instead of kernel boundaries, so such a call is three launches
-// (classify, runs, this) instead of five.  It only has work when some page received several runs.
-__global__ void __launch_bounds__(256) fp8_strips_one_block_kernel(Fp8Args a, int grid_rows) {
-    pdl_launch_dependents();
-    pdl_wait();
-    if (a.ctl[kCtlConflict] == 0) return;
-    const int64_t first = threadIdx.x >> 5;
-    for (int by = 0; by < grid_rows; ++by) fp8_amax_body(a, by, first, kWarpsPerCta);
-    __syncthreads();
-    for (int by = 0; by < grid_rows; ++by) fp8_rescale_body(a, by, first, kWarpsPerCta);
-    __syncthreads();
-    for (int by = 0; by < grid_rows; ++by) fp8_write_body(a, by, first, kWarpsPerCta);
-}
-
 // --------------------------------------------------------------------------- runs
 __device__ __forceinline__ bool slot_valid(const Fp8Args& a, int s) { return s >= 0 && int64_t(s) < a.num_slots; }
 
@@ -524,61 +509,64 @@ __global__ void __launch_bounds__(256) fp8_classify_kernel(Fp8Args a) {
     }
 }
 
-// Persistent thread blocks walk the units (run, head, k|v), unit u going to block u mod gridDim.x,
-// the 2 * Hkv units of a run side by side so that neighbouring blocks read neighbouring 256-byte
-// pieces of the same rows at the same time.  A row of one head is 256 bytes = 16 lanes x 16 bytes,
-// THREADS / 16 rows per load instruction, 16 loads in flight per thread: 256 threads hold a whole
-// 256-row run (64 KiB) in registers, so the rows are read from memory once.  Runs longer than the
-// registers hold (32 threads: 32 rows) read the remainder a second time, from L2.
-// (Measured slower on 32768 rows x 8 heads, 43.2 us for this kernel: the rows parked in shared memory by 512
-// threads, two blocks per SM, 51 us - 24.5 M executed instructions against 18.9 M, the kernel is bound by its
-// instruction count; asynchronous copies into three 64 KiB buffers, one 17-warp block per SM, 70.8 us.)
+// Groups of threads walk the units (run, head, k|v), the 2 * Hkv units of a run side by side so that neighbouring
+// groups read neighbouring 256-byte pieces of the same rows at the same time.  A row of one head is 256 bytes =
+// 16 lanes x 16 bytes, THREADS / 16 rows per load instruction, 16 loads in flight per thread: a block of 256
+// threads holds a whole 256-row run (64 KiB) in registers, so the rows are read from memory once; a single warp
+// (the form the calls of few tokens use: a decode step's runs are one row long) holds 32 rows.  Rows past what
+// the registers hold are read a second time, from L2.
+// (Measured slower on 32768 rows x 8 heads, 43.2 us for the kernel of persistent 256-thread blocks: the rows parked
+// in shared memory by 512 threads, two blocks per SM, 51 us - 24.5 M executed instructions against 18.9 M;
+// asynchronous copies into three 64 KiB buffers, one 17-warp block per SM, 70.8 us; no rows held at all, pass 2
+// re-reading them from L2, with 3, 4 or 6 blocks per SM, 56 / 53 / 53 us per call against 50.5; the loads of a
+// unit issued before its run's length is known, 52.3 against 50.4.)
+
+// Scratch of one group of threads working on a unit (a block, or one warp of a block).
+struct RunScratch {
+    int len;
+    float red[8], scale, ratio;
+};
+
 template <int THREADS>
-__global__ void __launch_bounds__(THREADS, THREADS == 256 ? 2 : 16) fp8_run_kernel(Fp8Args a) {
+__device__ __forceinline__ void group_sync() {
+    if (THREADS == 32) __syncwarp();
+    else __syncthreads();
+}
+
+// The units first_unit, first_unit + unit_step, ... of the runs in run_list (global or shared memory), worked on
+// by a group of THREADS threads (tid = index in the group): a whole block, or one warp on its own.
+template <int THREADS>
+__device__ __forceinline__ void fp8_run_units(const Fp8Args& a, const int2* run_list, int n_runs, int64_t first_unit,
+                                              int64_t unit_step, int tid, RunScratch& sc, bool reset_counts) {
     constexpr int kRowsPerLoad = THREADS / 16, kHeld = 16 * kRowsPerLoad, kWarps = THREADS / 32;
-    __shared__ int s_len;
-    __shared__ float s_red[kWarps], s_scale, s_ratio;
-    pdl_launch_dependents();
-    pdl_wait();                                   // the run list, the counts and the conflict flag of the kernel in front
-    const int tid = threadIdx.x;
-    if (a.ctl[kCtlConflict] != 0) {
-        // some page got several runs: the three strip kernels do the work; all that is left to do here
-        // is to put the run counts back to zero
-        const int64_t stride = int64_t(gridDim.x) * THREADS;
-        for (int64_t i = int64_t(blockIdx.x) * THREADS + tid; i < a.n_tokens; i += stride) {
-            int slot;
-            if (is_run_start(a, i, slot)) a.count[a.page_of(slot)] = 0;
-        }
-        return;
-    }
     const int sides = 2 * a.n_kv_heads;
-    const int64_t n_units = int64_t(a.ctl[kCtlRuns]) * sides;
+    const int64_t n_units = int64_t(n_runs) * sides;
     const int lane16 = tid & 15, rsub = tid >> 4;
     const int64_t dst_pitch = int64_t(a.n_kv_heads) * kHeadDim;
-    for (int64_t unit = blockIdx.x; unit < n_units; unit += gridDim.x) {
+    for (int64_t unit = first_unit; unit < n_units; unit += unit_step) {
         const int run = int(unit / sides), y = int(unit - int64_t(run) * sides);
         const int head = y >> 1;
         const Fp8Side side = (y & 1) ? a.v : a.k;
-        const int2 first = a.run_list[run];
+        const int2 first = run_list[run];
         const int64_t start = first.x;
         const int slot0 = first.y;
         const int64_t page = a.page_of(slot0);
-        if (y == 0 && tid == 0) a.count[page] = 0;          // nobody reads the counts any more
+        if (reset_counts && y == 0 && tid == 0) a.count[page] = 0;          // nobody reads the counts any more
         // length of the run: the first offset whose token does not continue it
         int len = 1;
         for (int base = 1;; base += THREADS) {
-            if (tid == 0) s_len = INT_MAX;
-            __syncthreads();
+            if (tid == 0) sc.len = INT_MAX;
+            group_sync<THREADS>();
             const int64_t i = start + base + tid;
             bool cont = i < a.n_tokens;
             if (cont) {
                 const int s = __ldg(a.slot_mapping + i);
                 cont = s == slot0 + base + tid && int64_t(s) < a.num_slots && a.page_of(s) == page;
             }
-            if (!cont) atomicMin(&s_len, base + tid);
-            __syncthreads();
-            const int first_bad = s_len;
-            __syncthreads();
+            if (!cont) atomicMin(&sc.len, base + tid);
+            group_sync<THREADS>();
+            const int first_bad = sc.len;
+            group_sync<THREADS>();
             if (first_bad != INT_MAX) { len = first_bad; break; }
             len = base + THREADS;
         }
@@ -602,11 +590,11 @@ __global__ void __launch_bounds__(THREADS, THREADS == 256 ? 2 : 16) fp8_run_kern
         float m = fmaxf(__low2float(best), __high2float(best));
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-        if ((tid & 31) == 0) s_red[tid >> 5] = m;
-        __syncthreads();
+        if ((tid & 31) == 0) sc.red[tid >> 5] = m;
+        group_sync<THREADS>();
         if (tid == 0) {
 #pragma unroll
-            for (int w = 1; w < kWarps; ++w) m = fmaxf(m, s_red[w]);
+            for (int w = 1; w < kWarps; ++w) m = fmaxf(m, sc.red[w]);
             float s = old, ratio = -1.0f;
             if (m > 0.0f) {
                 const float c = __fdiv_rn(m, 448.0f);
@@ -616,11 +604,11 @@ __global__ void __launch_bounds__(THREADS, THREADS == 256 ? 2 : 16) fp8_run_kern
                     if (old > 0.0f) ratio = __fdiv_rn(old, c);
                 }
             }
-            s_scale = s;
-            s_ratio = ratio;
+            sc.scale = s;
+            sc.ratio = ratio;
         }
-        __syncthreads();
-        const float scale = s_scale, ratio = s_ratio;
+        group_sync<THREADS>();
+        const float scale = sc.scale, ratio = sc.ratio;
         if (ratio >= 0.0f) {
             // the page's scale grew: re-encode what the page holds for this head (rows this run is about
             // to overwrite included, which is harmless), before any new row is written
@@ -634,7 +622,7 @@ __global__ void __launch_bounds__(THREADS, THREADS == 256 ? 2 : 16) fp8_run_kern
                 q.w = rescale4(q.w, ratio);
                 *p = q;
             }
-            __syncthreads();
+            group_sync<THREADS>();
         }
         // pass 2: quantise with the final scale
         const Divisor div(scale);
@@ -655,10 +643,96 @@ __global__ void __launch_bounds__(THREADS, THREADS == 256 ? 2 : 16) fp8_run_kern
         for (int row = kHeld + rsub; row < len; row += kRowsPerLoad)
             *reinterpret_cast<uint2*>(dst + row * dst_pitch) =
                 div.quantise8(__ldg(reinterpret_cast<const uint4*>(src + (start + row) * side.pitch)));
-        __syncthreads();                          // s_red, s_scale and s_ratio are reused by the next unit
+        group_sync<THREADS>();                          // s_red, sc.scale and sc.ratio are reused by the next unit
     }
 }
 
+
+
+// Calls of more than 1024 tokens: persistent blocks of 256 threads, a block per unit, over the run list the
+// classification kernel wrote.
+__global__ void __launch_bounds__(256, 2) fp8_run_kernel(Fp8Args a) {
+    __shared__ RunScratch s_scratch;
+    pdl_launch_dependents();
+    pdl_wait();                                   // the run list, the counts and the conflict flag of the kernel in front
+    const int tid = threadIdx.x;
+    if (a.ctl[kCtlConflict] != 0) {
+        // some page got several runs: the three strip kernels do the work; all that is left to do here
+        // is to put the run counts back to zero
+        const int64_t stride = int64_t(gridDim.x) * 256;
+        for (int64_t i = int64_t(blockIdx.x) * 256 + tid; i < a.n_tokens; i += stride) {
+            int slot;
+            if (is_run_start(a, i, slot)) a.count[a.page_of(slot)] = 0;
+        }
+        return;
+    }
+    fp8_run_units<256>(a, a.run_list, a.ctl[kCtlRuns], blockIdx.x, gridDim.x, tid, s_scratch, true);
+}
+
+// Calls of at most kSmallTokens tokens (a decode step, a short prompt) in ONE launch.  Every block cuts the whole
+// token list into runs for itself, in shared memory - a few kilobytes of slot_mapping out of L2 - and finds out
+// whether some page receives two runs (a hash table of the runs' pages); all blocks come to the same list and the
+// same answer, so no block has to wait for another.  Then every warp takes (run, head, k|v) units of its own.  If
+// some page did get two runs, block 0 alone runs the three strip phases, separated by block-wide barriers.
+constexpr int kSmallTokens = 1024;
+
+__global__ void __launch_bounds__(256, 2) fp8_small_kernel(Fp8Args a, int grid_rows) {
+    constexpr int kPer = kSmallTokens / 256;      // consecutive tokens per thread
+    constexpr int kHash = 2 * kSmallTokens;
+    __shared__ int2 s_runs[kSmallTokens];
+    __shared__ int s_hash[kHash];                 // page + 1 of a run, 0 = free
+    __shared__ int s_warp_runs[8], s_conflict;
+    __shared__ RunScratch s_scratch[8];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int i = tid; i < kHash; i += 256) s_hash[i] = 0;
+    if (tid == 0) s_conflict = 0;
+    int slot[kPer], mine = 0;
+    bool starts[kPer];
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+        const int64_t i = int64_t(tid) * kPer + j;
+        starts[j] = i < a.n_tokens && is_run_start(a, i, slot[j]);
+        mine += starts[j];
+    }
+    int incl = mine;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += v;
+    }
+    if (lane == 31) s_warp_runs[warp] = incl;
+    __syncthreads();                              // also: the hash table is clear
+    int at = incl - mine, n_runs = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+        if (w < warp) at += s_warp_runs[w];
+        n_runs += s_warp_runs[w];
+    }
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+        if (!starts[j]) continue;
+        s_runs[at++] = make_int2(tid * kPer + j, slot[j]);
+        const int key = int(a.page_of(slot[j])) + 1;
+        for (uint32_t h = (uint32_t(key) * 2654435761u) >> 21;; h = (h + 1) & (kHash - 1)) {
+            const int seen = atomicCAS(&s_hash[h], 0, key);
+            if (seen == key) s_conflict = 1;
+            if (seen == 0 || seen == key) break;
+        }
+    }
+    __syncthreads();
+    if (s_conflict) {
+        if (blockIdx.x != 0) return;
+        for (int by = 0; by < grid_rows; ++by) fp8_amax_body(a, by, warp, kWarpsPerCta);
+        __syncthreads();
+        for (int by = 0; by < grid_rows; ++by) fp8_rescale_body(a, by, warp, kWarpsPerCta);
+        __syncthreads();
+        for (int by = 0; by < grid_rows; ++by) fp8_write_body(a, by, warp, kWarpsPerCta);
+        return;
+    }
+    fp8_run_units<32>(a, s_runs, n_runs, int64_t(blockIdx.x) * 8 + warp, int64_t(gridDim.x) * 8, lane, s_scratch[warp], false);
+}
 
 }  // namespace ib
 
@@ -723,22 +797,19 @@ int infer_kv_append(const infer_kv_pool_t* pool, const void* k, const void* v, i
     a.run_list = reinterpret_cast<int2*>((reinterpret_cast<uintptr_t>(a.count + pool->num_blocks) + 7) & ~uintptr_t(7));
     a.ctl = reinterpret_cast<int*>(a.run_list + pool->num_blocks);
     a.num_blocks = int(pool->num_blocks);
-    // runs: count and list them, then persistent thread blocks take (run, head, k|v) units
-    ib::fp8_classify_kernel<<<unsigned((n_tokens + 255) / 256), 256, 0, stream>>>(a);
-    if (n_tokens <= 1024) {
-        int64_t grid = n_tokens * 2 * pool->n_kv_heads;              // at most one unit per block
-        if (grid > int64_t(pool->sm_count) * 16) grid = int64_t(pool->sm_count) * 16;
-        IB_CUDA(ib::launch_pdl(ib::fp8_run_kernel<32>, dim3(unsigned(grid)), dim3(32), 0, stream, a));
-    } else {
-        IB_CUDA(ib::launch_pdl(ib::fp8_run_kernel<256>, dim3(unsigned(pool->sm_count) * 2), dim3(256), 0, stream, a));
-    }
-    // strips: only when some page received several runs (the kernels return at once otherwise)
-    const int64_t strips = (n_tokens + ib::kStrip - 1) / ib::kStrip;
-    const int rows = 2 * ((pool->n_kv_heads + 1) / 2);             // grid rows: (k|v) x head pair
-    if (n_tokens <= 1024) {
-        IB_CUDA(ib::launch_pdl(ib::fp8_strips_one_block_kernel, dim3(1), dim3(256), 0, stream, a, rows));
+    const int rows = 2 * ((pool->n_kv_heads + 1) / 2);             // grid rows of the strip phases: (k|v) x head pair
+    if (n_tokens <= ib::kSmallTokens) {
+        // one launch: every block finds the runs for itself, every warp takes units (at most n_tokens * 2 Hkv of them)
+        int64_t grid = (n_tokens * 2 * pool->n_kv_heads + 7) / 8;
+        if (grid > int64_t(pool->sm_count) * 2) grid = int64_t(pool->sm_count) * 2;
+        IB_CUDA(ib::launch_pdl(ib::fp8_small_kernel, dim3(unsigned(grid)), dim3(256), 0, stream, a, rows));
         return ib::check_launch();
     }
+    // runs: count and list them, then persistent thread blocks take (run, head, k|v) units
+    ib::fp8_classify_kernel<<<unsigned((n_tokens + 255) / 256), 256, 0, stream>>>(a);
+    IB_CUDA(ib::launch_pdl(ib::fp8_run_kernel, dim3(unsigned(pool->sm_count) * 2), dim3(256), 0, stream, a));
+    // strips: only when some page received several runs (the kernels return at once otherwise)
+    const int64_t strips = (n_tokens + ib::kStrip - 1) / ib::kStrip;
     int64_t per_row = (strips + ib::kWarpsPerCta - 1) / ib::kWarpsPerCta;
     // The strip kernels stride over their strips, so any grid works; they only have work when slots are
     // scattered, and otherwise every block of theirs just reads a flag and leaves: 6 blocks per SM keeps
