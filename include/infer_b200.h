@@ -121,6 +121,9 @@ INFER_API int infer_decode_step_advance(int32_t* context_lens, int32_t* slot_map
  * flash_attn_decode stub (src/operators/flashattn/flashattn_decode.cu:1-13).
  * q, out: bf16 [batch, n_q_heads, 128] contiguous.  Any n_q_heads that is a multiple of the
  * pool's kv heads with at most 8 query heads per kv head (group sizes 1..8, e.g. 40 over 8).
+ * q and out may also be pinned host memory given by its device-valid address (with unified addressing the
+ * pointer itself): the kernel then reads the queries and writes the output rows over PCIe, which saves a
+ * host-fed caller two copies.  The same holds for q, k, v and out of infer_paged_decode_append.
  * workspace: infer_paged_decode_workspace_bytes() of 16-byte aligned device memory that the
  * caller zero-fills ONCE before its first use; a call leaves the part that has to be zero
  * (a status word and the ticket counters of contexts split over thread blocks) at zero
