@@ -83,7 +83,15 @@ struct TmaSmem {
     static constexpr int bars = scan + kTmaThreads * 4;
     static constexpr int pages = bars + 2 * kStages * 8 + 16;      // page of the tile in each stage (fused append)
     static constexpr int patch = pages + 16;                        // 512 bytes per consumer warp: a new k row and v row
-    static constexpr int total = patch + kConsumerWarps * 512;
+    static constexpr int rem = patch + kConsumerWarps * 512;        // tokens in every sequence's last tile, one byte each
+    static constexpr int total = rem + kMaxBatch;
+};
+
+// Tensor maps with boxes of 16, 32 and 64 token rows: the last tile of a sequence is copied with the smallest box
+// that holds its tokens (the rows behind them belong to nobody, or to the future).
+struct TailMaps {
+    CUtensorMap k[3];
+    CUtensorMap v[3];
 };
 static_assert(TmaSmem::patch % 16 == 0, "the staging rows are written by 16-byte asynchronous copies");
 
@@ -92,7 +100,8 @@ __device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, 256;"
 template <int HPC>
 __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_kernel(DecodeParams p,
                                                                     const __grid_constant__ CUtensorMap map_k,
-                                                                    const __grid_constant__ CUtensorMap map_v) {
+                                                                    const __grid_constant__ CUtensorMap map_v,
+                                                                    const __grid_constant__ TailMaps tails) {
     constexpr int TT = 128 / HPC;          // tokens per tile
     constexpr int WPH = kConsumerWarps / HPC;   // consumer warps per kv head
     constexpr int SUB = TT * 128;          // bytes of one (head, half) sub-tile
@@ -120,7 +129,8 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_kernel(DecodeParams
     // them may be the kernel directly in front: wait for it before the first look at them.  (Two attention
     // launches never share an SM - each takes nearly all of its shared memory - so nothing is lost.)
     if (p.new_k != nullptr) pdl_wait();
-    build_tile_prefix(p.context_lens, p.batch, TT, s_tp, s_scan);   // ends with __syncthreads
+    uint8_t* s_rem = smem + TmaSmem::rem;
+    build_tile_prefix(p.context_lens, p.batch, TT, s_tp, s_scan, s_rem);   // ends with __syncthreads
     // Everything above only reads step metadata; the pools and q may still be written by the
     // kernel in front of this one (the append) when this kernel was launched programmatically.
     pdl_launch_dependents();
@@ -151,14 +161,29 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_kernel(DecodeParams
                 const uint32_t kdst = tiles_u32 + s * (2 * kTileBytes), vdst = kdst + kTileBytes;
                 if (p.stall_producer) continue;          // self-test: nothing is armed, every wait on this stage runs out
                 s_page[s] = page;                         // for the warp that appends into this tile; released by the arrival below
-                mbar_expect_tx(bar, 2 * kTileBytes);
+                // a sequence's last tile: only the rows that exist (in boxes of 16, 32 or 64 rows); what the stage
+                // holds behind them is masked by the consumers like any row past the context's end
+                const CUtensorMap* mk = &map_k;
+                const CUtensorMap* mv = &map_v;
+                uint32_t bytes = 2 * kTileBytes;
+                if (t == sg.ntiles - 1) {
+                    const int rem = s_rem[sg.b];
+#pragma unroll
+                    for (int i = 2; i >= 0; --i)
+                        if (rem != 0 && (16 << i) < TT && rem <= (16 << i)) {
+                            mk = &tails.k[i];
+                            mv = &tails.v[i];
+                            bytes = 4 * HPC * (16 << i) * 128;
+                        }
+                }
+                mbar_expect_tx(bar, bytes);
 #pragma unroll
                 for (int hl = 0; hl < HPC; ++hl) {
                     const int head = sg.hg * HPC + hl;
 #pragma unroll
                     for (int half = 0; half < 2; ++half) {
-                        tma_load_3d(kdst + (hl * 2 + half) * SUB, &map_k, bar, half * 64, head, slot0);
-                        tma_load_3d(vdst + (hl * 2 + half) * SUB, &map_v, bar, half * 64, head, slot0);
+                        tma_load_3d(kdst + (hl * 2 + half) * SUB, mk, bar, half * 64, head, slot0);
+                        tma_load_3d(vdst + (hl * 2 + half) * SUB, mv, bar, half * 64, head, slot0);
                     }
                 }
             }
@@ -747,8 +772,13 @@ template <int HPC>
 static int launch_bf16(const DecodeParams& p, const infer_kv_pool* pool, int grid, cudaStream_t st) {
     int idx = 0;
     while ((16 << idx) != 128 / HPC) ++idx;
+    TailMaps tails;
+    for (int i = 0; i < 3; ++i) {
+        tails.k[i] = pool->maps[i].k;
+        tails.v[i] = pool->maps[i].v;
+    }
     IB_CUDA(launch_pdl(decode_tma_kernel<HPC>, dim3(grid), dim3(kTmaThreads), TmaSmem::total + 1024, st, p,
-                       pool->maps[idx].k, pool->maps[idx].v));
+                       pool->maps[idx].k, pool->maps[idx].v, tails));
     return INFER_OK;
 }
 

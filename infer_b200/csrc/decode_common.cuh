@@ -75,8 +75,10 @@ inline DecodeLayout decode_layout(int grid, int rows) {
 // Exclusive prefix of tiles per sequence into shared memory (s_tp[batch] = total).
 // Every thread of the CTA must call it (blockDim.x a multiple of 32, at most 1024); ends with
 // a __syncthreads().  Warp-shuffle scan, then the warp totals through shared memory.
+// With s_rem (one byte per sequence, optional) it also records how many tokens the sequence's last tile holds
+// (context_len mod tile_tokens; 0 = a full tile), for a producer that copies only the rows that exist.
 __device__ inline void build_tile_prefix(const int32_t* __restrict__ context_lens, int batch, int tile_tokens,
-                                         int* s_tp, int* s_scratch /* 32 ints */) {
+                                         int* s_tp, int* s_scratch /* 32 ints */, uint8_t* s_rem = nullptr) {
     const int nt = blockDim.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int per = (batch + nt - 1) / nt;
     const int lo = min(batch, tid * per), hi = min(batch, lo + per);
@@ -94,7 +96,9 @@ __device__ inline void build_tile_prefix(const int32_t* __restrict__ context_len
     for (int w = 0; w < warp; ++w) run += s_scratch[w];
     for (int i = lo; i < hi; ++i) {
         s_tp[i] = run;
-        run += (max(context_lens[i], 0) + tile_tokens - 1) / tile_tokens;
+        const int n = max(context_lens[i], 0);
+        run += (n + tile_tokens - 1) / tile_tokens;
+        if (s_rem != nullptr) s_rem[i] = uint8_t(n % tile_tokens);
     }
     if (tid == nt - 1) s_tp[batch] = run;
     __syncthreads();
