@@ -87,11 +87,12 @@ struct TmaSmem {
     static constexpr int total = rem + kMaxBatch;
 };
 
-// Tensor maps with boxes of 16, 32 and 64 token rows: the last tile of a sequence is copied with the smallest box
-// that holds its tokens (the rows behind them belong to nobody, or to the future).
+// Tensor maps with boxes of 16, 32, 64 and 128 token rows: the last tile of a sequence is copied with the smallest
+// box that holds its tokens (the rows behind them belong to nobody, or to the future).
+constexpr int kTailMaps = 4;
 struct TailMaps {
-    CUtensorMap k[3];
-    CUtensorMap v[3];
+    CUtensorMap k[kTailMaps];
+    CUtensorMap v[kTailMaps];
 };
 static_assert(TmaSmem::patch % 16 == 0, "the staging rows are written by 16-byte asynchronous copies");
 
@@ -169,7 +170,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_kernel(DecodeParams
                 if (t == sg.ntiles - 1) {
                     const int rem = s_rem[sg.b];
 #pragma unroll
-                    for (int i = 2; i >= 0; --i)
+                    for (int i = kTailMaps - 1; i >= 0; --i)
                         if (rem != 0 && (16 << i) < TT && rem <= (16 << i)) {
                             mk = &tails.k[i];
                             mv = &tails.v[i];
@@ -410,13 +411,15 @@ struct Fp8Smem {
     static constexpr int scan = prefix + (kMaxBatch + 1) * 4 + 12;
     static constexpr int bars = scan + threads * 4;
     static constexpr int meta = bars + 2 * kStages * 8 + 16;      // [kStages][HPC][2] floats: k scale, v scale
-    static constexpr int total = meta + kStages * HPC * 8;
+    static constexpr int rem = meta + kStages * HPC * 8;           // tokens in every sequence's last tile, one byte each
+    static constexpr int total = rem + kMaxBatch;
 };
 
 template <int HPC>
 __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_fp8_kernel(DecodeParams p,
                                                                           const __grid_constant__ CUtensorMap map_k,
-                                                                          const __grid_constant__ CUtensorMap map_v) {
+                                                                          const __grid_constant__ CUtensorMap map_v,
+                                                                          const __grid_constant__ TailMaps tails) {
     static_assert(HPC == 1 || HPC == 2 || HPC == 4 || HPC == 8, "1, 2, 4 or 8 kv heads per tile");
     constexpr int W = kConsumerWarps;
     constexpr int TT = kFp8TileTokens / HPC;     // tokens per tile
@@ -446,7 +449,8 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_fp8_kernel(DecodePa
         fence_mbar_init();
         fence_proxy_async();
     }
-    build_tile_prefix(p.context_lens, p.batch, TT, s_tp, s_scan);
+    uint8_t* s_rem = smem + L::rem;
+    build_tile_prefix(p.context_lens, p.batch, TT, s_tp, s_scan, s_rem);
     pdl_launch_dependents();
     pdl_wait();
 
@@ -486,11 +490,25 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_fp8_kernel(DecodePa
                 const uint32_t bar = full0 + s * 8;
                 const uint32_t kdst = tiles_u32 + s * (2 * kTileBytes), vdst = kdst + kTileBytes;
                 if (p.stall_producer) continue;          // self-test: nothing is armed, every wait on this stage runs out
-                mbar_expect_tx(bar, 2 * kTileBytes);      // release: the scales above are visible to the waiters
+                // a sequence's last tile: only the rows that exist (see decode_tma_kernel)
+                const CUtensorMap* mk = &map_k;
+                const CUtensorMap* mv = &map_v;
+                uint32_t bytes = 2 * kTileBytes;
+                if (t == sg.ntiles - 1) {
+                    const int rem = s_rem[sg.b];
+#pragma unroll
+                    for (int i = kTailMaps - 1; i >= 0; --i)
+                        if (rem != 0 && (16 << i) < TT && rem <= (16 << i)) {
+                            mk = &tails.k[i];
+                            mv = &tails.v[i];
+                            bytes = 2 * HPC * (16 << i) * 128;
+                        }
+                }
+                mbar_expect_tx(bar, bytes);               // release: the scales above are visible to the waiters
 #pragma unroll
                 for (int hl = 0; hl < HPC; ++hl) {        // the heads' boxes back to back: adjacent lines of every token row
-                    tma_load_3d(kdst + hl * kHeadBytes, &map_k, bar, 0, sg.hg * HPC + hl, slot0);
-                    tma_load_3d(vdst + hl * kHeadBytes, &map_v, bar, 0, sg.hg * HPC + hl, slot0);
+                    tma_load_3d(kdst + hl * kHeadBytes, mk, bar, 0, sg.hg * HPC + hl, slot0);
+                    tma_load_3d(vdst + hl * kHeadBytes, mv, bar, 0, sg.hg * HPC + hl, slot0);
                 }
             }
             g += sg.t1 - sg.t0;
@@ -768,15 +786,20 @@ static DecodeConfig decode_config(const infer_kv_pool* pool, int n_q_heads, size
     return c;
 }
 
+static TailMaps tail_maps(const infer_kv_pool* pool) {
+    TailMaps tails;
+    for (int i = 0; i < kTailMaps; ++i) {
+        tails.k[i] = pool->maps[i].k;
+        tails.v[i] = pool->maps[i].v;
+    }
+    return tails;
+}
+
 template <int HPC>
 static int launch_bf16(const DecodeParams& p, const infer_kv_pool* pool, int grid, cudaStream_t st) {
     int idx = 0;
     while ((16 << idx) != 128 / HPC) ++idx;
-    TailMaps tails;
-    for (int i = 0; i < 3; ++i) {
-        tails.k[i] = pool->maps[i].k;
-        tails.v[i] = pool->maps[i].v;
-    }
+    const TailMaps tails = tail_maps(pool);
     IB_CUDA(launch_pdl(decode_tma_kernel<HPC>, dim3(grid), dim3(kTmaThreads), TmaSmem::total + 1024, st, p,
                        pool->maps[idx].k, pool->maps[idx].v, tails));
     return INFER_OK;
@@ -787,7 +810,7 @@ static int launch_fp8(const DecodeParams& p, const infer_kv_pool* pool, int grid
     int idx = 0;
     while ((16 << idx) != kFp8TileTokens / HPC) ++idx;
     IB_CUDA(launch_pdl(decode_tma_fp8_kernel<HPC>, dim3(grid), dim3(kTmaThreads), Fp8Smem<HPC>::total + 1024, st, p,
-                       pool->maps[idx].k, pool->maps[idx].v));
+                       pool->maps[idx].k, pool->maps[idx].v, tail_maps(pool)));
     return INFER_OK;
 }
 
