@@ -58,8 +58,8 @@ UNIT = "GB/s"
 BASE_BATCH = 64
 # DRAM traffic figures from the ncu captures summarised under profiles/ (dram__bytes_read.sum +
 # dram__bytes_write.sum of one launch of a small case; each tile is read once, so traffic grows with the
-# units processed): decode_tma_kernel 259.5 MB for 249.9 MB of KV; prefill_tc_kernel 119.0 MB for 4 sequences.
-DECODE_TRAFFIC_PER_KV_BYTE = 259.5 / 249.9
+# units processed): decode_tma_kernel 253.5 MB for 249.9 MB of KV; prefill_tc_kernel 119.0 MB for 4 sequences.
+DECODE_TRAFFIC_PER_KV_BYTE = 253.5 / 249.9
 PREFILL_TRAFFIC_PER_SEQUENCE = 119.0e6 / 4
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_TFLOPS = 1400.0
@@ -859,7 +859,7 @@ def main():
                          "frac_of_8000": achieved / 8000.0, "decode_ms": decode_ms,
                          "decode_ms_median": r["decode_ms_median"], "decode_ms_min": r["decode_ms_min"],
                          "traffic": kv_bytes * DECODE_TRAFFIC_PER_KV_BYTE,
-                         "traffic_note": "DRAM bytes per decode launch: ncu capture of a batch-16 case (259.5 MB read + "
+                         "traffic_note": "DRAM bytes per decode launch: ncu capture of a batch-16 case (253.5 MB read + "
                                          "written for 249.9 MB of KV), scaled by KV bytes"},
             "append": {"decode_shape_us": append_ms * 1e3, "decode_shape_tok_s": n_seq / (append_ms * 1e-3),
                        "bulk_rows": n_bulk, "bulk_tok_s": n_bulk / (bulk_ms * 1e-3),
