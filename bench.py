@@ -27,6 +27,8 @@ One JSON line is printed by rank 0:
   strong     strong scaling: the long-context configuration (batch 256, 64q/8kv heads) and the
              Qwen3-8B decode shape at batch 64, the 8 KV heads sharded N ways, with the single-GPU
              step they scale from measured in the same process;
+  engine     (N = 1) the path inside the engine loop: scheduler, step metadata, one synthetic-weight attention
+             layer, decode through per-bucket CUDA graphs; prefill tok/s and decode ms per step, host work included;
   validated  (N > 1) attention outputs all-gathered over NCCL and checked against the CPU oracle;
   reference_gpu  (N = 1) the library call the reference makes for decode (flash_attn's
              flash_attn_with_kvcache), timed on the same tensors;
@@ -525,6 +527,48 @@ def bench_flash_attn(w, cl, bt, slots, out, steps):
             "max_abs_diff_vs_this_library": err}
 
 
+def bench_engine(device, n_requests=64, max_tokens=48, device_metadata=False):
+    """The path inside the engine loop (scheduler -> step metadata -> model -> postprocess, the reference's
+    LLMEngine.step, infer/engine/llm_engine.py:46-82) with ONE synthetic-weight attention layer as the model:
+    prompts U[512, 2048] prefilled, then decode steps through per-bucket CUDA graphs.  Host scheduling and the
+    per-step metadata upload are inside the timed regions (wall clock around synchronised steps)."""
+    import numpy as np
+    from infer_b200.context import reset_context
+    from infer_b200.engine import AttentionLayerModel, Engine, LayerRunner, Scheduler
+    rng = np.random.default_rng(77)
+    hidden, hq, hkv, vocab, block = 2048, 32, 8, 4096, 256
+    prompts = [rng.integers(0, vocab, size=int(n)).tolist() for n in rng.integers(512, 2049, size=n_requests)]
+    pages = sum(-(-(len(pr) + max_tokens) // block) for pr in prompts) + 8
+    model = AttentionLayerModel(hidden, hq, hkv, vocab, 4096, device, seed=3)
+    runner = LayerRunner(model, pages, block, n_requests, 4096, device, device_metadata=device_metadata)
+    engine = Engine(runner, Scheduler(pages, block, max_num_seqs=n_requests, max_num_batched_tokens=1 << 20))
+    for pr in prompts:
+        engine.add_request(pr, max_tokens)
+    t = {True: 0.0, False: 0.0}
+    n = {True: 0, False: 0}
+    toks = {True: 0, False: 0}
+    while not engine.scheduler.is_finished():
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        seqs, is_prefill, _ = engine.step()
+        torch.cuda.synchronize()
+        t[is_prefill] += time.perf_counter() - t0
+        n[is_prefill] += 1
+        toks[is_prefill] += sum(len(s) - 1 for s in seqs) if is_prefill else len(seqs)
+        reset_context()
+    res = {"model": f"one attention layer, hidden {hidden}, {hq}q/{hkv}kv heads, synthetic weights (the real checkpoints are "
+                    "not in the image); qkv / output projections and norm + rotary in PyTorch, append + attention through "
+                    "this library",
+           "requests": n_requests, "prompt_tokens": toks[True], "prefill_steps": n[True],
+           "prefill_tok_s": toks[True] / max(t[True], 1e-9),
+           "decode_steps": n[False], "decode_ms_per_step": 1e3 * t[False] / max(n[False], 1),
+           "decode_tok_s": toks[False] / max(t[False], 1e-9),
+           "decode_launch": "one CUDA graph per batch-size bucket, replayed; host scheduling and metadata upload inside the time"}
+    del engine, runner, model
+    torch.cuda.empty_cache()
+    return res
+
+
 def bench_strong(ops, kind, world, rank, device, steps, warmup, barrier, peak):
     """One strong-scaling workload at ``world`` GPUs and, in the same process, the single-GPU problem it
     scales from (all 8 KV heads on this GPU)."""
@@ -578,7 +622,7 @@ def main():
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "long"],
                     help="decode = the full line; prefill = only the paged chunked-prefill configuration (single GPU, "
                          "used for profiler captures); long = only the long-context configuration as the headline")
-    ap.add_argument("--only", default="", help="comma-separated sub-benchmarks to run (prefill,fp8,fused,strong,flash); "
+    ap.add_argument("--only", default="", help="comma-separated sub-benchmarks to run (prefill,fp8,fused,strong,flash,engine); "
                                                "default: all, or none with --profile")
     ap.add_argument("--fp8", action="store_true", help="same as adding fp8 to --only")
     ap.add_argument("--batch", type=int, default=BASE_BATCH,
@@ -622,7 +666,7 @@ def main():
         dist.init_process_group("nccl", device_id=device)
     want = set(filter(None, args.only.split(",")))
     if not want and not args.profile:
-        want = {"prefill", "fp8", "fused", "strong", "flash"}
+        want = {"prefill", "fp8", "fused", "strong", "flash", "engine"}
     if args.fp8:
         want.add("fp8")
 
@@ -814,6 +858,17 @@ def main():
     prefill = None
     if "prefill" in want and world == 1:
         prefill = bench_prefill(ops, device, 16, 10, 3)
+    engine = None
+    if "engine" in want and world == 1:
+        try:
+            engine = bench_engine(device)
+            on_device = bench_engine(device, device_metadata=True)
+            engine["decode_ms_per_step_device_metadata"] = on_device["decode_ms_per_step"]
+            engine["decode_tok_s_device_metadata"] = on_device["decode_tok_s"]
+            engine["device_metadata"] = ("the same loop with the decode step's lengths, slots and positions advanced on the "
+                                         "GPU by one small kernel instead of rebuilt and uploaded by the host every step")
+        except Exception as exc:                                  # pragma: no cover - reported, the line still prints
+            engine = {"failed": f"{type(exc).__name__}: {str(exc)[:200]}"}
 
     if rank == 0:
         value = job_bytes / (step_ms * 1e-3) / 1e9
@@ -869,7 +924,7 @@ def main():
                        "bulk2_gbs": bulk2_bytes / (bulk2_ms * 1e-3) / 1e9 if bulk2_ms else None},
             "clocks": clocks.summary(),
         }
-        for key, obj in (("fp8_kv", fp8), ("fused_append", fused), ("prefill", prefill), ("strong", strong),
+        for key, obj in (("fp8_kv", fp8), ("fused_append", fused), ("prefill", prefill), ("strong", strong), ("engine", engine),
                          ("validated", validated), ("reference_gpu", flash), ("cpu_baseline", cpu)):
             if obj is not None:
                 line[key] = obj

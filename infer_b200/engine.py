@@ -149,9 +149,17 @@ class LayerRunner:
     prefill, decode through per-bucket CUDA graphs over static buffers."""
 
     def __init__(self, model: AttentionLayerModel, num_blocks: int, block_size: int, max_num_seqs: int, max_model_len: int,
-                 device, enforce_eager: bool = False):
+                 device, enforce_eager: bool = False, device_metadata: bool = False):
+        """``device_metadata``: keep the decode step's metadata on the GPU (``metadata.DecodeState``): while the
+        batch keeps its composition a step costs one small kernel (lengths + 1, slots and positions from the block
+        tables already on the device) and the upload of newly allocated page ids, instead of the reference's
+        per-step rebuild and upload (infer/engine/model_runner.py:110-126); the graphs read the state's tensors."""
         self.model, self.block_size, self.device, self.enforce_eager = model, block_size, torch.device(device), enforce_eager
         self.max_num_seqs, self.max_pages = max_num_seqs, -(-max_model_len // block_size)
+        self.state = None
+        if device_metadata and not enforce_eager:
+            self.state = metadata.DecodeState(min(max_num_seqs, 512), self.max_pages, block_size, self.device)
+            self._state_ids, self._state_lens = None, None
         # one zero-filled tensor [2, num_blocks, block_size, Hkv, 128]; the layer gets its two halves
         self.kv_cache = torch.zeros(2, num_blocks, block_size, model.n_kv_heads, 128, dtype=torch.bfloat16, device=device)
         model.attn.k_cache, model.attn.v_cache = self.kv_cache[0], self.kv_cache[1]
@@ -172,6 +180,9 @@ class LayerRunner:
             block_tables=torch.zeros(max_bs, self.max_pages, dtype=torch.int32, device=dev),
             outputs=torch.zeros(max_bs, self.model.hidden, dtype=torch.bfloat16, device=dev))
         v = self.vars
+        if self.state is not None:                 # the graphs read the device-resident state directly
+            v.update(positions=self.state.positions, slot_mapping=self.state.slot_mapping,
+                     context_lens=self.state.context_lens, block_tables=self.state.block_tables)
         self.graph_bs = [b for b in [1, 2, 4, 8] if b <= max_bs] + list(range(16, max_bs + 1, 16))
         pool = None
         for bs in reversed(self.graph_bs):
@@ -201,6 +212,11 @@ class LayerRunner:
         ctx = get_context()
         bs = next(b for b in self.graph_bs if b >= n)
         v = self.vars
+        if self.state is not None:                 # metadata already in place (run() advanced the state)
+            v["input_ids"][:n] = input_ids
+            self.graphs[bs].replay()
+            self.last_tap, self.last_bucket = self.graph_taps[bs], bs
+            return self.model.compute_logits(v["outputs"][:n])
         for name, t in v.items():
             if name == "slot_mapping":
                 t.fill_(-1)
@@ -223,6 +239,20 @@ class LayerRunner:
             ctx = get_context()
             if ctx.block_tables is None:
                 ctx.block_tables = metadata.prepare_block_tables(seqs, self.device)
+        elif self.state is not None and len(seqs) <= 512:
+            ids, lens = [s.seq_id for s in seqs], [len(s) for s in seqs]
+            if ids == self._state_ids and lens == [n + 1 for n in self._state_lens]:
+                self.state.publish_new_pages(seqs)
+            else:                                  # new composition (a request finished, arrived or was preempted)
+                self.state.load(seqs, pending=1)
+            self.state.advance()                   # also publishes the Context
+            self._state_ids, self._state_lens = ids, lens
+            n = len(seqs)
+            ctx = get_context()
+            ctx.slot_mapping, ctx.context_lens = self.state.slot_mapping[:n], self.state.context_lens[:n]
+            ctx.block_tables = self.state.block_tables[:n]
+            input_ids = torch.tensor([s.last_token for s in seqs], dtype=torch.int64).pin_memory().to(self.device, non_blocking=True)
+            positions = self.state.positions[:n]
         else:
             input_ids, positions = metadata.prepare_decode(seqs, self.block_size, self.device)
         logits = self.run_model(input_ids, positions, is_prefill)

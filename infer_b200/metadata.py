@@ -127,12 +127,14 @@ class DecodeState:
         self.host_lens = [0] * max_batch
         self.host_pages = [0] * max_batch          # pages known to the device per row
 
-    def load(self, seqs: list[Sequence]):
-        """Full upload for a new batch composition; lengths are those BEFORE the next step's token."""
+    def load(self, seqs: list[Sequence], pending: int = 0):
+        """Full upload for a new batch composition; lengths are those BEFORE the next step's token.
+        ``pending``: tokens at the end of every sequence that the coming ``advance()`` calls will count (1 when the
+        engine has already appended the sampled token whose k/v the next step stores)."""
         n, width = len(seqs), self.block_tables.shape[1]
         if n > self.context_lens.numel() or any(len(s.block_table) > width for s in seqs):
             raise ValueError("batch or page list exceeds the static buffers")
-        lens = [len(s) for s in seqs] + [0] * (self.context_lens.numel() - n)
+        lens = [len(s) - pending for s in seqs] + [0] * (self.context_lens.numel() - n)
         rows = [s.block_table + [-1] * (width - len(s.block_table)) for s in seqs]
         rows += [[-1] * width] * (self.context_lens.numel() - n)
         self.context_lens.copy_(torch.tensor(lens, dtype=torch.int32), non_blocking=True)

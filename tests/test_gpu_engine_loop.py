@@ -29,13 +29,15 @@ def _oracle_step(tap, ctx, n_rows, is_prefill, kc, vc, scale):
     return o.view(want.shape), want
 
 
-@pytest.mark.parametrize("eager", [False, True], ids=["bucket-graphs", "eager"])
-def test_engine_loop_against_oracle(eager):
+@pytest.mark.parametrize("eager,device_metadata", [(False, False), (True, False), (False, True)],
+                         ids=["bucket-graphs", "eager", "bucket-graphs-device-metadata"])
+def test_engine_loop_against_oracle(eager, device_metadata):
     torch.cuda.set_device(0)
     num_blocks, hq, hkv = 7, 16, 8
     sch, seqs, c_prompt = scenario(num_blocks)
     model = AttentionLayerModel(hidden=256, n_q_heads=hq, n_kv_heads=hkv, vocab=1000, max_position=2048, device="cuda")
-    runner = LayerRunner(model, num_blocks, 256, max_num_seqs=8, max_model_len=1536, device="cuda", enforce_eager=eager)
+    runner = LayerRunner(model, num_blocks, 256, max_num_seqs=8, max_model_len=1536, device="cuda", enforce_eager=eager,
+                         device_metadata=device_metadata)
     assert eager or runner.graph_bs == [1, 2, 4, 8]
     runner.kv_cache.zero_()                               # the capture's warm-up steps wrote nothing (slot -1), but be explicit
     engine = Engine(runner, sch)
