@@ -232,8 +232,8 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_kernel(DecodeParams
         // Fused append.  The token at position ctx - 1 is not in the pool yet: its k and v rows come with the call.
         // Every warp of a segment that ends its sequence starts an asynchronous copy of this head's two rows into
         // its 512 bytes of staging memory (lanes 0-15 sixteen bytes of k each, lanes 16-31 of v): no register and
-        // no instruction waits for them (a plain load here costs microseconds behind the bulk copies queued on
-        // this SM).  The warp whose 16 tokens of the last tile include the position moves the rows, once the tile
+        // no instruction waits for them (with plain loads here, and a register holding the rows, the step measured
+        // slower than two launches: such a load takes about a microsecond to return while the SM streams tiles).  The warp whose 16 tokens of the last tile include the position moves the rows, once the tile
         // has arrived, into the tile in shared memory, where the products below find them, and into the pool, where
         // the next step will.  The last tile of a (sequence, head) belongs to one CTA and a tile's rows to one warp,
         // so each row is written once; what the bulk copy brought for that row (stale or half-written) is replaced.
