@@ -29,7 +29,8 @@ One JSON line is printed by rank 0:
              step they scale from measured in the same process;
   engine     (N = 1) the path inside the engine loop: scheduler, step metadata, one synthetic-weight attention
              layer, decode through per-bucket CUDA graphs; prefill tok/s and decode ms per step, host work included;
-  validated  (N > 1) attention outputs all-gathered over NCCL and checked against the CPU oracle;
+  validated  the timed step's outputs (all-gathered over NCCL when N > 1) checked against the CPU oracle on three
+             sequences, and the rows it appended compared bit for bit with the inputs;
   reference_gpu  (N = 1) the library call the reference makes for decode (flash_attn's
              flash_attn_with_kvcache), timed on the same tensors;
   cpu_baseline  the torch-CPU restatement of the reference path, timed on a sample.
@@ -331,8 +332,11 @@ def validate_gathered(w, out, world, rank, n_check=3):
     pages and queries of every shard) and compare with the CPU oracle of the unsharded problem on rank 0."""
     import numpy as np
     import torch.distributed as dist
-    from infer_b200.sharding import gather_heads
     from oracle import paged_kv_oracle as oracle
+    if world > 1:
+        from infer_b200.sharding import gather_heads
+    else:
+        gather_heads = lambda t: t                     # one GPU holds every head: nothing to gather
     full_out = gather_heads(out)
     full_q = gather_heads(w.q)
     order = np.argsort(w.context_lens)
@@ -349,9 +353,18 @@ def validate_gathered(w, out, world, rank, n_check=3):
             err = (full_out[b:b + 1].float().cpu() - want).abs()
             max_err = max(max_err, float(err.max()))
             ok = ok and bool((err <= 2e-2 + 1e-2 * want.abs()).all())
-    dist.barrier()
-    return {"nranks": world, "sequences": len(picks), "max_err": max_err, "ok": ok,
-            "tolerance": "2e-2 abs + 1e-2 rel against the CPU oracle", "gather": "nccl all_gather"}
+    # the rows the step appended: bit-exact in the pools, every sequence
+    flat_k, flat_v = w.k_cache.view(-1, w.n_kv_heads, 128), w.v_cache.view(-1, w.n_kv_heads, 128)
+    at = w.slot_mapping.to(out.device).long()
+    rows_ok = bool(torch.equal(flat_k[at], w.k)) and bool(torch.equal(flat_v[at], w.v))
+    if world > 1:
+        flag = torch.tensor([int(rows_ok)], device=out.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        rows_ok = bool(flag.item())
+        dist.barrier()
+    return {"nranks": world, "sequences": len(picks), "max_err": max_err, "ok": ok and rows_ok, "appended_rows_bit_exact": rows_ok,
+            "tolerance": "2e-2 abs + 1e-2 rel against the CPU oracle",
+            "gather": "nccl all_gather" if world > 1 else "none (one GPU holds every head)"}
 
 
 # ------------------------------------------------------------------------------- sub-benchmarks
@@ -830,9 +843,12 @@ def main():
         ops.paged_attn_decode(w.q, w.k_cache, w.v_cache, cl, bt, w.scale, out=out)
         flash = bench_flash_attn(w, cl, bt, slots, out, args.steps)
     validated = None
-    if world > 1:
-        ops.store_kvcache(w.k, w.v, w.k_cache, w.v_cache, slots)
-        ops.paged_attn_decode(w.q, w.k_cache, w.v_cache, cl, bt, w.scale, out=out)
+    if world > 1 or not args.profile:
+        # the step as it was timed (one launch), on pools whose new rows are cleared first
+        flat = w.slot_mapping.to(device).long()
+        w.k_cache.view(-1, w.n_kv_heads, 128)[flat] = 0
+        w.v_cache.view(-1, w.n_kv_heads, 128)[flat] = 0
+        ops.paged_attn_decode_append(w.q, w.k, w.v, w.k_cache, w.v_cache, cl, bt, w.scale, out=out)
         validated = validate_gathered(w, out, world, rank)
 
     # ---- max over ranks
