@@ -11,7 +11,6 @@
 //
 // The work split (equal KV bytes per CTA, two scratch slots per CTA, the last CTA of a split
 // sequence merging its partials) is described in decode_common.cuh.
-#include <cstdlib>
 #include <mutex>
 #include <utility>
 
@@ -33,7 +32,8 @@ constexpr int kMergeSlotFloats = 36 * 32;         // 32 accumulators + up to two
 // row r belongs to query head hg * rows + r.
 __device__ __forceinline__ void merge_if_last(const DecodeParams& p, const int* s_tp, int ng, const Segment& sg,
                                               int chunk, int rows, volatile int* s_flag) {
-    const int first = ng * s_tp[sg.b] + sg.hg * sg.ntiles;
+    // first real tile of the (b, hg) in the padded numbering; the CTAs c0..c1 hold its real tiles
+    const int first = ng * s_tp[sg.b] + sg.hg * (sg.ntiles + p.seg_overhead) + p.seg_overhead;
     const int c0 = first / chunk, c1 = (first + sg.ntiles - 1) / chunk;
     asm volatile("bar.sync 1, 256;" ::: "memory");          // every partial store of this CTA is issued
     if (threadIdx.x == 0) {
@@ -131,7 +131,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_kernel(DecodeParams
     // launches never share an SM - each takes nearly all of its shared memory - so nothing is lost.)
     if (p.new_k != nullptr) pdl_wait();
     uint8_t* s_rem = smem + TmaSmem::rem;
-    build_tile_prefix(p.context_lens, p.batch, TT, s_tp, s_scan, s_rem);   // ends with __syncthreads
+    build_tile_prefix(p.context_lens, p.batch, TT, s_tp, s_scan, s_rem, p.seg_overhead);   // ends with __syncthreads
     // Everything above only reads step metadata; the pools and q may still be written by the
     // kernel in front of this one (the append) when this kernel was launched programmatically.
     pdl_launch_dependents();
@@ -150,7 +150,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_kernel(DecodeParams
         uint32_t it = 0;
         bool ok = true;
         for (int g = lo; g < hi && ok;) {
-            const Segment sg = locate_segment(s_tp, p.batch, ng, g, hi);
+            const Segment sg = locate_segment(s_tp, p.batch, ng, g, hi, p.seg_overhead);
             const int32_t* table = p.block_tables + int64_t(sg.b) * p.bt_stride;
             for (int t = sg.t0; t < sg.t1; ++t, ++it) {
                 const uint32_t s = it % kStages, ph = (it / kStages) & 1;
@@ -188,7 +188,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_kernel(DecodeParams
                     }
                 }
             }
-            g += sg.t1 - sg.t0;
+            g += sg.span;
         }
         // Do not leave while a copy may still be in flight: wait for the last armed stages.
         const uint32_t armed = p.stall_producer ? 0u : (it < uint32_t(kStages) ? it : uint32_t(kStages));
@@ -210,7 +210,11 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_kernel(DecodeParams
     // A wait that runs out only clears `ok`: the warp keeps walking the same tiles and
     // barriers as its siblings (without computing) so that no named barrier is left short.
     for (int g = lo; g < hi;) {
-        const Segment sg = locate_segment(s_tp, p.batch, ng, g, hi);
+        const Segment sg = locate_segment(s_tp, p.batch, ng, g, hi, p.seg_overhead);
+        if (sg.t0 == sg.t1) {                      // only padding of this (b, hg) lies in the range
+            g += sg.span;
+            continue;
+        }
         const int ctx = p.context_lens[sg.b];
         const int head = sg.hg * HPC + hl;
         // Query fragments: rows 0..group-1 of the 16-row A operand, zero elsewhere.
@@ -380,7 +384,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_kernel(DecodeParams
             }
         }
         if (!(sg.t0 == 0 && sg.t1 == sg.ntiles)) merge_if_last(p, s_tp, ng, sg, chunk, HPC * p.group, s_flag);
-        g += sg.t1 - sg.t0;
+        g += sg.span;
     }
     if (!ok && lane == 0) atomicExch(p.status, kStatusMagic | 2);
 }
@@ -450,7 +454,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_fp8_kernel(DecodePa
         fence_proxy_async();
     }
     uint8_t* s_rem = smem + L::rem;
-    build_tile_prefix(p.context_lens, p.batch, TT, s_tp, s_scan, s_rem);
+    build_tile_prefix(p.context_lens, p.batch, TT, s_tp, s_scan, s_rem, p.seg_overhead);
     pdl_launch_dependents();
     pdl_wait();
 
@@ -467,7 +471,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_fp8_kernel(DecodePa
         uint32_t it = 0;
         bool ok = true;
         for (int g = lo; g < hi && ok;) {
-            const Segment sg = locate_segment(s_tp, p.batch, ng, g, hi);
+            const Segment sg = locate_segment(s_tp, p.batch, ng, g, hi, p.seg_overhead);
             const int32_t* table = p.block_tables + int64_t(sg.b) * p.bt_stride;
             for (int t = sg.t0; t < sg.t1; ++t, ++it) {
                 const uint32_t s = it % kStages, ph = (it / kStages) & 1;
@@ -511,7 +515,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_fp8_kernel(DecodePa
                     tma_load_3d(vdst + hl * kHeadBytes, mv, bar, 0, sg.hg * HPC + hl, slot0);
                 }
             }
-            g += sg.t1 - sg.t0;
+            g += sg.span;
         }
         const uint32_t armed = p.stall_producer ? 0u : (it < uint32_t(kStages) ? it : uint32_t(kStages));
         for (uint32_t j = 0; j < armed; ++j) {
@@ -535,7 +539,11 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_fp8_kernel(DecodePa
     bool ok = true;
 
     for (int g = lo; g < hi;) {
-        const Segment sg = locate_segment(s_tp, p.batch, ng, g, hi);
+        const Segment sg = locate_segment(s_tp, p.batch, ng, g, hi, p.seg_overhead);
+        if (sg.t0 == sg.t1) {                      // only padding of this (b, hg) lies in the range
+            g += sg.span;
+            continue;
+        }
         const int ctx = p.context_lens[sg.b];
         const int head = sg.hg * HPC + hl;
         // B fragments of Q^T in f16: column gid is query head gid of the group.  MMA k-slots
@@ -750,7 +758,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_fp8_kernel(DecodePa
             }
         }
         if (!(sg.t0 == 0 && sg.t1 == sg.ntiles)) merge_if_last(p, s_tp, ng, sg, chunk, HPC * p.group, s_flag);
-        g += sg.t1 - sg.t0;
+        g += sg.span;
     }
     if (!ok && lane == 0) atomicExch(p.status, kStatusMagic | 2);
 }
@@ -837,6 +845,12 @@ int decode_prepare_device() {
     return INFER_OK;
 }
 
+// Tiles of padding in front of every (sequence, head group) in the numbering that is cut into equal ranges.
+// Swept on the GPU, us per launch at 0 / 1 / 2 / 3 / 4 tiles: Qwen3-8B batch 64 171.5 / 165.9 / 163.8 / 163.3 / 165.9,
+// long-context batch 256 830 / 802 / 784 / 776 / 778, one KV head of the batch-64 workload 30.7 / 29.7 / 29.0 / 28.0 /
+// 27.9, the 8-sequence Qwen3-0.6B case 12.4 / 11.4 / 9.3 / 10.0 / 9.9.
+constexpr int kSegOverheadTiles = 3;
+
 // The step's new k and v rows for a launch that also appends them (null: the pools already hold them).
 struct NewRows {
     const void* k = nullptr;
@@ -885,6 +899,7 @@ static int paged_decode(const infer_kv_pool_t* pool, void* out, const void* q, c
     p.scale_log2 = softmax_scale * 1.4426950408889634f;
     p.wait_limit = wait_limit;
     p.stall_producer = stall_producer;
+    p.seg_overhead = kSegOverheadTiles;
     p.new_k = static_cast<const __nv_bfloat16*>(rows.k);
     p.new_v = static_cast<const __nv_bfloat16*>(rows.v);
     p.new_k_stride = rows.k_stride;
