@@ -329,34 +329,50 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_kernel(DecodeParams
         l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
         l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
 
-        // tree merge of the WPH warps that share a kv head
-        if (WPH > 1) {
+        // merge of the WPH warps that share a kv head
+        auto put = [&](float* slot) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                slot[(2 * j) * 32 + lane] = o[j][0];
+                slot[(2 * j + 1) * 32 + lane] = o[j][1];
+            }
+            slot[32 * 32 + lane] = m_run;
+            slot[33 * 32 + lane] = l_run;
+        };
+        auto take = [&](const float* slot) {
+            const float m2 = slot[32 * 32 + lane], l2 = slot[33 * 32 + lane];
+            const float mm = fmaxf(m_run, m2);
+            const float a1 = m_run == -INFINITY ? 0.f : fast_exp2(m_run - mm);
+            const float a2 = m2 == -INFINITY ? 0.f : fast_exp2(m2 - mm);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                o[j][0] = o[j][0] * a1 + slot[(2 * j) * 32 + lane] * a2;
+                o[j][1] = o[j][1] * a1 + slot[(2 * j + 1) * 32 + lane] * a2;
+            }
+            l_run = l_run * a1 + l2 * a2;
+            m_run = mm;
+        };
+        if (WPH == 8) {
+            // eight warps, four slots, three barriers: warps 4-7 hand over to warps 0-3, warps 1-3 hand over (each in
+            // the slot it has just read, which nobody else looks at) to warp 0
+            if (tw >= 4) put(s_merge + (tw - 4) * kMergeSlotFloats);
+            consumer_bar();
+            if (tw < 4) take(s_merge + tw * kMergeSlotFloats);
+            if (tw >= 1 && tw < 4) put(s_merge + tw * kMergeSlotFloats);
+            consumer_bar();
+            if (tw == 0) {
+                take(s_merge + 1 * kMergeSlotFloats);
+                take(s_merge + 2 * kMergeSlotFloats);
+                take(s_merge + 3 * kMergeSlotFloats);
+            }
+            consumer_bar();                       // the slots are written again at the end of the next segment
+        } else if (WPH > 1) {
 #pragma unroll
             for (int stride = WPH / 2; stride >= 1; stride >>= 1) {
                 float* slot = s_merge + (hl * stride + (tw % stride)) * kMergeSlotFloats;
-                if (tw >= stride && tw < 2 * stride) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        slot[(2 * j) * 32 + lane] = o[j][0];
-                        slot[(2 * j + 1) * 32 + lane] = o[j][1];
-                    }
-                    slot[32 * 32 + lane] = m_run;
-                    slot[33 * 32 + lane] = l_run;
-                }
+                if (tw >= stride && tw < 2 * stride) put(slot);
                 consumer_bar();
-                if (tw < stride) {
-                    const float m2 = slot[32 * 32 + lane], l2 = slot[33 * 32 + lane];
-                    const float mm = fmaxf(m_run, m2);
-                    const float a1 = m_run == -INFINITY ? 0.f : fast_exp2(m_run - mm);
-                    const float a2 = m2 == -INFINITY ? 0.f : fast_exp2(m2 - mm);
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        o[j][0] = o[j][0] * a1 + slot[(2 * j) * 32 + lane] * a2;
-                        o[j][1] = o[j][1] * a1 + slot[(2 * j + 1) * 32 + lane] * a2;
-                    }
-                    l_run = l_run * a1 + l2 * a2;
-                    m_run = mm;
-                }
+                if (tw < stride) take(slot);
                 consumer_bar();
             }
         }
