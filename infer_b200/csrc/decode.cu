@@ -35,9 +35,9 @@ __device__ __forceinline__ void merge_if_last(const DecodeParams& p, const int* 
     // first real tile of the (b, hg) in the padded numbering; the CTAs c0..c1 hold its real tiles
     const int first = ng * s_tp[sg.b] + sg.hg * (sg.ntiles + p.seg_overhead) + p.seg_overhead;
     const int c0 = first / chunk, c1 = (first + sg.ntiles - 1) / chunk;
-    asm volatile("bar.sync 1, 256;" ::: "memory");          // every partial store of this CTA is issued
+    asm volatile("bar.sync 1, 256;" ::: "memory");          // every partial store of this CTA is ordered before ...
     if (threadIdx.x == 0) {
-        __threadfence();                                     // ... and visible before the ticket is
+        __threadfence();                                     // ... this fence, which is cumulative: they are visible before the ticket is
         const int ticket = atomicAdd(p.counters + c0, 1);
         const int last = ticket == c1 - c0;
         if (last) p.counters[c0] = 0;                        // all participants have drawn: ready for the next launch
@@ -396,7 +396,6 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_kernel(DecodeParams
                     p.ws_ml[(slot * rows + r) * 2 + 0] = m_run;
                     p.ws_ml[(slot * rows + r) * 2 + 1] = l_run;
                 }
-                __threadfence();
             }
         }
         if (!(sg.t0 == 0 && sg.t1 == sg.ntiles)) merge_if_last(p, s_tp, ng, sg, chunk, HPC * p.group, s_flag);
@@ -769,7 +768,6 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_fp8_kernel(DecodePa
                         p.ws_ml[(slot * rows + r) * 2 + 0] = m_run[y];
                         p.ws_ml[(slot * rows + r) * 2 + 1] = l_run[y];
                     }
-                    __threadfence();
                 }
             }
         }
