@@ -86,6 +86,14 @@ def measured_tflops():
         return FALLBACK_TFLOPS, "of fallback"
 
 
+def measured_tflops_burst():
+    try:
+        with open(ROOT / "MEASURED_PEAKS.json") as f:
+            return float(json.load(f)["bf16_tflops"])
+    except Exception:
+        return None
+
+
 class ClockSampler:
     """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
@@ -390,6 +398,14 @@ def bench_prefill(ops, device, n_seqs, steps, warmup, dense=True, sample_clocks=
     for _ in range(warmup):
         step()
     torch.cuda.synchronize()
+    # a burst on a GPU that has idled for two seconds (the way MEASURED_PEAKS.json's bf16_tflops was taken), before the
+    # sustained measurement below: under the 1000 W cap the chip clocks lower once the cap binds
+    burst_tflops = None
+    if sample_clocks:
+        time.sleep(2.0)
+        burst_ms = _timed(lambda: ops.paged_attn_prefill(w.q, w.k_cache, w.v_cache, cu_q, cu_k, mq, mk, w.scale, bt, out=out),
+                          10, 0, stream)
+        burst_tflops = flops / (burst_ms * 1e-3) / 1e12
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
     with ClockSampler(device.index) as clocks:
         t_end = time.time() + (0.5 if sample_clocks else 0.0)
@@ -418,6 +434,9 @@ def bench_prefill(ops, device, n_seqs, steps, warmup, dense=True, sample_clocks=
         "flops_per_step": flops, "tflops_step": flops / (step_ms * 1e-3) / 1e12, "ms_per_step": step_ms,
         "attn_ms": attn_ms, "attn_ms_min": min(attn_all), "attn_ms_max": max(attn_all),
         "tflops": achieved, "peak": peak, "frac": achieved / peak, "peak_kind": kind, "bound": "tensor",
+        "tflops_burst": burst_tflops, "burst_note": "10 calls after two idle seconds; compare with bf16_tflops (burst) of "
+                                                    "MEASURED_PEAKS.json, `tflops` with bf16_tflops_sustained",
+        "frac_burst": (burst_tflops / measured_tflops_burst()) if burst_tflops and measured_tflops_burst() else None,
         "timed_steps": steps * rounds,
         "traffic": PREFILL_TRAFFIC_PER_SEQUENCE * n_seqs,
         "append": {"rows": n_tok, "ms": append_ms, "tok_s": n_tok / (append_ms * 1e-3),
