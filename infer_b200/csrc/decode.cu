@@ -237,10 +237,11 @@ __global__ void __launch_bounds__(kTmaThreads, 1) decode_tma_kernel(DecodeParams
         // Every warp of a segment that ends its sequence starts an asynchronous copy of this head's two rows into
         // its 512 bytes of staging memory (lanes 0-15 sixteen bytes of k each, lanes 16-31 of v): no register and
         // no instruction waits for them (with plain loads here, and a register holding the rows, the step measured
-        // slower than two launches: such a load takes about a microsecond to return while the SM streams tiles).  The warp whose 16 tokens of the last tile include the position moves the rows, once the tile
-        // has arrived, into the tile in shared memory, where the products below find them, and into the pool, where
-        // the next step will.  The last tile of a (sequence, head) belongs to one CTA and a tile's rows to one warp,
-        // so each row is written once; what the bulk copy brought for that row (stale or half-written) is replaced.
+        // slower than two launches: such a load takes about a microsecond to return while the SM streams tiles).
+        // The warp whose 16 tokens of the last tile include the position moves the rows, once the tile has arrived,
+        // into the tile in shared memory, where the products below find them, and into the pool, where the next
+        // step will.  The last tile of a (sequence, head) belongs to one CTA and a tile's rows to one warp, so each
+        // row is written once; what the bulk copy brought for that row (stale or half-written) is replaced.
         const bool appends = p.new_k != nullptr && sg.t1 == sg.ntiles;
         const uint32_t stage_row = tiles_u32 + TmaSmem::patch + warp * 512 + lane * 16;
         if (appends) {
