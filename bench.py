@@ -63,9 +63,10 @@ UNIT = "GB/s"
 BASE_BATCH = 64
 # DRAM traffic figures from the ncu captures summarised under profiles/ (dram__bytes_read.sum +
 # dram__bytes_write.sum of one launch of a small case; each tile is read once, so traffic grows with the
-# units processed): decode_tma_kernel 253.5 MB for 249.9 MB of KV; prefill_tc_kernel 119.0 MB for 4 sequences.
+# units processed): decode_tma_kernel 253.5 MB for 249.9 MB of KV; prefill_tc_kernel 520.0 MB for the 16 sequences
+# of the benchmark itself (119.0 MB for a 4-sequence case).
 DECODE_TRAFFIC_PER_KV_BYTE = 253.5 / 249.9
-PREFILL_TRAFFIC_PER_SEQUENCE = 119.0e6 / 4
+PREFILL_TRAFFIC_PER_SEQUENCE = 520.0e6 / 16
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_TFLOPS = 1400.0
 
