@@ -491,3 +491,32 @@ def test_fused_append_decode_rows_and_output_in_pinned_host_memory():
     assert torch.equal(out_h, want.cpu())
     assert torch.equal(d["k_cache"].view(torch.int16), d2["k_cache"].view(torch.int16))
     assert torch.equal(d["v_cache"].view(torch.int16), d2["v_cache"].view(torch.int16))
+
+
+@pytest.mark.parametrize("hq,hkv", [(24, 8), (40, 8), (7, 1), (48, 8), (8, 8)])
+def test_fused_append_decode_any_group_size(hq, hkv):
+    """The one-launch step for query-head groups of 3, 5, 7, 6 and 1 heads (Qwen3-14B is 40 over 8)."""
+    rng = np.random.default_rng(hq + 1)
+    lens = rng.integers(100, 2600, size=10)
+    w = workloads._decode_workload("any-group", 78 + hq, hq, hkv, lens, workloads._pool_size(lens), "cpu")
+    got, want = _fused_step(w)
+    assert_close(got, want, ATOL_BF16, RTOL_BF16, f"fused step {hq}q/{hkv}kv")
+
+
+def test_fused_append_decode_long_context_full_size():
+    """The long-context shape at full size (batch 256, contexts up to 32768 tokens, half the batch sharing the
+    pages of a 2048-token prefix) through the one-launch step: pools bit for bit on the GPU against the inputs,
+    outputs of the shortest, a middle and the longest sequence against the oracle."""
+    w = workloads.config4(device="cuda", longest_at_cap=True)
+    cl, bt = w.context_lens_tensor().cuda(), w.block_tables_tensor().cuda()
+    got = ops.paged_attn_decode_append(w.q, w.k, w.v, w.k_cache, w.v_cache, cl, bt, w.scale)
+    torch.cuda.synchronize()
+    at = w.slot_mapping.cuda().long()
+    assert torch.equal(w.k_cache.view(-1, w.n_kv_heads, 128)[at], w.k) and torch.equal(w.v_cache.view(-1, w.n_kv_heads, 128)[at], w.v)
+    order = np.argsort(w.context_lens)
+    for b in (int(order[0]), int(order[len(order) // 2]), int(order[-1])):
+        pages = torch.tensor(w.block_tables[b], device="cuda")
+        kc, vc = w.k_cache[pages].cpu(), w.v_cache[pages].cpu()
+        local = torch.arange(len(pages), dtype=torch.int32)[None]
+        want = oracle.paged_decode(w.q[b:b + 1].cpu(), kc, vc, torch.tensor([w.context_lens[b]], dtype=torch.int32), local, w.scale)
+        assert_close(got[b:b + 1], want, ATOL_BF16, RTOL_BF16, f"fused step, long-context, sequence {b} ({w.context_lens[b]} tokens)")
